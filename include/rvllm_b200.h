@@ -1,0 +1,198 @@
+/*
+ * rvllm_b200 — C ABI of the B200 (sm_100a) FP8 decode hot path.
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" is CUDA device memory
+ * owned by the caller; the library never allocates or frees device memory on these
+ * paths (the decode-stack object in section 7 is the one exception and says so).
+ * `stream` is a cudaStream_t / CUstream passed as void*.  All launches are
+ * asynchronous on that stream and safe to record into a CUDA graph.
+ *
+ * Return value: 0 on success; a negative RVLLM_E_* code otherwise.  After a failure
+ * rvllm_b200_last_error() returns a thread-local, human-readable reason.  Functions that
+ * carry a reference entry-point name (cutlass_*, fa_sm89_*) keep the reference's own
+ * convention (0 ok, non-zero error).
+ *
+ * "Reference" below is solidsf-inc/rvLLM v0.3.0; each entry cites the reference
+ * interface it replaces as file:line within that project.
+ */
+#ifndef RVLLM_B200_H
+#define RVLLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RVLLM_OK 0
+#define RVLLM_E_INVALID (-1)     /* argument failed validation; nothing was launched */
+#define RVLLM_E_LAUNCH (-2)      /* CUDA refused the launch */
+#define RVLLM_E_UNSUPPORTED (-3) /* shape outside what the kernels implement */
+#define RVLLM_E_WORKSPACE (-4)   /* workspace missing, misaligned or too small */
+#define RVLLM_E_ARTIFACT (-5)    /* manifest / artifact verification failed */
+#define RVLLM_E_NO_DEVICE (-6)   /* no usable CUDA device / driver */
+
+/* 16-bit activation types */
+#define RVLLM_F16 0
+#define RVLLM_BF16 1
+/* GEMM output kinds */
+#define RVLLM_OUT_F16 0
+#define RVLLM_OUT_BF16 1
+#define RVLLM_OUT_F32 2
+/* MLP activations */
+#define RVLLM_ACT_SILU 0
+#define RVLLM_ACT_GELU_TANH 1
+
+/* ---- 0. library ------------------------------------------------------------------- */
+int rvllm_b200_abi_version(void);          /* = 1 */
+const char* rvllm_b200_last_error(void);   /* thread-local; "" when no error */
+const char* rvllm_b200_build_arch(void);   /* "sm_100a" */
+
+/* ---- 1. fused RMSNorm + per-token FP8 quantisation ----------------------------------
+ * Replaces FusedRmsnormFp8QuantLaunch / FusedAddRmsnormFp8QuantLaunch /
+ * QuantizeFp8PerTokenLaunch (v3/crates/rvllm-fused/src/launcher.rs:96-274) and the kernels
+ * they launch (kernels/fused_rmsnorm_fp8_quant.cu:52,108,166).  Same validation: hidden /
+ * dim a multiple of 8, num_tokens > 0, dim <= 65536 for the plain quantiser; same launch
+ * geometry (grid = tokens, block = min(hidden, 1024), quantiser block >= 256).
+ * out_fp8 [T, H] u8, scale [T] f32, in / gamma / residual 16-bit of `dtype`. */
+int rvllm_fused_rmsnorm_fp8_quant_validate(uint32_t num_tokens, uint32_t hidden, float eps);
+int rvllm_fused_rmsnorm_fp8_quant_launch(uint32_t num_tokens, uint32_t hidden, float eps, void* out_fp8,
+                                         float* scale, const void* in_hidden, const void* gamma, int dtype,
+                                         void* stream);
+int rvllm_fused_add_rmsnorm_fp8_quant_launch(uint32_t num_tokens, uint32_t hidden, float eps, void* out_fp8,
+                                             float* scale, void* residual_out, const void* in_hidden,
+                                             const void* residual_in, const void* gamma, int dtype,
+                                             void* stream);
+int rvllm_quantize_fp8_per_token_validate(uint32_t num_tokens, uint32_t dim);
+int rvllm_quantize_fp8_per_token_launch(uint32_t num_tokens, uint32_t dim, void* out_fp8, float* scale,
+                                        const void* in, int dtype, void* stream);
+
+/* ---- 2. act(gate) * up + per-token FP8 quantisation ---------------------------------
+ * Replaces FusedSiluMulFp8QuantLaunch (launcher.rs:280-323; kernels
+ * kernels/fused_silu_fp8_quant.cu:42, v3/kernels/fused_gelu_mul_fp8_quant.cu:53).
+ * gate_up [T, 2*I] 16-bit laid out [gate | up]; out_fp8 [T, I]; scale [T]. */
+int rvllm_fused_act_mul_fp8_quant_validate(uint32_t num_tokens, uint32_t intermediate);
+int rvllm_fused_act_mul_fp8_quant_launch(uint32_t num_tokens, uint32_t intermediate, int act, void* out_fp8,
+                                         float* scale, const void* gate_up, int dtype, void* stream);
+
+/* ---- 3. greedy argmax ---------------------------------------------------------------
+ * Replaces ArgmaxLaunch (launcher.rs:329-399; kernels/argmax.cu:81,132).  logits [T, V]
+ * f32, out [T] i32.  use_grid != 0 selects the multi-CTA-per-row variant, which first
+ * clears `out` with an async memset exactly as the reference launcher does. */
+int rvllm_argmax_validate(uint32_t num_tokens, uint32_t vocab);
+int rvllm_argmax_launch(uint32_t num_tokens, uint32_t vocab, const float* logits, int32_t* out, int use_grid,
+                        void* stream);
+
+/* ---- 4. FP8 E4M3 GEMMs --------------------------------------------------------------
+ * A [M, K] u8 row-major, per-token scale a_scale[M]; W [N, K] u8 row-major, per-output-
+ * channel scale w_scale[N]; f32 accumulation; deterministic (no float atomics).
+ *
+ * cutlass_fp8_gemm_channelscale / _workspace: the reference's exported pair
+ * (kernels/cutlass_fp8_gemm_channelscale.cu:98,163; loaded by
+ * v3/crates/rvllm-cutlass/src/lib_so.rs:403-415): D_f16 = f16(row_scale[m] * (col_scale[n] * acc)).
+ * cutlass_fp8_gemm_v0 / cutlass_fp8_gemm_residual_v0 (+ _workspace_size): scalar weight
+ * scale `b_scale` (device pointer to one f32), optional f16 residual
+ * (kernels/cutlass_fp8_gemm_residual.cu:252-287, lib_so.rs:1486-1500). */
+int cutlass_fp8_gemm_channelscale(void* out_f16, const void* a_fp8, const void* b_fp8, const void* row_scale,
+                                  const void* col_scale, int M, int N, int K, void* workspace,
+                                  size_t workspace_size, void* stream);
+size_t cutlass_fp8_gemm_channelscale_workspace(int M, int N, int K);
+int cutlass_fp8_gemm_v0(void* out_f16, const void* a_fp8, const void* b_fp8, const void* a_scales,
+                        const void* b_scale, int M, int N, int K, void* workspace, size_t workspace_size,
+                        void* stream);
+size_t cutlass_fp8_gemm_v0_workspace_size(int M, int N, int K);
+int cutlass_fp8_gemm_residual_v0(void* out_f16, const void* a_fp8, const void* b_fp8, const void* a_scales,
+                                 const void* b_scale, const void* residual_f16, int M, int N, int K,
+                                 void* workspace, size_t workspace_size, void* stream);
+size_t cutlass_fp8_gemm_residual_v0_workspace_size(int M, int N, int K);
+
+/* New exports in the same style.  The reference has no single kernel that applies a
+ * per-channel weight scale and a residual (kernels/cutlass_fp8_gemm_channelscale.cu:3 vs
+ * kernels/cutlass_fp8_gemm_residual.cu:3); its executor composes them
+ * (v3/crates/rvllm-runtime/src/layer_exec.rs:439-450,523-534).
+ * out_kind: RVLLM_OUT_*; residual (may be NULL, may alias out) has the output's 16-bit type.
+ * impl: 0 = pick by shape, 1 = weight-streaming mma.sync kernel, 2 = tcgen05/TMEM kernel. */
+int rvllm_fp8_gemm_channelscale(void* out, int out_kind, const void* a_fp8, const void* w_fp8,
+                                const float* a_scale, const float* w_scale, const void* residual, int M, int N,
+                                int K, int impl, void* workspace, size_t workspace_size, void* stream);
+size_t rvllm_fp8_gemm_workspace(int M, int N, int K);
+/* Status word of the tcgen05 kernel's bounded waits: 0 = every wait completed; otherwise
+ * (site << 16 | CTA) of the first wait that ran out.  Synchronous (copies from the device);
+ * for tests and diagnosis, not for the decode loop.  reset != 0 clears it. */
+int rvllm_fp8_gemm_tc_status(int* status, int reset);
+
+/* gate|up projection + act(gate)*up + per-token FP8 re-quantisation in one call
+ * (reference: GEMM at layer_exec.rs:484-494 followed by FusedSiluMulFp8QuantLaunch :509).
+ * W [2*I, K] rows [gate(0..I) | up(I..2I)]; out_fp8 [M, I]; out_scale [M].
+ * Needs rvllm_fp8_gemm_gateup_workspace(M, I, K) bytes of workspace. */
+int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void* a_fp8, const void* w_fp8,
+                                    const float* a_scale, const float* w_scale, int M, int I, int K, int act,
+                                    int dtype, int impl, void* workspace, size_t workspace_size, void* stream);
+size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K);
+
+/* ---- 5. FP8-KV paged GQA decode attention -------------------------------------------
+ * The fa_sm89_* family the reference loads from libfa_sm89_kernels.so
+ * (v3/kernels/fp8_decode_v2.cu:939-1112; loader v3/crates/rvllm-attention/src/lib.rs:353-493).
+ * Output f16 [batch, heads, head_dim]; head_dim in {128, 256, 512}. */
+int rvllm_fa_sm89_abi_version(void);          /* 2 */
+int fa_sm89_fp8_output_dtype(void);           /* 1 = f16 */
+int fa_sm89_fp8_output_element_size(void);    /* 2 */
+uint64_t fa_sm89_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim);
+int fa_sm89_paged_decode_fp8(void* q_fp8, void* k_cache_fp8, void* v_cache_fp8, void* output,
+                             void* block_tables, void* context_lens, void* workspace, size_t workspace_bytes,
+                             void* k_scale_cache, void* v_scale_cache, void* q_scale_cache, float* q_descale,
+                             float* k_descale, float* v_descale, float scale, int batch_size, int num_heads,
+                             int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                             int num_blocks_total, int window_size_left, void* stream);
+/* Present because the reference loader requires the symbols; f16-KV decode and FP8 prefill
+ * are outside this path and return -1. */
+int fa_sm89_paged_decode(void* q, void* k_cache, void* v_cache, void* output, void* block_tables,
+                         void* context_lens, void* workspace, size_t workspace_bytes, float scale,
+                         int batch_size, int num_heads, int num_kv_heads, int head_dim, int block_size,
+                         int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream);
+int fa_sm89_paged_prefill_fp8(void* q_fp8, void* k_cache_fp8, void* v_cache_fp8, void* output,
+                              void* block_tables, void* context_lens, void* cu_seqlens_q, void* workspace,
+                              size_t workspace_bytes, void* k_scale_cache, void* v_scale_cache,
+                              void* q_scale_cache, float* q_descale, float* k_descale, float* v_descale,
+                              float scale, int total_q, int max_seqlen_q, int batch_size, int num_heads,
+                              int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                              int num_blocks_total, int window_size_left, void* stream);
+/* Same kernel with the output type selectable and head_dim 64 allowed
+ * (PagedDecodeParams, v3/crates/rvllm-attention/src/decode.rs:14-102). */
+int rvllm_paged_decode_fp8_validate(int batch_size, int num_heads, int num_kv_heads, int head_dim,
+                                    int block_size, int max_blocks_per_seq, int num_blocks_total,
+                                    int window_size_left, float scale);
+uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim);
+int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads);
+int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
+                           int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
+                           void* workspace, size_t workspace_bytes, const float* k_scale_cache,
+                           const float* v_scale_cache, const float* q_scale_cache, const float* q_descale,
+                           const float* k_descale, const float* v_descale, float scale, int batch_size,
+                           int num_heads, int num_kv_heads, int head_dim, int block_size,
+                           int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream);
+
+/* ---- 6. neighbours of the path ------------------------------------------------------
+ * RoPE + Q quantisation + paged FP8 KV write with per-(slot, head) scales
+ * (v3/kernels/fused_rope_partial_fp8kv.cu:54; launcher
+ * v3/crates/rvllm-fused/src/gemma4_launcher.rs:248-400) with an explicit input row
+ * stride, and the token embedding gather (kernels/embedding_gather_f16.cu). */
+int rvllm_rope_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in, int in_stride, void* q_fp8,
+                            void* k_cache, void* v_cache, float* k_scale_cache, float* v_scale_cache,
+                            float* q_scale_cache, const void* cos_table, const void* sin_table,
+                            const int32_t* positions, const int32_t* slot_mapping, int num_tokens, int num_heads,
+                            int num_kv_heads, int head_dim, int rotary_dim, int max_positions,
+                            int num_cache_slots, int dtype, void* stream);
+int rvllm_embedding_gather_launch(void* out, const void* table, const int32_t* token_ids, int num_tokens,
+                                  int hidden, int vocab, void* stream);
+
+/* FP8 encode / decode of a flat array with the kernels' own convert instructions
+ * (used by the bit-exactness tests; not on the decode path). */
+int rvllm_e4m3_encode_f32(void* out_u8, const float* in, size_t n, void* stream);
+int rvllm_e4m3_decode_f32(float* out, const void* in_u8, size_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RVLLM_B200_H */

@@ -16,7 +16,7 @@
  * pin is the f64 host check of v3/crates/rvllm-bench/src/main.rs:832-843, which the
  * f64 mode below restates).
  *
- * Build: see Makefile (gcc -O3 -march=native -fopenmp -shared).
+ * Build: see Makefile (gcc -O3 -fopenmp -shared, no fast-math, no fp contraction).
  */
 #include <math.h>
 #include <stdint.h>
@@ -273,7 +273,7 @@ int orc_rmsnorm_fp8_quant(uint8_t *out, float *scales, uint16_t *residual_out,
             for (int i = 0; i < hidden; i++) {
                 float a = orc_h2f(row[i], dtype);
                 if (residual) a += orc_h2f(residual[(size_t)r * hidden + i], dtype);
-                partial[i % block_dim] += a * a; /* i ascending == thread-strided order */
+                partial[i % block_dim] = fmaf(a, a, partial[i % block_dim]); /* i ascending == thread-strided order; device code contracts to fma */
                 if (residual) {
                     uint16_t h = orc_f2h(a, dtype);
                     if (residual_out) residual_out[(size_t)r * hidden + i] = h;
@@ -352,7 +352,8 @@ int orc_quantize_fp8_per_token_f32(uint8_t *out, float *scales, const float *in,
  *         reference.rs:168-198.  Row layout [gate(0..I) | up(I..2I)]. */
 static inline float act_f32(float g, int act) {
     if (act == 0) return g / (1.0f + expf(-g));
-    float inner = 0.7978845608f * (g + 0.044715f * g * g * g);
+    float x3 = g * g * g; /* the device compiler contracts x + c*x3 into one fma */
+    float inner = 0.7978845608f * fmaf(0.044715f, x3, g);
     return 0.5f * g * (1.0f + tanhf(inner));
 }
 

@@ -1,0 +1,187 @@
+// C-ABI entry points of FP8-KV paged decode attention: validation, workspace contract, launches.
+#include <limits.h>
+#include <math.h>
+
+#include "../../include/rvllm_b200.h"
+#include "host_util.h"
+#include "paged_decode_fp8.cuh"
+
+extern "C" {
+// ---------------------------------------------------------------- stage 3: attention
+int rvllm_paged_decode_fp8_validate(int batch_size, int num_heads, int num_kv_heads, int head_dim,
+                                    int block_size, int max_blocks_per_seq, int num_blocks_total,
+                                    int window_size_left, float scale) {
+    if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0)
+        return rv_fail(RVLLM_E_INVALID, "batch, heads and kv_heads must be > 0");
+    if (num_heads % num_kv_heads != 0) return rv_fail(RVLLM_E_INVALID, "heads must be a multiple of kv_heads");
+    if (num_heads / num_kv_heads > 32) return rv_fail(RVLLM_E_INVALID, "GQA group larger than 32");
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256 && head_dim != 512)
+        return rv_fail(RVLLM_E_INVALID, "head_dim must be 64, 128, 256 or 512");
+    if (block_size <= 0 || max_blocks_per_seq <= 0 || num_blocks_total <= 0)
+        return rv_fail(RVLLM_E_INVALID, "paging dimensions must be > 0");
+    if (window_size_left < -1 || window_size_left == INT_MAX)
+        return rv_fail(RVLLM_E_INVALID, "window_size_left must be >= -1");
+    if (!isfinite(scale) || scale <= 0.0f) return rv_fail(RVLLM_E_INVALID, "scale must be finite and > 0");
+    if (batch_size > INT_MAX / num_heads) return rv_fail(RVLLM_E_INVALID, "batch * heads overflows");
+    const long long capacity = (long long)block_size * max_blocks_per_seq;
+    if (window_size_left >= 0 && (long long)window_size_left + 1 > capacity)
+        return rv_fail(RVLLM_E_INVALID, "window does not fit the block table");
+    long long elems = (long long)num_blocks_total * block_size;
+    if (elems > LLONG_MAX / num_kv_heads / head_dim) return rv_fail(RVLLM_E_INVALID, "cache size overflows");
+    return RVLLM_OK;
+}
+
+int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads) {
+    return rvattn::pick_max_chunks(batch_size, num_kv_heads);
+}
+
+uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim) {
+    if (batch_size <= 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0 ||
+        num_heads / num_kv_heads > 32 ||
+        (head_dim != 64 && head_dim != 128 && head_dim != 256 && head_dim != 512))
+        return UINT64_MAX;
+    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads);
+    if (chunks <= 1) return 0;
+    unsigned long long v = (unsigned long long)batch_size * (unsigned long long)num_heads;
+    if (v > (1ULL << 40)) return UINT64_MAX;
+    return v * (unsigned long long)chunks * (unsigned long long)(head_dim + 2) * sizeof(float);
+}
+
+}  // extern "C"
+
+namespace {
+
+template <int HD, int GT, typename OutT>
+int launch_attn(const rvattn::Params& p, cudaStream_t s) {
+    auto kern = rvattn::paged_decode_fp8_kernel<HD, GT, OutT>;
+    const size_t smem = (size_t)rvattn::WARPS * GT * (HD + 2) * sizeof(float);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
+    dim3 grid(p.kv_heads, p.max_chunks, p.batch);
+    kern<<<grid, rvattn::THREADS, smem, s>>>(p);
+    int rc = rv_launched("paged_decode_fp8");
+    if (rc) return rc;
+    if (p.max_chunks > 1) {
+        rvattn::paged_decode_fp8_combine_kernel<HD, OutT><<<p.batch * p.heads, HD < 256 ? HD : 256, 0, s>>>(
+            p.workspace, (OutT*)p.out, p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq,
+            p.window_size_left, p.max_chunks);
+        rc = rv_launched("paged_decode_fp8_combine");
+    }
+    return rc;
+}
+
+template <int HD, typename OutT>
+int launch_attn_gt(const rvattn::Params& p, cudaStream_t s) {
+    const int group = p.heads / p.kv_heads;
+    if (group == 1) return launch_attn<HD, 1, OutT>(p, s);
+    if (group == 2) return launch_attn<HD, 2, OutT>(p, s);
+    return launch_attn<HD, 4, OutT>(p, s);
+}
+
+template <typename OutT>
+int launch_attn_hd(const rvattn::Params& p, int head_dim, cudaStream_t s) {
+    switch (head_dim) {
+        case 64: return launch_attn_gt<64, OutT>(p, s);
+        case 128: return launch_attn_gt<128, OutT>(p, s);
+        case 256: return launch_attn_gt<256, OutT>(p, s);
+        default: return launch_attn_gt<512, OutT>(p, s);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
+                           int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
+                           void* workspace, size_t workspace_bytes, const float* k_scale_cache,
+                           const float* v_scale_cache, const float* q_scale_cache, const float* q_descale,
+                           const float* k_descale, const float* v_descale, float scale, int batch_size,
+                           int num_heads, int num_kv_heads, int head_dim, int block_size,
+                           int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream) {
+    int rc = rvllm_paged_decode_fp8_validate(batch_size, num_heads, num_kv_heads, head_dim, block_size,
+                                             max_blocks_per_seq, num_blocks_total, window_size_left, scale);
+    if (rc) return rc;
+    if (!q_fp8 || !k_cache_fp8 || !v_cache_fp8 || !output || !block_tables || !context_lens)
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if ((!q_scale_cache && !q_descale) || (!k_scale_cache && !k_descale) || (!v_scale_cache && !v_descale))
+        return rv_fail(RVLLM_E_INVALID, "each of Q, K, V needs a scale cache or a scalar descale");
+    if (!rv_aligned(q_fp8, 16) || !rv_aligned(k_cache_fp8, 16) || !rv_aligned(v_cache_fp8, 16))
+        return rv_fail(RVLLM_E_INVALID, "q / k_cache / v_cache must be 16-byte aligned");
+    if (out_dtype != RVLLM_F16 && out_dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "bad output dtype");
+    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads);
+    const uint64_t need = rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim);
+    if (need == UINT64_MAX) return rv_fail(RVLLM_E_INVALID, "workspace size overflows");
+    if (chunks > 1 && (!workspace || !rv_aligned(workspace, sizeof(float)) || (uint64_t)workspace_bytes < need))
+        return rv_fail(RVLLM_E_WORKSPACE, "attention workspace missing, misaligned or smaller than the query reports");
+    rvattn::Params p;
+    p.q = (const uint8_t*)q_fp8;
+    p.k_cache = (const uint8_t*)k_cache_fp8;
+    p.v_cache = (const uint8_t*)v_cache_fp8;
+    p.out = output;
+    p.workspace = (float*)workspace;
+    p.block_tables = block_tables;
+    p.context_lens = context_lens;
+    p.k_scale_cache = k_scale_cache;
+    p.v_scale_cache = v_scale_cache;
+    p.q_scale_cache = q_scale_cache;
+    p.q_descale = q_descale;
+    p.k_descale = k_descale;
+    p.v_descale = v_descale;
+    p.scale = scale;
+    p.batch = batch_size;
+    p.heads = num_heads;
+    p.kv_heads = num_kv_heads;
+    p.block_size = block_size;
+    p.bs_shift = -1;
+    for (int sft = 0; sft < 31; sft++)
+        if ((1 << sft) == block_size) p.bs_shift = sft;
+    p.max_blocks_per_seq = max_blocks_per_seq;
+    p.num_blocks_total = num_blocks_total;
+    p.window_size_left = window_size_left;
+    p.max_chunks = chunks;
+    cudaStream_t s = (cudaStream_t)stream;
+    return out_dtype == RVLLM_F16 ? launch_attn_hd<__half>(p, head_dim, s)
+                                  : launch_attn_hd<__nv_bfloat16>(p, head_dim, s);
+}
+
+int rvllm_fa_sm89_abi_version(void) { return 2; }
+int fa_sm89_fp8_output_dtype(void) { return 1; }
+int fa_sm89_fp8_output_element_size(void) { return 2; }
+
+uint64_t fa_sm89_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim) {
+    if (head_dim != 128 && head_dim != 256 && head_dim != 512) return UINT64_MAX;
+    return rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim);
+}
+
+int fa_sm89_paged_decode_fp8(void* q_fp8, void* k_cache_fp8, void* v_cache_fp8, void* output,
+                             void* block_tables, void* context_lens, void* workspace, size_t workspace_bytes,
+                             void* k_scale_cache, void* v_scale_cache, void* q_scale_cache, float* q_descale,
+                             float* k_descale, float* v_descale, float scale, int batch_size, int num_heads,
+                             int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                             int num_blocks_total, int window_size_left, void* stream) {
+    if (head_dim != 128 && head_dim != 256 && head_dim != 512) return -1;
+    int rc = rvllm_paged_decode_fp8(q_fp8, k_cache_fp8, v_cache_fp8, output, RVLLM_F16, (const int32_t*)block_tables,
+                                    (const int32_t*)context_lens, workspace, workspace_bytes,
+                                    (const float*)k_scale_cache, (const float*)v_scale_cache,
+                                    (const float*)q_scale_cache, q_descale, k_descale, v_descale, scale, batch_size,
+                                    num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                                    num_blocks_total, window_size_left, stream);
+    return rc == RVLLM_OK ? 0 : -1;
+}
+
+int fa_sm89_paged_decode(void*, void*, void*, void*, void*, void*, void*, size_t, float, int, int, int, int, int,
+                         int, int, int, void*) {
+    rv_fail(RVLLM_E_UNSUPPORTED, "f16-KV decode is outside the FP8 decode path");
+    return -1;
+}
+int fa_sm89_paged_prefill_fp8(void*, void*, void*, void*, void*, void*, void*, void*, size_t, void*, void*, void*,
+                              float*, float*, float*, float, int, int, int, int, int, int, int, int, int, int,
+                              void*) {
+    rv_fail(RVLLM_E_UNSUPPORTED, "FP8 prefill is outside the FP8 decode path");
+    return -1;
+}
+
+
+}  // extern "C"

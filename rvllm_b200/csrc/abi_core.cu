@@ -1,0 +1,256 @@
+// Host side of the C ABI: argument validation mirroring the reference launch descriptors,
+// geometry selection and kernel launches.  No device allocation, no synchronisation; every
+// call only enqueues work on the caller's stream.
+#include <limits.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/rvllm_b200.h"
+#include "host_util.h"
+// the PTX-module translation units double as this library's kernels
+#include "greedy_argmax.cu"
+#include "rope_kv_write.cu"
+#include "rowq_gelu.cu"
+#include "rowq_rmsnorm.cu"
+#include "rowq_silu.cu"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+}  // namespace
+
+int rv_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+// The reference launchers pass min(dim, 1024) threads as is; a block that is not a whole
+// number of warps would run full-mask shuffles with missing lanes, so it is rounded down
+// (identical to the reference geometry for every dimension that is a multiple of 32).
+static inline uint32_t round_block(uint32_t b) { return b < 32 ? 32 : b - b % 32; }
+
+int rv_launched(const char* what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return rv_fail(RVLLM_E_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+    }
+    return RVLLM_OK;
+}
+namespace rvhost {
+int fail_msg(int code, const char* msg) { return rv_fail(code, "%s", msg); }
+}  // namespace rvhost
+
+extern "C" {
+
+int rvllm_b200_abi_version(void) { return 1; }
+const char* rvllm_b200_last_error(void) { return g_err; }
+const char* rvllm_b200_build_arch(void) { return "sm_100a"; }
+
+// ---------------------------------------------------------------- stage 1
+int rvllm_fused_rmsnorm_fp8_quant_validate(uint32_t num_tokens, uint32_t hidden, float eps) {
+    if (hidden == 0 || hidden % 8 != 0) return rv_fail(RVLLM_E_INVALID, "hidden must be a positive multiple of 8");
+    if (num_tokens == 0) return rv_fail(RVLLM_E_INVALID, "num_tokens must be > 0");
+    if (!isfinite(eps) || eps < 0.0f) return rv_fail(RVLLM_E_INVALID, "eps must be finite and >= 0");
+    return RVLLM_OK;
+}
+
+int rvllm_fused_rmsnorm_fp8_quant_launch(uint32_t num_tokens, uint32_t hidden, float eps, void* out_fp8,
+                                         float* scale, const void* in_hidden, const void* gamma, int dtype,
+                                         void* stream) {
+    int rc = rvllm_fused_rmsnorm_fp8_quant_validate(num_tokens, hidden, eps);
+    if (rc) return rc;
+    if (!out_fp8 || !scale || !in_hidden || !gamma) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens), block(round_block(rv_umin(hidden, 1024)));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        fused_rmsnorm_fp8_quant_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale, (const __half*)in_hidden,
+                                                                (const __half*)gamma, eps, (int)hidden);
+    else
+        fused_rmsnorm_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale,
+                                                                     (const __nv_bfloat16*)in_hidden,
+                                                                     (const __nv_bfloat16*)gamma, eps, (int)hidden);
+    return rv_launched("fused_rmsnorm_fp8_quant");
+}
+
+int rvllm_fused_add_rmsnorm_fp8_quant_launch(uint32_t num_tokens, uint32_t hidden, float eps, void* out_fp8,
+                                             float* scale, void* residual_out, const void* in_hidden,
+                                             const void* residual_in, const void* gamma, int dtype,
+                                             void* stream) {
+    int rc = rvllm_fused_rmsnorm_fp8_quant_validate(num_tokens, hidden, eps);
+    if (rc) return rc;
+    if (!out_fp8 || !scale || !residual_out || !in_hidden || !residual_in || !gamma)
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens), block(round_block(rv_umin(hidden, 1024)));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        fused_add_rmsnorm_fp8_quant_kernel<<<grid, block, 128, s>>>(
+            (uint8_t*)out_fp8, scale, (__half*)residual_out, (const __half*)in_hidden, (const __half*)residual_in,
+            (const __half*)gamma, eps, (int)hidden);
+    else
+        fused_add_rmsnorm_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>(
+            (uint8_t*)out_fp8, scale, (__nv_bfloat16*)residual_out, (const __nv_bfloat16*)in_hidden,
+            (const __nv_bfloat16*)residual_in, (const __nv_bfloat16*)gamma, eps, (int)hidden);
+    return rv_launched("fused_add_rmsnorm_fp8_quant");
+}
+
+int rvllm_quantize_fp8_per_token_validate(uint32_t num_tokens, uint32_t dim) {
+    if (dim == 0 || dim % 8 != 0) return rv_fail(RVLLM_E_INVALID, "dim must be a positive multiple of 8");
+    if (num_tokens == 0) return rv_fail(RVLLM_E_INVALID, "num_tokens must be > 0");
+    if (dim > 65536) return rv_fail(RVLLM_E_INVALID, "dim must be <= 65536");
+    return RVLLM_OK;
+}
+
+int rvllm_quantize_fp8_per_token_launch(uint32_t num_tokens, uint32_t dim, void* out_fp8, float* scale,
+                                        const void* in, int dtype, void* stream) {
+    int rc = rvllm_quantize_fp8_per_token_validate(num_tokens, dim);
+    if (rc) return rc;
+    if (!out_fp8 || !scale || !in) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens), block(round_block(rv_umax(rv_umin(dim, 1024), 256)));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        quantize_fp8_per_token_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale, (const __half*)in, (int)dim);
+    else
+        quantize_fp8_per_token_bf16_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale,
+                                                                    (const __nv_bfloat16*)in, (int)dim);
+    return rv_launched("quantize_fp8_per_token");
+}
+
+// ---------------------------------------------------------------- stage 2c
+int rvllm_fused_act_mul_fp8_quant_validate(uint32_t num_tokens, uint32_t intermediate) {
+    if (intermediate == 0 || intermediate % 8 != 0)
+        return rv_fail(RVLLM_E_INVALID, "intermediate must be a positive multiple of 8");
+    if (num_tokens == 0) return rv_fail(RVLLM_E_INVALID, "num_tokens must be > 0");
+    return RVLLM_OK;
+}
+
+int rvllm_fused_act_mul_fp8_quant_launch(uint32_t num_tokens, uint32_t intermediate, int act, void* out_fp8,
+                                         float* scale, const void* gate_up, int dtype, void* stream) {
+    int rc = rvllm_fused_act_mul_fp8_quant_validate(num_tokens, intermediate);
+    if (rc) return rc;
+    if (!out_fp8 || !scale || !gate_up) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (!rv_aligned(gate_up, 16) || !rv_aligned(out_fp8, 8)) return rv_fail(RVLLM_E_INVALID, "gate_up / out misaligned");
+    if (act != RVLLM_ACT_SILU && act != RVLLM_ACT_GELU_TANH) return rv_fail(RVLLM_E_INVALID, "unknown activation");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    uint32_t b = rv_umin(intermediate, 1024);
+    b = rv_umax(32, b - b % 32);
+    dim3 grid(num_tokens), block(b);
+    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t* o = (uint8_t*)out_fp8;
+    int I = (int)intermediate;
+    if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16)
+        fused_silu_mul_fp8_quant_kernel<<<grid, block, 128, s>>>(o, scale, (const __half*)gate_up, I);
+    else if (act == RVLLM_ACT_SILU)
+        fused_silu_mul_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>(o, scale, (const __nv_bfloat16*)gate_up, I);
+    else if (dtype == RVLLM_F16)
+        fused_gelu_mul_fp8_quant_kernel<<<grid, block, 128, s>>>(o, scale, (const __half*)gate_up, I);
+    else
+        fused_gelu_mul_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>(o, scale, (const __nv_bfloat16*)gate_up, I);
+    return rv_launched("fused_act_mul_fp8_quant");
+}
+
+// ---------------------------------------------------------------- stage 4
+int rvllm_argmax_validate(uint32_t num_tokens, uint32_t vocab) {
+    if (vocab == 0) return rv_fail(RVLLM_E_INVALID, "vocab must be > 0");
+    if (vocab > (uint32_t)INT_MAX) return rv_fail(RVLLM_E_INVALID, "vocab too large");
+    if (num_tokens == 0) return rv_fail(RVLLM_E_INVALID, "num_tokens must be > 0");
+    return RVLLM_OK;
+}
+
+int rvllm_argmax_launch(uint32_t num_tokens, uint32_t vocab, const float* logits, int32_t* out, int use_grid,
+                        void* stream) {
+    int rc = rvllm_argmax_validate(num_tokens, vocab);
+    if (rc) return rc;
+    if (!logits || !out) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (use_grid) {
+        if (cudaMemsetAsync(out, 0, sizeof(int32_t) * (size_t)num_tokens, s) != cudaSuccess)
+            return rv_fail(RVLLM_E_LAUNCH, "cudaMemsetAsync(out) failed");
+        dim3 grid((vocab + 1023) / 1024, num_tokens), block(256);
+        argmax_grid_f32_kernel<<<grid, block, 0, s>>>(logits, out, (int)vocab);
+    } else {
+        uint32_t b = 1;
+        while (b * 2 <= rv_umin(vocab, 1024)) b *= 2;  // min(vocab, 1024) rounded down to a power of two
+        argmax_kernel<<<dim3(num_tokens), dim3(b), 0, s>>>(logits, out, (int)vocab);
+    }
+    return rv_launched("argmax");
+}
+
+// ---------------------------------------------------------------- neighbours
+int rvllm_rope_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in, int in_stride, void* q_fp8,
+                            void* k_cache, void* v_cache, float* k_scale_cache, float* v_scale_cache,
+                            float* q_scale_cache, const void* cos_table, const void* sin_table,
+                            const int32_t* positions, const int32_t* slot_mapping, int num_tokens, int num_heads,
+                            int num_kv_heads, int head_dim, int rotary_dim, int max_positions,
+                            int num_cache_slots, int dtype, void* stream) {
+    if (num_tokens <= 0 || num_heads <= 0 || num_kv_heads <= 0) return rv_fail(RVLLM_E_INVALID, "bad token/head counts");
+    if (head_dim < 64 || head_dim % 64 != 0 || head_dim > 512) return rv_fail(RVLLM_E_INVALID, "head_dim must be 64..512, multiple of 64");
+    if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return rv_fail(RVLLM_E_INVALID, "bad rotary_dim");
+    if (max_positions <= 0 || num_cache_slots <= 0 || in_stride <= 0) return rv_fail(RVLLM_E_INVALID, "bad sizes");
+    if (!q_in || !k_in || !v_in || !q_fp8 || !k_cache || !v_cache || !k_scale_cache || !v_scale_cache ||
+        !q_scale_cache || !positions || !slot_mapping || (rotary_dim > 0 && (!cos_table || !sin_table)))
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens, num_heads > num_kv_heads ? num_heads : num_kv_heads), block(head_dim / 2);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        rvllm_rope_fp8kv_kernel<<<grid, block, 0, s>>>(
+            (const __half*)q_in, (const __half*)k_in, (const __half*)v_in, in_stride, (uint8_t*)q_fp8,
+            (uint8_t*)k_cache, (uint8_t*)v_cache, k_scale_cache, v_scale_cache, q_scale_cache,
+            (const __half*)cos_table, (const __half*)sin_table, positions, slot_mapping, num_tokens, num_heads,
+            num_kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
+    else
+        rvllm_rope_fp8kv_bf16_kernel<<<grid, block, 0, s>>>(
+            (const __nv_bfloat16*)q_in, (const __nv_bfloat16*)k_in, (const __nv_bfloat16*)v_in, in_stride,
+            (uint8_t*)q_fp8, (uint8_t*)k_cache, (uint8_t*)v_cache, k_scale_cache, v_scale_cache, q_scale_cache,
+            (const __nv_bfloat16*)cos_table, (const __nv_bfloat16*)sin_table, positions, slot_mapping, num_tokens,
+            num_heads, num_kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
+    return rv_launched("rope_fp8kv");
+}
+
+int rvllm_embedding_gather_launch(void* out, const void* table, const int32_t* token_ids, int num_tokens,
+                                  int hidden, int vocab, void* stream) {
+    if (num_tokens <= 0 || hidden <= 0 || vocab <= 0) return rv_fail(RVLLM_E_INVALID, "bad embedding shapes");
+    if (!out || !table || !token_ids) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    int b = hidden / 8 < 256 ? (hidden / 8 < 32 ? 32 : ((hidden / 8 + 31) / 32) * 32) : 256;
+    embedding_gather_f16_kernel<<<num_tokens, b, 0, (cudaStream_t)stream>>>((__half*)out, (const __half*)table,
+                                                                           token_ids, hidden, vocab);
+    return rv_launched("embedding_gather");
+}
+
+}  // extern "C"
+
+namespace {
+__global__ void e4m3_encode_kernel(uint8_t* out, const float* in, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = rv::f32_to_e4m3(in[i]);
+}
+__global__ void e4m3_decode_kernel(float* out, const uint8_t* in, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        // convert through the pair instruction with the byte in the low half
+        float2 f = rv::e4m3x2_to_f32x2((uint32_t)in[i]);
+        out[i] = f.x;
+    }
+}
+}  // namespace
+
+extern "C" {
+int rvllm_e4m3_encode_f32(void* out_u8, const float* in, size_t n, void* stream) {
+    if (!out_u8 || !in || n == 0) return rv_fail(RVLLM_E_INVALID, "bad encode arguments");
+    e4m3_encode_kernel<<<296, 256, 0, (cudaStream_t)stream>>>((uint8_t*)out_u8, in, n);
+    return rv_launched("e4m3_encode");
+}
+int rvllm_e4m3_decode_f32(float* out, const void* in_u8, size_t n, void* stream) {
+    if (!out || !in_u8 || n == 0) return rv_fail(RVLLM_E_INVALID, "bad decode arguments");
+    e4m3_decode_kernel<<<296, 256, 0, (cudaStream_t)stream>>>(out, (const uint8_t*)in_u8, n);
+    return rv_launched("e4m3_decode");
+}
+}

@@ -1,0 +1,240 @@
+// C-ABI entry points of the FP8 GEMM family: validation, kernel choice, launches.
+#include <limits.h>
+#include <math.h>
+
+#include "../../include/rvllm_b200.h"
+#include "host_util.h"
+#include "fp8_gemm_stream.cuh"
+#include "fp8_gemm_tc.cuh"
+
+extern "C" {
+// ---------------------------------------------------------------- stage 2: GEMM
+}  // extern "C"
+
+namespace {
+
+struct GemmArgs {
+    void* out;
+    int out_kind;
+    const void* a;
+    const void* w;
+    const float* a_scale;
+    const float* w_scale;
+    const void* residual;
+    int M, N, K;
+};
+
+int validate_gemm(const GemmArgs& g) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0) return rv_fail(RVLLM_E_INVALID, "M, N, K must be > 0");
+    if (!g.out || !g.a || !g.w || !g.a_scale || !g.w_scale) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (g.out_kind < 0 || g.out_kind > 2) return rv_fail(RVLLM_E_INVALID, "unknown output kind");
+    if (g.residual && g.out_kind == RVLLM_OUT_F32) return rv_fail(RVLLM_E_INVALID, "residual needs a 16-bit output");
+    if ((long long)g.M * g.N > (1LL << 40) || (long long)g.N * g.K > (1LL << 42))
+        return rv_fail(RVLLM_E_INVALID, "problem size overflows");
+    if (g.K % 64 != 0) return rv_fail(RVLLM_E_UNSUPPORTED, "K must be a multiple of 64");
+    if (!rv_aligned(g.a, 16) || !rv_aligned(g.w, 16)) return rv_fail(RVLLM_E_INVALID, "A / W must be 16-byte aligned");
+    return RVLLM_OK;
+}
+
+template <int NT8, int EPI, typename OutT>
+int launch_stream_one(const rvgemm::StreamParams& p, int splits, int mblocks, cudaStream_t s) {
+    auto kern = rvgemm::fp8_gemm_stream_kernel<NT8, EPI, OutT>;
+    const size_t smem = (size_t)rvgemm::K_WARPS * NT8 * 8 * rvgemm::TILE_N * sizeof(float);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the streaming GEMM");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.N + rvgemm::TILE_N - 1) / rvgemm::TILE_N, splits, mblocks);
+    cfg.blockDim = dim3(rvgemm::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return rv_fail(RVLLM_E_LAUNCH, "streaming GEMM launch: %s", cudaGetErrorString(e));
+    }
+    return RVLLM_OK;
+}
+
+template <int NT8>
+int launch_stream_epi(const GemmArgs& g, const rvgemm::StreamParams& p, int splits, int mblocks, cudaStream_t s) {
+    using namespace rvgemm;
+    if (g.out_kind == RVLLM_OUT_F32) return launch_stream_one<NT8, EPI_F32, __half>(p, splits, mblocks, s);
+    if (g.out_kind == RVLLM_OUT_F16)
+        return g.residual ? launch_stream_one<NT8, EPI_RESIDUAL, __half>(p, splits, mblocks, s)
+                          : launch_stream_one<NT8, EPI_SCALE, __half>(p, splits, mblocks, s);
+    return g.residual ? launch_stream_one<NT8, EPI_RESIDUAL, __nv_bfloat16>(p, splits, mblocks, s)
+                      : launch_stream_one<NT8, EPI_SCALE, __nv_bfloat16>(p, splits, mblocks, s);
+}
+
+// Split-K factor for the streaming kernel: enough CTAs for two per SM, at most the
+// portable cluster size, and at least two 64-byte chunks per k-warp.
+int stream_splits(int M, int N, int K, int mblocks) {
+    (void)M;
+    const int tiles = ((N + rvgemm::TILE_N - 1) / rvgemm::TILE_N) * mblocks;
+    int s = (2 * 148 + tiles - 1) / tiles;
+    const int chunks = K / rvgemm::CHUNK;
+    while (s > 1 && chunks / (s * rvgemm::K_WARPS) < 2) s--;
+    if (s < 1) s = 1;
+    if (s > 8) s = 8;
+    return s;
+}
+
+int launch_stream(const GemmArgs& g, cudaStream_t s) {
+    rvgemm::StreamParams p;
+    p.a = (const uint8_t*)g.a;
+    p.w = (const uint8_t*)g.w;
+    p.a_scale = g.a_scale;
+    p.w_scale = g.w_scale;
+    p.out = g.out;
+    p.residual = g.residual;
+    p.M = g.M;
+    p.N = g.N;
+    p.K = g.K;
+    p.ldo = g.N;
+    int nt8 = (g.M + 7) / 8;
+    if (nt8 > 8) nt8 = 8;
+    if (nt8 == 3) nt8 = 4;
+    if (nt8 > 4 && nt8 < 8) nt8 = 8;
+    const int mblocks = (g.M + nt8 * 8 - 1) / (nt8 * 8);
+    const int splits = stream_splits(g.M, g.N, g.K, mblocks);
+    switch (nt8) {
+        case 1: return launch_stream_epi<1>(g, p, splits, mblocks, s);
+        case 2: return launch_stream_epi<2>(g, p, splits, mblocks, s);
+        case 4: return launch_stream_epi<4>(g, p, splits, mblocks, s);
+        default: return launch_stream_epi<8>(g, p, splits, mblocks, s);
+    }
+}
+
+int run_gemm(const GemmArgs& g, int impl, void* workspace, size_t workspace_size, cudaStream_t s) {
+    int rc = validate_gemm(g);
+    if (rc) return rc;
+    if (impl == 0) impl = rvtc::prefer_tc(g.M, g.N, g.K) ? 2 : 1;
+    if (impl == 2) {
+        rvtc::TcArgs t;
+        t.out = g.out;
+        t.out_kind = g.out_kind;
+        t.a = g.a;
+        t.w = g.w;
+        t.a_scale = g.a_scale;
+        t.w_scale = g.w_scale;
+        t.residual = g.residual;
+        t.M = g.M;
+        t.N = g.N;
+        t.K = g.K;
+        return rvtc::launch(t, workspace, workspace_size, s);
+    }
+    if (impl != 1) return rv_fail(RVLLM_E_INVALID, "impl must be 0, 1 or 2");
+    return launch_stream(g, s);
+}
+
+// Device-side broadcast of a scalar weight scale is done by pointing w_scale at a
+// per-channel vector; the reference's scalar-B-scale entry points are served by
+// expanding the scalar into the head of the caller's workspace.
+__global__ void fill_scale_kernel(float* dst, const float* scalar, int n) {
+    const float v = *scalar;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = v;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t rvllm_fp8_gemm_workspace(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return rvtc::workspace_bytes(M, N, K);
+}
+
+int rvllm_fp8_gemm_channelscale(void* out, int out_kind, const void* a_fp8, const void* w_fp8,
+                                const float* a_scale, const float* w_scale, const void* residual, int M, int N,
+                                int K, int impl, void* workspace, size_t workspace_size, void* stream) {
+    GemmArgs g = {out, out_kind, a_fp8, w_fp8, a_scale, w_scale, residual, M, N, K};
+    return run_gemm(g, impl, workspace, workspace_size, (cudaStream_t)stream);
+}
+
+int cutlass_fp8_gemm_channelscale(void* out_f16, const void* a_fp8, const void* b_fp8, const void* row_scale,
+                                  const void* col_scale, int M, int N, int K, void* workspace,
+                                  size_t workspace_size, void* stream) {
+    GemmArgs g = {out_f16, RVLLM_OUT_F16, a_fp8, b_fp8, (const float*)row_scale, (const float*)col_scale,
+                  nullptr, M, N, K};
+    return run_gemm(g, 0, workspace, workspace_size, (cudaStream_t)stream) == RVLLM_OK ? 0 : -1;
+}
+size_t cutlass_fp8_gemm_channelscale_workspace(int M, int N, int K) { return rvllm_fp8_gemm_workspace(M, N, K); }
+
+static int scalar_b_gemm(void* out_f16, const void* a_fp8, const void* b_fp8, const void* a_scales,
+                         const void* b_scale, const void* residual, int M, int N, int K, void* workspace,
+                         size_t workspace_size, void* stream) {
+    if (N <= 0 || !b_scale) return rv_fail(RVLLM_E_INVALID, "bad scalar-scale GEMM arguments");
+    const size_t head = ((size_t)N * sizeof(float) + 255) & ~(size_t)255;
+    if (!workspace || !rv_aligned(workspace, 16) || workspace_size < head)
+        return rv_fail(RVLLM_E_WORKSPACE, "workspace too small for the expanded weight scale");
+    cudaStream_t s = (cudaStream_t)stream;
+    fill_scale_kernel<<<(N + 255) / 256, 256, 0, s>>>((float*)workspace, (const float*)b_scale, N);
+    int rc = rv_launched("fill_scale");
+    if (rc) return rc;
+    GemmArgs g = {out_f16, RVLLM_OUT_F16, a_fp8, b_fp8, (const float*)a_scales, (const float*)workspace,
+                  residual, M, N, K};
+    return run_gemm(g, 0, (char*)workspace + head, workspace_size - head, s);
+}
+
+int cutlass_fp8_gemm_v0(void* out_f16, const void* a_fp8, const void* b_fp8, const void* a_scales,
+                        const void* b_scale, int M, int N, int K, void* workspace, size_t workspace_size,
+                        void* stream) {
+    return scalar_b_gemm(out_f16, a_fp8, b_fp8, a_scales, b_scale, nullptr, M, N, K, workspace, workspace_size,
+                         stream) == RVLLM_OK ? 0 : -1;
+}
+size_t cutlass_fp8_gemm_v0_workspace_size(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return (((size_t)N * sizeof(float) + 255) & ~(size_t)255) + rvllm_fp8_gemm_workspace(M, N, K);
+}
+int cutlass_fp8_gemm_residual_v0(void* out_f16, const void* a_fp8, const void* b_fp8, const void* a_scales,
+                                 const void* b_scale, const void* residual_f16, int M, int N, int K,
+                                 void* workspace, size_t workspace_size, void* stream) {
+    if (!residual_f16) return -1;
+    return scalar_b_gemm(out_f16, a_fp8, b_fp8, a_scales, b_scale, residual_f16, M, N, K, workspace,
+                         workspace_size, stream) == RVLLM_OK ? 0 : -1;
+}
+size_t cutlass_fp8_gemm_residual_v0_workspace_size(int M, int N, int K) {
+    return cutlass_fp8_gemm_v0_workspace_size(M, N, K);
+}
+
+int rvllm_fp8_gemm_tc_status(int* status, int reset) {
+    if (!status) return rv_fail(RVLLM_E_INVALID, "status pointer is null");
+    return rvtc::read_status(status, reset != 0) == 0 ? RVLLM_OK : rv_fail(RVLLM_E_LAUNCH, "cannot read the status word");
+}
+
+size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {
+    if (M <= 0 || I <= 0 || K <= 0) return 0;
+    const size_t stage = ((size_t)M * 2 * (size_t)I * 2 + 255) & ~(size_t)255;
+    return stage + rvllm_fp8_gemm_workspace(M, 2 * I, K);
+}
+
+int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void* a_fp8, const void* w_fp8,
+                                    const float* a_scale, const float* w_scale, int M, int I, int K, int act,
+                                    int dtype, int impl, void* workspace, size_t workspace_size, void* stream) {
+    if (M <= 0 || I <= 0 || K <= 0 || I > INT_MAX / 2) return rv_fail(RVLLM_E_INVALID, "M, I, K must be > 0");
+    int rc = rvllm_fused_act_mul_fp8_quant_validate((uint32_t)M, (uint32_t)I);
+    if (rc) return rc;
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    const size_t stage = ((size_t)M * 2 * (size_t)I * 2 + 255) & ~(size_t)255;
+    if (!workspace || !rv_aligned(workspace, 256) || workspace_size < rvllm_fp8_gemm_gateup_workspace(M, I, K))
+        return rv_fail(RVLLM_E_WORKSPACE, "gate-up workspace missing, misaligned or too small");
+    // The projection lands in the 16-bit type the standalone chain would use, so the
+    // activation + re-quantisation sees bit-identical inputs either way.
+    GemmArgs g = {workspace, dtype == RVLLM_F16 ? RVLLM_OUT_F16 : RVLLM_OUT_BF16, a_fp8, w_fp8, a_scale, w_scale,
+                  nullptr, M, 2 * I, K};
+    rc = run_gemm(g, impl, (char*)workspace + stage, workspace_size - stage, (cudaStream_t)stream);
+    if (rc) return rc;
+    return rvllm_fused_act_mul_fp8_quant_launch((uint32_t)M, (uint32_t)I, act, out_fp8, out_scale, workspace, dtype,
+                                                stream);
+}
+
+
+}  // extern "C"

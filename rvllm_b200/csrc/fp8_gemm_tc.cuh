@@ -1,0 +1,464 @@
+// tcgen05 / TMEM FP8 E4M3 GEMM for sm_100a:
+//     D[m, n] = epilogue( a_scale[m] * ( w_scale[n] * sum_k A[m, k] * W[n, k] ) )
+// Same operand layout and epilogue contract as the streaming kernel (A [M, K], W [N, K],
+// both row-major fp8; reference: kernels/cutlass_fp8_gemm_channelscale.cu:98-161,
+// kernels/cutlass_fp8_gemm_residual.cu:48-83).
+//
+// The roles are swapped relative to a textbook GEMM so that decode-sized batches still
+// fill the 128-lane tensor-core tile: a 128-row slab of W is the MMA's M operand, the
+// batch rows are its N operand (16..256), so the accumulator in TMEM is D^T
+// [128 weight rows (lanes) x BN batch rows (columns)] in f32.
+//
+//   warp 0   : TMA producer — one lane issues cp.async.bulk.tensor.2d loads of a
+//              128 x 128 B weight tile and a BN x 128 B activation tile per stage
+//              (128-byte swizzle), completion counted on an mbarrier per stage.
+//   warp 1   : allocates TMEM, then one lane issues four tcgen05.mma (K = 32) per stage
+//              and commits the stage's "empty" barrier; a final commit signals the
+//              epilogue.
+//   warps 2-5: epilogue — tcgen05.ld of the warp's 32-lane quarter, scales, optional
+//              residual, narrow, store (64 B contiguous per batch row per warp).
+//
+// Split-K uses a thread-block cluster along K exactly like the streaming kernel: each
+// CTA parks its f32 tile in its own (now idle) stage memory, the cluster synchronises,
+// and each CTA finishes an interleaved share by reading its peers through DSMEM in a
+// fixed order — no global scratch, no atomics, bitwise reproducible.  No multicast loads
+// are used anywhere.
+//
+// Every mbarrier wait is bounded; when one runs out the kernel records it in a device
+// status word, stops waiting, and still walks through every barrier and the TMEM
+// release so that neither it nor its cluster peers hang.
+#pragma once
+#include <cooperative_groups.h>
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace rvhost {
+int fail_msg(int code, const char* msg);
+}
+
+namespace rvtc {
+
+namespace cg = cooperative_groups;
+
+constexpr int TILE_W = 128;   // weight rows per CTA (UMMA M)
+constexpr int BK = 128;       // K bytes per stage (one 128-byte swizzle atom)
+constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
+constexpr int THREADS = 192;
+constexpr int EPI_WARP0 = 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ int g_status = 0;  // 0 ok; otherwise (site << 16 | detail) of the first wait that gave up
+
+struct TcParams {
+    const float* a_scale;
+    const float* w_scale;
+    void* out;
+    const void* residual;
+    int M, N, K;
+    int kblocks;  // ceil(K / BK)
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and records `site`) if the phase never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int site) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicCAS(&g_status, 0, (site << 16) | (int)(blockIdx.x & 0xffff));
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile [rows x 128 B], 128-byte swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr & 0x3ffffu) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+    return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
+}
+
+constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2;
+
+template <int BN> struct Cfg {
+    static constexpr int STAGE_BYTES = TILE_W * BK + BN * BK;
+    static constexpr int STAGES = (BN <= 64) ? 8 : (BN <= 128 ? 6 : 4);
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int RING = STAGES * STAGE_BYTES;
+    static constexpr int SMEM = RING + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(TILE_W * BN * 4 <= RING, "partial tile must fit in the stage ring");
+};
+
+template <int BN, int EPI, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, TcParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(ring + C::RING);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int S = gridDim.y, split = blockIdx.y;
+    const int n0 = blockIdx.x * TILE_W, m0 = blockIdx.z * BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb_lo = (int)((long long)split * p.kblocks / S);
+    const int kb_hi = (int)((long long)(split + 1) * p.kblocks / S);
+    const int nkb = kb_hi - kb_lo;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(acc_ready, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool alive = true;
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+                if (alive && i >= C::STAGES) alive = mbar_wait(empty + s, ph ^ 1u, 1);
+                if (!alive) break;
+                uint8_t* w_dst = ring + (size_t)s * C::STAGE_BYTES;
+                mbar_expect_tx(full + s, C::STAGE_BYTES);
+                tma_load_2d(w_dst, &map_w, (kb_lo + i) * BK, n0, full + s);
+                tma_load_2d(w_dst + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            bool alive = true;
+            for (int i = 0; i < nkb && alive; i++) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+                alive = mbar_wait(full + s, ph, 2);
+                if (!alive) break;
+                tc_fence_after();
+                const uint32_t w_addr = smem_u32(ring + (size_t)s * C::STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(w_addr);
+                const uint64_t bdesc = smem_desc_sw128(w_addr + TILE_W * BK);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; k++)
+                    umma_f8(tmem_base, adesc + (uint64_t)(k * UMMA_K >> 4), bdesc + (uint64_t)(k * UMMA_K >> 4), idesc,
+                            (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty + s);  // frees the stage once these MMAs have read it
+            }
+            umma_commit(acc_ready);  // arrives when every MMA issued above has completed
+        }
+    }
+    __syncwarp();
+
+    // ---- epilogue ----------------------------------------------------------------------
+    float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32, only when S > 1
+    if (warp >= EPI_WARP0) {
+        const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32 * quarter ...
+        const int r = quarter * 32 + lane;
+        const int n = n0 + r;
+        bool ready = true;
+        if (nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+        tc_fence_after();
+        const float ws = (n < p.N) ? p.w_scale[n] : 0.0f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t v[16];
+            if (nkb > 0 && ready) {
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[j] = 0u;
+            }
+            if (S > 1) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) part[(size_t)(c0 + j) * TILE_W + r] = __uint_as_float(v[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int m = m0 + c0 + j;
+                    if (m < p.M && n < p.N) {
+                        float val = p.a_scale[m] * (ws * __uint_as_float(v[j]));
+                        const size_t o = (size_t)m * p.N + n;
+                        if (EPI == EPI_F32) {
+                            reinterpret_cast<float*>(p.out)[o] = val;
+                        } else {
+                            if (EPI == EPI_RESIDUAL)
+                                val += rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                            reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    if (S > 1) {
+        cluster.sync();
+        const float* peer[8];
+#pragma unroll
+        for (int s = 0; s < 8; s++) peer[s] = s < S ? cluster.map_shared_rank(part, s) : part;
+        for (int e = split * THREADS + threadIdx.x; e < BN * TILE_W; e += S * THREADS) {
+            const int ml = e / TILE_W, r = e % TILE_W;
+            const int m = m0 + ml, n = n0 + r;
+            float sum = 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; s++)
+                if (s < S) sum += peer[s][e];
+            if (m < p.M && n < p.N) {
+                float val = p.a_scale[m] * (p.w_scale[n] * sum);
+                const size_t o = (size_t)m * p.N + n;
+                if (EPI == EPI_F32) {
+                    reinterpret_cast<float*>(p.out)[o] = val;
+                } else {
+                    if (EPI == EPI_RESIDUAL) val += rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                    reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
+                }
+            }
+        }
+        cluster.sync();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+struct TcArgs {
+    void* out;
+    int out_kind;
+    const void* a;
+    const void* w;
+    const float* a_scale;
+    const float* w_scale;
+    const void* residual;
+    int M, N, K;
+};
+
+inline size_t workspace_bytes(int, int, int) { return 0; }
+
+// Which shapes go to the tensor-core kernel when the caller lets the library choose.
+inline bool prefer_tc(int M, int N, int K) {
+    (void)N;
+    (void)K;
+    (void)M;
+    return false;
+}
+
+inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+    });
+    return fn;
+}
+
+// Row-major fp8 matrix [rows, K] -> 2-D map with a (128 B x box_rows) box, 128-byte swizzle,
+// zero fill outside the matrix (covers a ragged last K block and rows past the end).
+inline bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+    const void* p;
+    int rows, K, box;
+    bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && K == o.K && box == o.box; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.K << 20) ^ (size_t)k.box;
+    }
+};
+// Tensor maps are pure functions of (pointer, shape); cache them so a decode step that
+// reuses its buffers does not re-encode.
+inline bool cached_map(CUtensorMap* out, const void* base, int rows, int K, int box) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{base, rows, K, box};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    if (!make_map(out, base, rows, K, box)) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return true;
+}
+
+template <int BN, int EPI, typename OutT>
+int launch_one(const TcArgs& g, int splits, cudaStream_t s) {
+    using C = Cfg<BN>;
+    CUtensorMap mw, ma;
+    if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || !cached_map(&ma, g.a, g.M, g.K, BN))
+        return rvhost::fail_msg(-2, "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
+    auto kern = fp8_gemm_tc_kernel<BN, EPI, OutT>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+        return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
+    TcParams p;
+    p.a_scale = g.a_scale;
+    p.w_scale = g.w_scale;
+    p.out = g.out;
+    p.residual = g.residual;
+    p.M = g.M;
+    p.N = g.N;
+    p.K = g.K;
+    p.kblocks = (g.K + BK - 1) / BK;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((g.N + TILE_W - 1) / TILE_W, splits, (g.M + BN - 1) / BN);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, mw, ma, p) != cudaSuccess) {
+        cudaGetLastError();
+        return rvhost::fail_msg(-2, "tcgen05 GEMM launch failed");
+    }
+    return 0;
+}
+
+template <int BN>
+int launch_epi(const TcArgs& g, int splits, cudaStream_t s) {
+    if (g.out_kind == 2) return launch_one<BN, EPI_F32, __half>(g, splits, s);
+    if (g.out_kind == 0)
+        return g.residual ? launch_one<BN, EPI_RESIDUAL, __half>(g, splits, s)
+                          : launch_one<BN, EPI_SCALE, __half>(g, splits, s);
+    return g.residual ? launch_one<BN, EPI_RESIDUAL, __nv_bfloat16>(g, splits, s)
+                      : launch_one<BN, EPI_SCALE, __nv_bfloat16>(g, splits, s);
+}
+
+inline int pick_splits(int M, int N, int K, int bn) {
+    const int tiles = ((N + TILE_W - 1) / TILE_W) * ((M + bn - 1) / bn);
+    const int kblocks = (K + BK - 1) / BK;
+    int s = (148 + tiles - 1) / tiles;
+    while (s > 1 && kblocks / s < 4) s--;
+    if (s < 1) s = 1;
+    if (s > 8) s = 8;
+    return s;
+}
+
+inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s, int force_splits = 0) {
+    if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");
+    int bn = g.M <= 16 ? 16 : g.M <= 32 ? 32 : g.M <= 64 ? 64 : g.M <= 128 ? 128 : 256;
+    const int splits = force_splits > 0 ? force_splits : pick_splits(g.M, g.N, g.K, bn);
+    switch (bn) {
+        case 16: return launch_epi<16>(g, splits, s);
+        case 32: return launch_epi<32>(g, splits, s);
+        case 64: return launch_epi<64>(g, splits, s);
+        case 128: return launch_epi<128>(g, splits, s);
+        default: return launch_epi<256>(g, splits, s);
+    }
+}
+
+inline int read_status(int* out, bool reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -2;
+    *out = v;
+    if (reset && v != 0) {
+        int z = 0;
+        if (cudaMemcpyToSymbol(g_status, &z, sizeof(int)) != cudaSuccess) return -2;
+    }
+    return 0;
+}
+
+}  // namespace rvtc

@@ -1,0 +1,13 @@
+// PTX module `fused_gelu_mul_fp8_quant`: GELU-tanh(gate) * up + per-token FP8
+// quantisation.  Entry-point contract: v3/kernels/fused_gelu_mul_fp8_quant.cu:53 of
+// the reference (out_fp8, scales, gate_up, intermediate); body in rowq_act.cuh.
+#include "rowq_act.cuh"
+
+extern "C" __global__ void __launch_bounds__(1024)
+fused_gelu_mul_fp8_quant_kernel(uint8_t* out, float* scales, const __half* gate_up, int intermediate) {
+    rvact::act_mul_quant_row<rvact::ACT_GELU, __half>(out, scales, gate_up, intermediate);
+}
+extern "C" __global__ void __launch_bounds__(1024)
+fused_gelu_mul_fp8_quant_bf16_kernel(uint8_t* out, float* scales, const __nv_bfloat16* gate_up, int intermediate) {
+    rvact::act_mul_quant_row<rvact::ACT_GELU, __nv_bfloat16>(out, scales, gate_up, intermediate);
+}

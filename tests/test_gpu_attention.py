@@ -1,0 +1,238 @@
+"""GPU parity of FP8-KV paged GQA decode attention (split-KV + LSE combine) through the C ABI.
+
+Checked against (a) the CPU oracle in f64 (the reference's fa3_sm90_parity_bench
+reference_attention), (b) the oracle in the f32 step order of the reference's scalar kernel,
+and (c) the reference's own split-KV kernel (oracle/_ref/libfa_sm89_ref.so) on the same GPU.
+Pass rule of the reference's parity bench (v3/kernels/fp8_decode_v2_parity_bench.cu:196-198,
+433-446): |got - want| <= 2e-3 + 1e-2 * |want|.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+from tests import datagen  # noqa: E402
+from tests import ptx_harness as H  # noqa: E402
+
+ABS_TOL, REL_TOL = 2e-3, 1e-2
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def run_ours(c, out_dtype=torch.float16, scalar_q=None, scalar_kv=None, window=None):
+    from rvllm_b200.attention import PagedDecodeFp8Launcher, PagedDecodeParams
+    window = c["window"] if window is None else window
+    p = PagedDecodeParams(c["batch"], c["heads"], c["kv_heads"], c["head_dim"], c["block_size"], c["max_blocks"],
+                          c["num_blocks"], c.get("scale", 1.0 / np.sqrt(c["head_dim"])), window)
+    ws = torch.empty(max(p.workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
+    out = torch.full((c["batch"], c["heads"], c["head_dim"]), 123.0, dtype=out_dtype, device="cuda")
+    kw = {}
+    if scalar_q is None:
+        kw["q_scale_cache"] = dev(c["qs"])
+    else:
+        kw["q_descale"] = torch.tensor([scalar_q], dtype=torch.float32, device="cuda")
+    if scalar_kv is None:
+        kw["k_scale_cache"], kw["v_scale_cache"] = dev(c["ks"]), dev(c["vs"])
+    else:
+        kw["k_descale"] = torch.tensor([scalar_kv[0]], dtype=torch.float32, device="cuda")
+        kw["v_descale"] = torch.tensor([scalar_kv[1]], dtype=torch.float32, device="cuda")
+    keep = [dev(c["q"]), dev(c["k"]), dev(c["v"]), dev(c["tables"]), dev(c["ctx"])]
+    PagedDecodeFp8Launcher(p).launch(keep[0], keep[1], keep[2], out, keep[3], keep[4], workspace=ws, **kw)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+def run_oracle(orc, c, precise, scalar_q=None, scalar_kv=None, dtype=0, window=None):
+    window = c["window"] if window is None else window
+    kw = dict(window_size_left=window, precise=precise, dtype=dtype, num_blocks_total=c["num_blocks"])
+    if scalar_q is None:
+        kw["q_scale_cache"] = c["qs"]
+    else:
+        kw["q_descale"] = scalar_q
+    if scalar_kv is None:
+        kw["k_scale_cache"], kw["v_scale_cache"] = c["ks"], c["vs"]
+    else:
+        kw["k_descale"], kw["v_descale"] = scalar_kv
+    o = orc.paged_decode_fp8(c["q"], c["k"], c["v"], c["tables"], c["ctx"], c.get("scale", 1.0 / np.sqrt(c["head_dim"])),
+                             c["heads"], c["kv_heads"], c["head_dim"], c["block_size"], **kw)
+    return orc.from_bits16(o, dtype)
+
+
+def assert_close(got, want, abs_tol=ABS_TOL, rel_tol=REL_TOL):
+    assert np.array_equal(np.isnan(got), np.isnan(want)), "NaN rows differ"
+    ok = ~np.isnan(want)
+    err = np.abs(got[ok] - want[ok])
+    lim = abs_tol + rel_tol * np.abs(want[ok])
+    assert (err <= lim).all(), f"max abs err {err.max():.3e}, worst excess {(err - lim).max():.3e}"
+
+
+# ---- the reference parity bench's shape points (:121-147), plus head_dim 64 / 128 ------------
+POINTS = [
+    # H, KVH, HD, ctx, block_size, batch
+    (32, 16, 256, 1, 32, 1), (32, 16, 256, 2, 32, 1), (32, 16, 256, 17, 32, 1), (32, 16, 256, 128, 32, 1),
+    (32, 16, 256, 432, 32, 1), (32, 16, 256, 1024, 32, 1), (32, 16, 256, 128, 1, 1), (32, 16, 256, 1024, 1, 1),
+    (32, 16, 256, 128, 16, 1), (32, 16, 256, 1024, 16, 1), (32, 16, 256, 432, 32, 2),
+    (32, 4, 512, 1, 32, 1), (32, 4, 512, 2, 32, 1), (32, 4, 512, 17, 32, 1),
+    (16, 4, 512, 432, 32, 1), (16, 4, 512, 1300, 32, 1), (16, 4, 512, 8192, 32, 1), (16, 4, 512, 1300, 1, 1),
+    (16, 4, 512, 1300, 16, 1),
+    (8, 4, 64, 128, 16, 4), (32, 16, 128, 1500, 16, 3), (8, 8, 128, 300, 16, 2), (24, 2, 64, 700, 8, 2),
+]
+
+
+@pytest.mark.parametrize("recipe", ["bytes", "normal"])
+@pytest.mark.parametrize("H_,KVH,HD,ctx,bs,batch", POINTS)
+def test_decode_shape_points(orc, recipe, H_, KVH, HD, ctx, bs, batch):
+    ctxs = [ctx] * batch
+    if batch == 2:
+        ctxs[0] = 0  # the bench's "seq0 ctx = 0" point: zeros row
+    c = datagen.attention_case(orc, batch, H_, KVH, HD, bs, ctxs, seed=1234567 + ctx + HD, recipe=recipe)
+    got = run_ours(c)
+    assert_close(got, run_oracle(orc, c, precise=True))
+    assert_close(got, run_oracle(orc, c, precise=False))
+    if batch == 2:
+        assert (got[0] == 0).all()
+
+
+def test_scalar_scale_fallbacks_and_bf16(orc):
+    c = datagen.attention_case(orc, 1, 32, 16, 256, 32, [128], seed=7, recipe="bytes")
+    assert_close(run_ours(c, scalar_q=0.004), run_oracle(orc, c, True, scalar_q=0.004))
+    assert_close(run_ours(c, scalar_kv=(0.003, 0.006)), run_oracle(orc, c, True, scalar_kv=(0.003, 0.006)))
+    c2 = datagen.attention_case(orc, 3, 32, 16, 128, 16, [900, 40, 2000], seed=8)
+    assert_close(run_ours(c2, out_dtype=torch.bfloat16), run_oracle(orc, c2, True, dtype=1), abs_tol=8e-3)
+
+
+@pytest.mark.parametrize("HD,window", [(128, 1023), (256, 1023), (64, 100), (128, 0)])
+def test_sliding_window_ring(orc, HD, window):
+    """Contexts far beyond the window: only the last window+1 tokens are attended and pages
+    are looked up modulo the table length (ring)."""
+    bs = 16
+    ctxs = [5, window + 1, window + 2, 3 * window + 7, 20000]
+    mb = (window + 1 + bs - 1) // bs + 1
+    c = datagen.attention_case(orc, len(ctxs), 32, 16, HD, bs, ctxs, seed=11, window=window, max_blocks=mb)
+    got = run_ours(c)
+    assert_close(got, run_oracle(orc, c, precise=True))
+
+
+def test_config3_ragged_long_contexts(orc):
+    """Batch of ragged contexts up to 32768 (global layer, head_dim 256) and the sliding
+    twin (head_dim 128, window 1024); block_size 16, shuffled physical blocks."""
+    g = np.random.default_rng(2)
+    ctxs = g.integers(512, 32769, 12)
+    ctxs[0], ctxs[1] = 32768, 512
+    c = datagen.attention_case(orc, 12, 32, 16, 256, 16, ctxs, seed=2)
+    assert_close(run_ours(c), run_oracle(orc, c, precise=True))
+    mb = (1024 + 16 + 15) // 16 + 1
+    c2 = datagen.attention_case(orc, 12, 32, 16, 128, 16, ctxs, seed=2, window=1023, max_blocks=mb)
+    assert_close(run_ours(c2), run_oracle(orc, c2, precise=True))
+
+
+def test_large_batch_no_split(orc):
+    # 128 sequences x 16 KV heads: one chunk per sequence, no workspace needed
+    g = np.random.default_rng(3)
+    ctxs = g.integers(1, 700, 128)
+    c = datagen.attention_case(orc, 128, 32, 16, 128, 16, ctxs, seed=3)
+    assert_close(run_ours(c), run_oracle(orc, c, precise=True))
+
+
+def test_block_table_index_echo(orc):
+    """Block-table indexing, bit-exact: V rows carry their own slot number (as exactly
+    representable bytes) and K is zero, so attention returns the mean of the attended slots'
+    codes; any wrong page, offset or ring wrap changes the result."""
+    bs, HD, KVH, Hh = 16, 64, 2, 2
+    for window, ctxs in ((-1, [1, 16, 17, 100]), (40, [1, 41, 42, 1000])):
+        mb = 8 if window < 0 else (window + 1 + bs - 1) // bs + 1
+        c = datagen.attention_case(orc, len(ctxs), Hh, KVH, HD, bs, ctxs, seed=5, window=window, max_blocks=mb)
+        slots = c["num_blocks"] * bs
+        c["k"][:] = 0
+        sl = np.arange(slots)
+        # dims 0..2 of every V row encode the slot index in base 8 with exactly representable codes
+        codes = orc.e4m3_encode(np.arange(8, dtype=np.float32), orc.MODE_CUDA)
+        v = c["v"].reshape(slots, KVH, HD)
+        v[:] = 0
+        for d in range(3):
+            v[:, :, d] = codes[(sl >> (3 * d)) & 7][:, None]
+        c["vs"][:] = 1.0
+        c["ks"][:] = 1.0
+        got = run_ours(c, out_dtype=torch.float16)
+        want_slots = orc.attended_slots(c["tables"], c["ctx"], bs, c["num_blocks"], window, max_attend=128)
+        for b in range(len(ctxs)):
+            s = want_slots[b][want_slots[b] >= 0]
+            for d in range(3):
+                want = np.float16(np.float32(((s >> (3 * d)) & 7).astype(np.float32).mean()))
+                assert abs(float(got[b, 0, d]) - float(want)) <= 5e-3, (window, b, d)
+
+
+def test_invalid_data_gives_nan_never_a_fault(orc):
+    c = datagen.attention_case(orc, 4, 8, 4, 128, 16, [64, 64, 64, 64], seed=9)
+    c["ctx"][1] = -3                      # negative context
+    c["tables"][2, 1] = c["num_blocks"]   # physical block out of range
+    c["qs"][3 * 8 + 5] = 0.0              # non-positive q scale for one head
+    got = run_ours(c)
+    want = run_oracle(orc, c, precise=False)
+    assert np.isnan(got[1]).all() and np.isnan(got[2]).all()
+    assert np.isnan(got[3, 5]).all() and not np.isnan(got[3, 4]).any()
+    assert_close(got, want)
+    c["ctx"][0] = 16 * c["max_blocks"] + 1  # longer than the table, no window
+    assert np.isnan(run_ours(c)[0]).all()
+
+
+def test_launcher_validation_and_workspace_contract():
+    # v3/crates/rvllm-attention/src/decode.rs:732-766 and fp8_decode_v2.cu:1015-1037
+    from rvllm_b200 import _lib
+    from rvllm_b200.attention import PagedDecodeFp8Launcher, PagedDecodeParams
+    p = PagedDecodeParams(1, 32, 16, 256, 16, 64, 128, 0.0625)
+    z = torch.zeros(32 * 256 * 16 * 16, dtype=torch.uint8, device="cuda")
+    out = torch.zeros((1, 32, 256), dtype=torch.float16, device="cuda")
+    tables = torch.zeros((1, 64), dtype=torch.int32, device="cuda")
+    ctx = torch.full((1,), 100, dtype=torch.int32, device="cuda")
+    one = torch.ones(4096, dtype=torch.float32, device="cuda")
+    with pytest.raises(_lib.RvllmError) as e:  # split launch without a workspace
+        PagedDecodeFp8Launcher(p).launch(z, z, z, out, tables, ctx, workspace=None, k_scale_cache=one,
+                                         v_scale_cache=one, q_scale_cache=one)
+    assert e.value.code == _lib.E_WORKSPACE
+    with pytest.raises(_lib.InvalidArgument):  # no scale source for Q
+        ws = torch.empty(p.workspace_bytes(), dtype=torch.uint8, device="cuda")
+        PagedDecodeFp8Launcher(p).launch(z, z, z, out, tables, ctx, workspace=ws, k_scale_cache=one, v_scale_cache=one)
+
+
+needs_ref = pytest.mark.skipif(not os.path.exists(os.path.join(H.REF_DIR, "libfa_sm89_ref.so")),
+                               reason="oracle/_ref/libfa_sm89_ref.so not built (needs the reference checkout)")
+
+
+@needs_ref
+@pytest.mark.parametrize("HD,window,bs", [(256, -1, 16), (128, 1023, 16), (512, -1, 32)])
+def test_against_reference_split_kv_kernel(orc, HD, window, bs):
+    """Same inputs through the reference's fa_sm89_paged_decode_fp8 (compiled from
+    v3/kernels/fp8_decode_v2.cu) and through ours, on this GPU."""
+    ref = C.CDLL(os.path.join(H.REF_DIR, "libfa_sm89_ref.so"))
+    ref.fa_sm89_decode_workspace_size.restype = C.c_uint64
+    heads, kvh = (32, 16) if HD < 512 else (16, 4)
+    g = np.random.default_rng(HD)
+    ctxs = g.integers(1, 6000, 6)
+    mb = None if window < 0 else (window + 1 + bs - 1) // bs + 1
+    c = datagen.attention_case(orc, 6, heads, kvh, HD, bs, ctxs, seed=HD + 1, window=window, max_blocks=mb)
+    scale = float(1.0 / np.sqrt(HD))
+    t = [dev(c[k]) for k in ("q", "k", "v", "tables", "ctx", "ks", "vs", "qs")]
+    out = torch.zeros((6, heads, HD), dtype=torch.float16, device="cuda")
+    need = ref.fa_sm89_decode_workspace_size(6, heads, kvh, HD)
+    ws = torch.empty(max(int(need), 16), dtype=torch.uint8, device="cuda")
+    vp, f32, i32 = C.c_void_p, C.c_float, C.c_int
+    ref.fa_sm89_paged_decode_fp8.argtypes = [vp] * 7 + [C.c_size_t] + [vp] * 6 + [f32] + [i32] * 8 + [vp]
+    rc = ref.fa_sm89_paged_decode_fp8(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), out.data_ptr(),
+                                      t[3].data_ptr(), t[4].data_ptr(), ws.data_ptr(), int(need), t[5].data_ptr(),
+                                      t[6].data_ptr(), t[7].data_ptr(), None, None, None, scale, 6, heads, kvh, HD, bs,
+                                      c["max_blocks"], c["num_blocks"], window,
+                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    ref_out = out.float().cpu().numpy()
+    c["scale"] = scale
+    got = run_ours(c)
+    assert_close(got, ref_out)
+    assert_close(ref_out, run_oracle(orc, c, precise=True))  # and the oracle agrees with the reference itself
