@@ -420,9 +420,15 @@ int orc_fp8_gemm(void *out, const uint8_t *a, const uint8_t *w, const float *a_s
                     for (int k = 0; k < K; k++) acc += (double)ar[k] * (double)wf[k];
                     accf = (float)acc;
                 } else {
-                    float acc = 0.0f;
-                    for (int k = 0; k < K; k++) acc += ar[k] * wf[k];
-                    accf = acc;
+                    /* fp32 accumulation in 8 interleaved lanes (lane j takes k = j mod 8), lanes
+                     * added pairwise at the end: a fixed order that the compiler can keep in one
+                     * vector register, so the timed CPU baseline is not a scalar strawman. */
+                    float lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    int k = 0;
+                    for (; k + 8 <= K; k += 8)
+                        for (int j = 0; j < 8; j++) lane[j] += ar[k + j] * wf[k + j];
+                    for (; k < K; k++) lane[k & 7] += ar[k] * wf[k];
+                    accf = ((lane[0] + lane[4]) + (lane[2] + lane[6])) + ((lane[1] + lane[5]) + (lane[3] + lane[7]));
                 }
                 float v = a_scale[m] * (w_scale[n] * accf);
                 size_t o = (size_t)m * N + n;

@@ -55,9 +55,12 @@ template <int HD, int GT, typename OutT>
 int launch_attn(const rvattn::Params& p, cudaStream_t s) {
     auto kern = rvattn::paged_decode_fp8_kernel<HD, GT, OutT>;
     const size_t smem = (size_t)rvattn::WARPS * GT * (HD + 2) * sizeof(float);
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
+    static bool attr_set = false;  // per kernel instantiation
+    if (smem > 48 * 1024 && !attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
+        attr_set = true;
+    }
     dim3 grid(p.kv_heads, p.max_chunks, p.batch);
     kern<<<grid, rvattn::THREADS, smem, s>>>(p);
     int rc = rv_launched("paged_decode_fp8");

@@ -40,9 +40,12 @@ template <int NT8, int EPI, typename OutT>
 int launch_stream_one(const rvgemm::StreamParams& p, int splits, int mblocks, cudaStream_t s) {
     auto kern = rvgemm::fp8_gemm_stream_kernel<NT8, EPI, OutT>;
     const size_t smem = (size_t)rvgemm::K_WARPS * NT8 * 8 * rvgemm::TILE_N * sizeof(float);
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the streaming GEMM");
+    static bool attr_set = false;  // per kernel instantiation; set once so graph capture sees launches only
+    if (smem > 48 * 1024 && !attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the streaming GEMM");
+        attr_set = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.N + rvgemm::TILE_N - 1) / rvgemm::TILE_N, splits, mblocks);
     cfg.blockDim = dim3(rvgemm::THREADS);

@@ -387,8 +387,12 @@ int launch_one(const TcArgs& g, int splits, cudaStream_t s) {
     if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || !cached_map(&ma, g.a, g.M, g.K, BN))
         return rvhost::fail_msg(-2, "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
     auto kern = fp8_gemm_tc_kernel<BN, EPI, OutT>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-        return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
+    static bool attr_set = false;  // per kernel instantiation
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+            return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
+        attr_set = true;
+    }
     TcParams p;
     p.a_scale = g.a_scale;
     p.w_scale = g.w_scale;
