@@ -270,7 +270,7 @@ def dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src):
             "us_per_launch": sec * 1e6, "algorithmic_bytes_per_launch": algo, "traffic": None}
 
 
-def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None):
+def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None, profiler_range=False, seeded=False):
     import numpy as np
     from rvllm_b200.stack import DecodeStack
 
@@ -278,15 +278,23 @@ def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, ba
     stack = DecodeStack(c, weights)
     g = np.random.default_rng(3)
     prompt = g.integers(0, c["vocab"], (B, c["prompt_len"]), dtype=np.int32)
-    stack.reset(prompt)
-    stack.run(c["prompt_len"] - 1)       # prompt through the decode path; the next step emits token 1
+    if seeded:
+        stack.seed_context(c["prompt_len"] - 1)   # profiling runs: skip the prefill steps
+    else:
+        stack.reset(prompt)
+        stack.run(c["prompt_len"] - 1)   # prompt through the decode path; the next step emits token 1
     stack.run(max(warmup, 3))
     stack.sync()
     if barrier:
         barrier()
     if sampler:
         sampler.start()
+    if profiler_range:
+        torch.cuda.profiler.start()
     sec = time_steps(torch, stack, steps)
+    if profiler_range:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else None
     if barrier:
         barrier()
@@ -342,7 +350,8 @@ def run_gpu_arm(args, cfg):
     setup_s = time.perf_counter() - t0
 
     B = args.batch
-    main = run_batch(torch, cfg, weights, B, args.steps, args.warmup, args.e2e_steps, ClockSampler(local), barrier)
+    main = run_batch(torch, cfg, weights, B, args.steps, args.warmup, args.e2e_steps, ClockSampler(local), barrier,
+                     profiler_range=args.profiler_range, seeded=args.seeded_context)
     sec = torch.tensor([main["seconds"]], dtype=torch.float64, device="cuda")
     e2e_ms = torch.tensor([main["e2e"]["ms_per_step"] if "e2e" in main else 0.0], dtype=torch.float64, device="cuda")
     if dist:
@@ -368,7 +377,8 @@ def run_gpu_arm(args, cfg):
                              "achieved_gbs": main["step_bytes"] / (main["seconds"] / args.steps) / 1e9,
                              "frac_of_hbm_peak": step_frac}
     if rank == 0:
-        line["roofline"] = dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src)
+        if not args.no_roofline:
+            line["roofline"] = dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src)
         if world == 1 and not args.no_cpu_baseline:
             import oracle as orc
             orc.build()
@@ -401,6 +411,11 @@ def main():
     ap.add_argument("--gemm-impl", type=int, default=0)
     ap.add_argument("--all-batches", action="store_true", help="also time batch 1 and 128")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-roofline", action="store_true")
+    ap.add_argument("--seeded-context", action="store_true",
+                    help="profiling aid: fill the KV caches synthetically instead of running the 512 prefill steps")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     from rvllm_b200.stack import gemma31b_shape
     need = 512 + max(args.warmup, 3) + args.steps + args.e2e_steps + 8

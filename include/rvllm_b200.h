@@ -48,6 +48,12 @@ extern "C" {
 int rvllm_b200_abi_version(void);          /* = 1 */
 const char* rvllm_b200_last_error(void);   /* thread-local; "" when no error */
 const char* rvllm_b200_build_arch(void);   /* "sm_100a" */
+/* Programmatic dependent launch: when enabled (the default) every kernel is launched with the
+ * programmatic-stream-serialization attribute, so the next kernel on the stream may start its
+ * prologue and weight prefetch while the current one drains; every kernel waits for its
+ * predecessor before touching dependent data.  Process-wide; set it before recording graphs. */
+void rvllm_b200_set_pdl(int enabled);
+int rvllm_b200_get_pdl(void);
 
 /* ---- 1. fused RMSNorm + per-token FP8 quantisation ----------------------------------
  * Replaces FusedRmsnormFp8QuantLaunch / FusedAddRmsnormFp8QuantLaunch /
@@ -121,6 +127,9 @@ size_t rvllm_fp8_gemm_workspace(int M, int N, int K);
  * (site << 16 | CTA) of the first wait that ran out.  Synchronous (copies from the device);
  * for tests and diagnosis, not for the decode loop.  reset != 0 clears it. */
 int rvllm_fp8_gemm_tc_status(int* status, int reset);
+/* Overrides of the tcgen05 kernel's automatic choices, for tuning runs: TMA ring depth
+ * (2..8) and split-K factor (1..8); 0 restores the automatic choice.  Process-wide. */
+void rvllm_fp8_gemm_tc_tune(int stages, int splits);
 
 /* gate|up projection + act(gate)*up + per-token FP8 re-quantisation in one call
  * (reference: GEMM at layer_exec.rs:484-494 followed by FusedSiluMulFp8QuantLaunch :509).

@@ -79,6 +79,11 @@ void rvllm_stack_destroy(rvllm_stack* s);
 /* Restart every sequence at position 0.  prompt_tokens: host [batch, prompt_len] int32. */
 int rvllm_stack_reset(rvllm_stack* s, const int32_t* prompt_tokens);
 
+/* Profiling aid: restart with every sequence already at position `context`, the caches filled
+ * with constant bytes and scales instead of being produced by `context` decode steps.  The
+ * kernels then do the work of a step at that context length without the prefill run. */
+int rvllm_stack_seed_context(rvllm_stack* s, int context);
+
 /* Enqueue `n` decode steps (graph replays) on the stack's stream; returns without waiting.
  * rvllm_stack_sync waits for them. */
 int rvllm_stack_run(rvllm_stack* s, int n);

@@ -39,6 +39,8 @@ SIGNATURES = {
     "rvllm_b200_abi_version": (_i32, []),
     "rvllm_b200_last_error": (C.c_char_p, []),
     "rvllm_b200_build_arch": (C.c_char_p, []),
+    "rvllm_b200_set_pdl": (None, [_i32]),
+    "rvllm_b200_get_pdl": (_i32, []),
     "rvllm_fused_rmsnorm_fp8_quant_validate": (_i32, [_u32, _u32, _f32]),
     "rvllm_fused_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _i32, _vp]),
     "rvllm_fused_add_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),
@@ -59,6 +61,7 @@ SIGNATURES = {
     "rvllm_fp8_gemm_gateup_act_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "rvllm_fp8_gemm_gateup_workspace": (_sz, [_i32, _i32, _i32]),
     "rvllm_fp8_gemm_tc_status": (_i32, [C.POINTER(_i32), _i32]),
+    "rvllm_fp8_gemm_tc_tune": (None, [_i32, _i32]),
     "rvllm_fa_sm89_abi_version": (_i32, []),
     "fa_sm89_fp8_output_dtype": (_i32, []),
     "fa_sm89_fp8_output_element_size": (_i32, []),

@@ -62,12 +62,12 @@ int launch_attn(const rvattn::Params& p, cudaStream_t s) {
         attr_set = true;
     }
     dim3 grid(p.kv_heads, p.max_chunks, p.batch);
-    kern<<<grid, rvattn::THREADS, smem, s>>>(p);
+    rv_launch(kern, grid, dim3(rvattn::THREADS), smem, s, dim3(1, 1, 1), p);
     int rc = rv_launched("paged_decode_fp8");
     if (rc) return rc;
     if (p.max_chunks > 1) {
-        rvattn::paged_decode_fp8_combine_kernel<HD, OutT><<<p.batch * p.heads, HD < 256 ? HD : 256, 0, s>>>(
-            p.workspace, (OutT*)p.out, p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq,
+        rv_launch((rvattn::paged_decode_fp8_combine_kernel<HD, OutT>), dim3(p.batch * p.heads), dim3(HD < 256 ? HD : 256), 0,
+                  s, dim3(1, 1, 1), (const float*)p.workspace, (OutT*)p.out, (const int*)p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq,
             p.window_size_left, p.max_chunks);
         rc = rv_launched("paged_decode_fp8_combine");
     }

@@ -42,6 +42,10 @@ int rv_launched(const char* what) {
     }
     return RVLLM_OK;
 }
+static bool g_pdl = true;
+bool rv_pdl_enabled() { return g_pdl; }
+void rv_set_pdl(bool on) { g_pdl = on; }
+
 namespace rvhost {
 int fail_msg(int code, const char* msg) { return rv_fail(code, "%s", msg); }
 }  // namespace rvhost
@@ -51,6 +55,8 @@ extern "C" {
 int rvllm_b200_abi_version(void) { return 1; }
 const char* rvllm_b200_last_error(void) { return g_err; }
 const char* rvllm_b200_build_arch(void) { return "sm_100a"; }
+void rvllm_b200_set_pdl(int enabled) { rv_set_pdl(enabled != 0); }
+int rvllm_b200_get_pdl(void) { return rv_pdl_enabled() ? 1 : 0; }
 
 // ---------------------------------------------------------------- stage 1
 int rvllm_fused_rmsnorm_fp8_quant_validate(uint32_t num_tokens, uint32_t hidden, float eps) {
@@ -70,10 +76,10 @@ int rvllm_fused_rmsnorm_fp8_quant_launch(uint32_t num_tokens, uint32_t hidden, f
     dim3 grid(num_tokens), block(round_block(rv_umin(hidden, 1024)));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RVLLM_F16)
-        fused_rmsnorm_fp8_quant_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale, (const __half*)in_hidden,
+        rv_launch(fused_rmsnorm_fp8_quant_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), (uint8_t*)out_fp8, scale, (const __half*)in_hidden,
                                                                 (const __half*)gamma, eps, (int)hidden);
     else
-        fused_rmsnorm_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale,
+        rv_launch(fused_rmsnorm_fp8_quant_bf16_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), (uint8_t*)out_fp8, scale,
                                                                      (const __nv_bfloat16*)in_hidden,
                                                                      (const __nv_bfloat16*)gamma, eps, (int)hidden);
     return rv_launched("fused_rmsnorm_fp8_quant");
@@ -91,11 +97,11 @@ int rvllm_fused_add_rmsnorm_fp8_quant_launch(uint32_t num_tokens, uint32_t hidde
     dim3 grid(num_tokens), block(round_block(rv_umin(hidden, 1024)));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RVLLM_F16)
-        fused_add_rmsnorm_fp8_quant_kernel<<<grid, block, 128, s>>>(
+        rv_launch(fused_add_rmsnorm_fp8_quant_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), 
             (uint8_t*)out_fp8, scale, (__half*)residual_out, (const __half*)in_hidden, (const __half*)residual_in,
             (const __half*)gamma, eps, (int)hidden);
     else
-        fused_add_rmsnorm_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>(
+        rv_launch(fused_add_rmsnorm_fp8_quant_bf16_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), 
             (uint8_t*)out_fp8, scale, (__nv_bfloat16*)residual_out, (const __nv_bfloat16*)in_hidden,
             (const __nv_bfloat16*)residual_in, (const __nv_bfloat16*)gamma, eps, (int)hidden);
     return rv_launched("fused_add_rmsnorm_fp8_quant");
@@ -117,9 +123,9 @@ int rvllm_quantize_fp8_per_token_launch(uint32_t num_tokens, uint32_t dim, void*
     dim3 grid(num_tokens), block(round_block(rv_umax(rv_umin(dim, 1024), 256)));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RVLLM_F16)
-        quantize_fp8_per_token_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale, (const __half*)in, (int)dim);
+        rv_launch(quantize_fp8_per_token_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), (uint8_t*)out_fp8, scale, (const __half*)in, (int)dim);
     else
-        quantize_fp8_per_token_bf16_kernel<<<grid, block, 128, s>>>((uint8_t*)out_fp8, scale,
+        rv_launch(quantize_fp8_per_token_bf16_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), (uint8_t*)out_fp8, scale,
                                                                     (const __nv_bfloat16*)in, (int)dim);
     return rv_launched("quantize_fp8_per_token");
 }
@@ -147,13 +153,13 @@ int rvllm_fused_act_mul_fp8_quant_launch(uint32_t num_tokens, uint32_t intermedi
     uint8_t* o = (uint8_t*)out_fp8;
     int I = (int)intermediate;
     if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16)
-        fused_silu_mul_fp8_quant_kernel<<<grid, block, 128, s>>>(o, scale, (const __half*)gate_up, I);
+        rv_launch(fused_silu_mul_fp8_quant_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), o, scale, (const __half*)gate_up, I);
     else if (act == RVLLM_ACT_SILU)
-        fused_silu_mul_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>(o, scale, (const __nv_bfloat16*)gate_up, I);
+        rv_launch(fused_silu_mul_fp8_quant_bf16_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), o, scale, (const __nv_bfloat16*)gate_up, I);
     else if (dtype == RVLLM_F16)
-        fused_gelu_mul_fp8_quant_kernel<<<grid, block, 128, s>>>(o, scale, (const __half*)gate_up, I);
+        rv_launch(fused_gelu_mul_fp8_quant_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), o, scale, (const __half*)gate_up, I);
     else
-        fused_gelu_mul_fp8_quant_bf16_kernel<<<grid, block, 128, s>>>(o, scale, (const __nv_bfloat16*)gate_up, I);
+        rv_launch(fused_gelu_mul_fp8_quant_bf16_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), o, scale, (const __nv_bfloat16*)gate_up, I);
     return rv_launched("fused_act_mul_fp8_quant");
 }
 
@@ -175,11 +181,11 @@ int rvllm_argmax_launch(uint32_t num_tokens, uint32_t vocab, const float* logits
         if (cudaMemsetAsync(out, 0, sizeof(int32_t) * (size_t)num_tokens, s) != cudaSuccess)
             return rv_fail(RVLLM_E_LAUNCH, "cudaMemsetAsync(out) failed");
         dim3 grid((vocab + 1023) / 1024, num_tokens), block(256);
-        argmax_grid_f32_kernel<<<grid, block, 0, s>>>(logits, out, (int)vocab);
+        rv_launch(argmax_grid_f32_kernel, dim3(grid), dim3(block), 0, s, dim3(1, 1, 1), logits, out, (int)vocab);
     } else {
         uint32_t b = 1;
         while (b * 2 <= rv_umin(vocab, 1024)) b *= 2;  // min(vocab, 1024) rounded down to a power of two
-        argmax_kernel<<<dim3(num_tokens), dim3(b), 0, s>>>(logits, out, (int)vocab);
+        rv_launch(argmax_kernel, dim3(dim3(num_tokens)), dim3(dim3(b)), 0, s, dim3(1, 1, 1), logits, out, (int)vocab);
     }
     return rv_launched("argmax");
 }
@@ -202,13 +208,13 @@ int rvllm_rope_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in
     dim3 grid(num_tokens, num_heads > num_kv_heads ? num_heads : num_kv_heads), block(head_dim / 2);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RVLLM_F16)
-        rvllm_rope_fp8kv_kernel<<<grid, block, 0, s>>>(
+        rv_launch(rvllm_rope_fp8kv_kernel, dim3(grid), dim3(block), 0, s, dim3(1, 1, 1), 
             (const __half*)q_in, (const __half*)k_in, (const __half*)v_in, in_stride, (uint8_t*)q_fp8,
             (uint8_t*)k_cache, (uint8_t*)v_cache, k_scale_cache, v_scale_cache, q_scale_cache,
             (const __half*)cos_table, (const __half*)sin_table, positions, slot_mapping, num_tokens, num_heads,
             num_kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
     else
-        rvllm_rope_fp8kv_bf16_kernel<<<grid, block, 0, s>>>(
+        rv_launch(rvllm_rope_fp8kv_bf16_kernel, dim3(grid), dim3(block), 0, s, dim3(1, 1, 1), 
             (const __nv_bfloat16*)q_in, (const __nv_bfloat16*)k_in, (const __nv_bfloat16*)v_in, in_stride,
             (uint8_t*)q_fp8, (uint8_t*)k_cache, (uint8_t*)v_cache, k_scale_cache, v_scale_cache, q_scale_cache,
             (const __nv_bfloat16*)cos_table, (const __nv_bfloat16*)sin_table, positions, slot_mapping, num_tokens,
@@ -221,7 +227,7 @@ int rvllm_embedding_gather_launch(void* out, const void* table, const int32_t* t
     if (num_tokens <= 0 || hidden <= 0 || vocab <= 0) return rv_fail(RVLLM_E_INVALID, "bad embedding shapes");
     if (!out || !table || !token_ids) return rv_fail(RVLLM_E_INVALID, "null device pointer");
     int b = hidden / 8 < 256 ? (hidden / 8 < 32 ? 32 : ((hidden / 8 + 31) / 32) * 32) : 256;
-    embedding_gather_f16_kernel<<<num_tokens, b, 0, (cudaStream_t)stream>>>((__half*)out, (const __half*)table,
+    rv_launch(embedding_gather_f16_kernel, dim3(num_tokens), dim3(b), 0, (cudaStream_t)stream, dim3(1, 1, 1), (__half*)out, (const __half*)table,
                                                                            token_ids, hidden, vocab);
     return rv_launched("embedding_gather");
 }

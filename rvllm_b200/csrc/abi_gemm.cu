@@ -51,13 +51,18 @@ int launch_stream_one(const rvgemm::StreamParams& p, int splits, int mblocks, cu
     cfg.blockDim = dim3(rvgemm::THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = splits;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (rv_pdl_enabled()) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -211,6 +216,11 @@ size_t cutlass_fp8_gemm_residual_v0_workspace_size(int M, int N, int K) {
 int rvllm_fp8_gemm_tc_status(int* status, int reset) {
     if (!status) return rv_fail(RVLLM_E_INVALID, "status pointer is null");
     return rvtc::read_status(status, reset != 0) == 0 ? RVLLM_OK : rv_fail(RVLLM_E_LAUNCH, "cannot read the status word");
+}
+
+void rvllm_fp8_gemm_tc_tune(int stages, int splits) {
+    rvtc::tune().stages = stages;
+    rvtc::tune().splits = splits;
 }
 
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {

@@ -130,4 +130,12 @@ __device__ __forceinline__ uint4 ld_stream128(const void* p) {
     return v;
 }
 
+// Programmatic dependent launch.  Every kernel of the decode chain calls pdl_launch() first
+// (lets the next kernel of the stream start its prologue and weight prefetch while this one
+// runs) and pdl_wait() before it touches anything a predecessor wrote or may still read.
+// Both are no-ops when the kernel was launched without the programmatic-serialization
+// attribute (e.g. by a caller that uses plain launches).
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 }  // namespace rv

@@ -14,6 +14,7 @@
 
 #include "../../include/rvllm_b200.h"
 #include "../../include/rvllm_b200_stack.h"
+#include "common.cuh"
 #include "host_util.h"
 
 namespace {
@@ -41,6 +42,8 @@ __global__ void prepare_step_kernel(const int* __restrict__ positions, const int
                                     const int* __restrict__ tables_sliding, int* __restrict__ slots_global,
                                     int* __restrict__ slots_sliding, int* __restrict__ ctx_lens, int batch,
                                     int block_size, int mb_global, int mb_sliding) {
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= batch) return;
     const int pos = positions[b];
@@ -55,6 +58,8 @@ __global__ void prepare_step_kernel(const int* __restrict__ positions, const int
 __global__ void advance_kernel(int* __restrict__ tokens, const int* __restrict__ next, int* __restrict__ positions,
                                const int* __restrict__ prompt, int prompt_len, int* __restrict__ history,
                                int* __restrict__ step_counter, int max_steps, int batch) {
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int step = *step_counter;
     for (int b = threadIdx.x; b < batch; b += blockDim.x) {
         const int pos = positions[b];
@@ -65,6 +70,13 @@ __global__ void advance_kernel(int* __restrict__ tokens, const int* __restrict__
     }
     __syncthreads();
     if (threadIdx.x == 0) *step_counter = step + 1;
+}
+
+__global__ void fill_f32_kernel(float* dst, size_t n, float v) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = v;
+}
+__global__ void fill_i32_kernel(int* dst, int n, int v) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = v;
 }
 
 template <typename T>
@@ -247,7 +259,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
     const int B = c.batch, H = c.hidden;
     void* st = (void*)s->stream;
     int n = 0;
-    prepare_step_kernel<<<(B + 127) / 128, 128, 0, s->stream>>>(s->positions, s->tables_global, s->tables_sliding,
+    rv_launch(prepare_step_kernel, dim3((B + 127) / 128), dim3(128), 0, s->stream, dim3(1, 1, 1), s->positions, s->tables_global, s->tables_sliding,
                                                                 s->slots_global, s->slots_sliding, s->ctx_lens, B,
                                                                 c.block_size, s->mb_global, s->mb_sliding);
     RV_TRY(rv_launched("prepare_step"));
@@ -293,7 +305,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                        s->head.lm_head_scale, nullptr, B, c.vocab, H, c.gemm_impl, s->gemm_ws,
                                        s->gemm_ws_bytes, st));
     RV_TRY(rvllm_argmax_launch(B, c.vocab, s->logits, s->next_tokens, 0, st));
-    advance_kernel<<<1, 256, 0, s->stream>>>(s->tokens, s->next_tokens, s->positions, s->prompt, c.prompt_len,
+    rv_launch(advance_kernel, dim3(1), dim3(256), 0, s->stream, dim3(1, 1, 1), s->tokens, s->next_tokens, s->positions, s->prompt, c.prompt_len,
                                              s->history, s->step_counter, c.max_steps, B);
     RV_TRY(rv_launched("advance"));
     n += 4;
@@ -437,6 +449,22 @@ int rvllm_stack_reset(rvllm_stack* s, const int32_t* prompt_tokens) {
     }
     s->steps_done = 0;
     return cuda_ok(cudaStreamSynchronize(s->stream), "reset");
+}
+
+int rvllm_stack_seed_context(rvllm_stack* s, int context) {
+    if (!s || context < 0 || context >= s->cfg.max_context) return rv_fail(RVLLM_E_INVALID, "bad seeded context");
+    const rvllm_stack_config& c = s->cfg;
+    RV_TRY(rvllm_stack_reset(s, nullptr));
+    for (const LayerState& L : s->ls) {
+        const size_t slots = (size_t)L.num_blocks * c.block_size;
+        cudaMemsetAsync(L.k_cache, 0x34, slots * L.kv_dim, s->stream);  // 0.75 in E4M3
+        cudaMemsetAsync(L.v_cache, 0xb2, slots * L.kv_dim, s->stream);  // -0.625
+        fill_f32_kernel<<<256, 256, 0, s->stream>>>(L.k_scale, slots * c.kv_heads, 0.02f);
+        fill_f32_kernel<<<256, 256, 0, s->stream>>>(L.v_scale, slots * c.kv_heads, 0.03f);
+    }
+    fill_i32_kernel<<<1, 256, 0, s->stream>>>(s->positions, c.batch, context);
+    RV_TRY(rv_launched("seed context"));
+    return cuda_ok(cudaStreamSynchronize(s->stream), "seed context");
 }
 
 int rvllm_stack_run(rvllm_stack* s, int n) {

@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(THREADS, (NT8 <= 4 ? 2 : 1)) fp8_gemm_stream_k
         arow[i] = p.a + (size_t)m * p.K + 16 * t;
     }
 
+    rv::pdl_launch();
+    rv::pdl_wait();  // activations and the residual come from the previous kernel
     float acc[2][NT8][4];
 #pragma unroll
     for (int r = 0; r < 2; r++)

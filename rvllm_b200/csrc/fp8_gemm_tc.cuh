@@ -40,6 +40,7 @@
 namespace rvhost {
 int fail_msg(int code, const char* msg);
 }
+bool rv_pdl_enabled();
 
 namespace rvtc {
 
@@ -61,6 +62,7 @@ struct TcParams {
     const void* residual;
     int M, N, K;
     int kblocks;  // ceil(K / BK)
+    int stages;   // depth of the TMA ring (2..MAX_STAGES); sets the shared-memory footprint
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -148,13 +150,16 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
 
 constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2;
 
+constexpr int MAX_STAGES = 8;
+constexpr int HEADER_BYTES = 1024;  // barriers + TMEM address holder, in front of the ring
+
 template <int BN> struct Cfg {
     static constexpr int STAGE_BYTES = TILE_W * BK + BN * BK;
-    static constexpr int STAGES = (BN <= 64) ? 8 : (BN <= 128 ? 6 : 4);
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr int RING = STAGES * STAGE_BYTES;
-    static constexpr int SMEM = RING + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static_assert(TILE_W * BN * 4 <= RING, "partial tile must fit in the stage ring");
+    // stages needed so that the split-K partial tile [BN][128] f32 fits in the (idle) ring
+    static constexpr int MIN_STAGES = (TILE_W * BN * 4 + STAGE_BYTES - 1) / STAGE_BYTES < 2
+                                          ? 2 : (TILE_W * BN * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
+    static constexpr int smem_bytes(int stages) { return 1024 /*alignment slack*/ + HEADER_BYTES + stages * STAGE_BYTES; }
 };
 
 template <int BN, int EPI, typename OutT>
@@ -162,11 +167,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, TcParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t raw[];
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(ring + C::RING);
-    uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_ready = empty + C::STAGES;
+    uint8_t* header = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* ring = header + HEADER_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(header);
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* acc_ready = empty + MAX_STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    const int STAGES = p.stages;
 
     cg::cluster_group cluster = cg::this_cluster();
     const int S = gridDim.y, split = blockIdx.y;
@@ -176,8 +183,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int kb_hi = (int)((long long)(split + 1) * p.kblocks / S);
     const int nkb = kb_hi - kb_lo;
 
+    rv::pdl_launch();
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) {
+        for (int s = 0; s < STAGES; s++) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
@@ -192,11 +200,21 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == 0) {
         if (lane == 0) {
+            // Weights never depend on the previous kernel: fill the ring with weight tiles first,
+            // then wait for the predecessor and add the activation tiles of those stages.
+            const int pre = nkb < STAGES ? nkb : STAGES;
+            for (int i = 0; i < pre; i++) {
+                mbar_expect_tx(full + i, C::STAGE_BYTES);
+                tma_load_2d(ring + (size_t)i * C::STAGE_BYTES, &map_w, (kb_lo + i) * BK, n0, full + i);
+            }
+            rv::pdl_wait();
+            for (int i = 0; i < pre; i++)
+                tma_load_2d(ring + (size_t)i * C::STAGE_BYTES + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + i);
             bool alive = true;
-            for (int i = 0; i < nkb; i++) {
-                const int s = i % C::STAGES;
-                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
-                if (alive && i >= C::STAGES) alive = mbar_wait(empty + s, ph ^ 1u, 1);
+            for (int i = pre; i < nkb; i++) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                alive = mbar_wait(empty + s, ph ^ 1u, 1);
                 if (!alive) break;
                 uint8_t* w_dst = ring + (size_t)s * C::STAGE_BYTES;
                 mbar_expect_tx(full + s, C::STAGE_BYTES);
@@ -209,8 +227,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             constexpr uint32_t idesc = instr_desc(BN);
             bool alive = true;
             for (int i = 0; i < nkb && alive; i++) {
-                const int s = i % C::STAGES;
-                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
                 alive = mbar_wait(full + s, ph, 2);
                 if (!alive) break;
                 tc_fence_after();
@@ -227,6 +245,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
     }
     __syncwarp();
+    rv::pdl_wait();  // scales and the residual come from predecessors; also keeps completion ordered
 
     // ---- epilogue ----------------------------------------------------------------------
     float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32, only when S > 1
@@ -381,15 +400,20 @@ inline bool cached_map(CUtensorMap* out, const void* base, int rows, int K, int 
 }
 
 template <int BN, int EPI, typename OutT>
-int launch_one(const TcArgs& g, int splits, cudaStream_t s) {
+int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s) {
     using C = Cfg<BN>;
     CUtensorMap mw, ma;
     if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || !cached_map(&ma, g.a, g.M, g.K, BN))
         return rvhost::fail_msg(-2, "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
     auto kern = fp8_gemm_tc_kernel<BN, EPI, OutT>;
-    static bool attr_set = false;  // per kernel instantiation
+    if (stages < C::MIN_STAGES) stages = C::MIN_STAGES;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    while (stages > C::MIN_STAGES && C::smem_bytes(stages) > 227 * 1024) stages--;
+    static bool attr_set = false;  // per kernel instantiation: allow the largest ring once
     if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+        int most = MAX_STAGES;
+        while (most > C::MIN_STAGES && C::smem_bytes(most) > 227 * 1024) most--;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(most)) != cudaSuccess)
             return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
         attr_set = true;
     }
@@ -402,18 +426,24 @@ int launch_one(const TcArgs& g, int splits, cudaStream_t s) {
     p.N = g.N;
     p.K = g.K;
     p.kblocks = (g.K + BK - 1) / BK;
+    p.stages = stages;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((g.N + TILE_W - 1) / TILE_W, splits, (g.M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.dynamicSmemBytes = C::smem_bytes(stages);
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = splits;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (rv_pdl_enabled()) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     if (cudaLaunchKernelEx(&cfg, kern, mw, ma, p) != cudaSuccess) {
         cudaGetLastError();
         return rvhost::fail_msg(-2, "tcgen05 GEMM launch failed");
@@ -422,13 +452,13 @@ int launch_one(const TcArgs& g, int splits, cudaStream_t s) {
 }
 
 template <int BN>
-int launch_epi(const TcArgs& g, int splits, cudaStream_t s) {
-    if (g.out_kind == 2) return launch_one<BN, EPI_F32, __half>(g, splits, s);
+int launch_epi(const TcArgs& g, int splits, int stages, cudaStream_t s) {
+    if (g.out_kind == 2) return launch_one<BN, EPI_F32, __half>(g, splits, stages, s);
     if (g.out_kind == 0)
-        return g.residual ? launch_one<BN, EPI_RESIDUAL, __half>(g, splits, s)
-                          : launch_one<BN, EPI_SCALE, __half>(g, splits, s);
-    return g.residual ? launch_one<BN, EPI_RESIDUAL, __nv_bfloat16>(g, splits, s)
-                      : launch_one<BN, EPI_SCALE, __nv_bfloat16>(g, splits, s);
+        return g.residual ? launch_one<BN, EPI_RESIDUAL, __half>(g, splits, stages, s)
+                          : launch_one<BN, EPI_SCALE, __half>(g, splits, stages, s);
+    return g.residual ? launch_one<BN, EPI_RESIDUAL, __nv_bfloat16>(g, splits, stages, s)
+                      : launch_one<BN, EPI_SCALE, __nv_bfloat16>(g, splits, stages, s);
 }
 
 inline int pick_splits(int M, int N, int K, int bn) {
@@ -441,16 +471,34 @@ inline int pick_splits(int M, int N, int K, int bn) {
     return s;
 }
 
-inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s, int force_splits = 0) {
+// Experiment hooks (0 = automatic): ring depth and split-K factor.
+struct Tune {
+    int stages = 0;
+    int splits = 0;
+};
+inline Tune& tune() {
+    static Tune t;
+    return t;
+}
+
+// Ring depth: decode-sized tiles keep two CTAs per SM resident (~100 KB each), so one CTA's
+// prologue / epilogue overlaps the other's streaming; large tiles take the whole SM.
+inline int pick_stages(int bn) { return bn == 16 ? 6 : bn == 32 ? 5 : bn == 64 ? 4 : bn == 128 ? 6 : 4; }
+
+inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
     if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");
     int bn = g.M <= 16 ? 16 : g.M <= 32 ? 32 : g.M <= 64 ? 64 : g.M <= 128 ? 128 : 256;
-    const int splits = force_splits > 0 ? force_splits : pick_splits(g.M, g.N, g.K, bn);
+    int splits = tune().splits > 0 ? tune().splits : pick_splits(g.M, g.N, g.K, bn);
+    const int kblocks = (g.K + BK - 1) / BK;
+    if (splits > kblocks) splits = kblocks;
+    if (splits > 8) splits = 8;
+    const int stages = tune().stages > 0 ? tune().stages : pick_stages(bn);
     switch (bn) {
-        case 16: return launch_epi<16>(g, splits, s);
-        case 32: return launch_epi<32>(g, splits, s);
-        case 64: return launch_epi<64>(g, splits, s);
-        case 128: return launch_epi<128>(g, splits, s);
-        default: return launch_epi<256>(g, splits, s);
+        case 16: return launch_epi<16>(g, splits, stages, s);
+        case 32: return launch_epi<32>(g, splits, stages, s);
+        case 64: return launch_epi<64>(g, splits, stages, s);
+        case 128: return launch_epi<128>(g, splits, stages, s);
+        default: return launch_epi<256>(g, splits, stages, s);
     }
 }
 

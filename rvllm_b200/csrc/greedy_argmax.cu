@@ -106,6 +106,8 @@ __device__ __forceinline__ Cand scan_f32(const float* __restrict__ x, long long 
 extern "C" __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int row = blockIdx.x;
     if (logits == nullptr || out == nullptr || !launch_ok(vocab)) {
         if (out != nullptr && threadIdx.x == 0) out[row] = -1;
@@ -119,6 +121,8 @@ extern "C" __global__ void argmax_kernel(const float* __restrict__ logits, int* 
 extern "C" __global__ void argmax_f16_kernel(const __half* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int row = blockIdx.x;
     if (logits == nullptr || out == nullptr || !launch_ok(vocab)) {
         if (out != nullptr && threadIdx.x == 0) out[row] = -1;
@@ -136,6 +140,8 @@ extern "C" __global__ void argmax_f16_kernel(const __half* __restrict__ logits, 
 extern "C" __global__ void argmax_grid_f32_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    rv::pdl_launch();
+    rv::pdl_wait();
     if (logits == nullptr || out == nullptr || !launch_ok(vocab)) return;
     const int row = blockIdx.y, parts = gridDim.x;
     const long long chunk = ((long long)vocab + parts - 1) / parts;

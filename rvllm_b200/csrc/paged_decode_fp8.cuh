@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
     extern __shared__ __align__(16) float sm[];  // [WARPS][GT][HD + 2]
     __shared__ unsigned s_bad;  // bit j: q-head j of the tile is invalid; all ones: the whole KV head is
 
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int kvh = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit = lane / LPR, sub = lane % LPR;
@@ -286,6 +288,8 @@ __global__ void paged_decode_fp8_combine_kernel(const float* __restrict__ worksp
                                                 const int* __restrict__ context_lens, int heads, int block_size,
                                                 int max_blocks_per_seq, int window_size_left, int max_chunks) {
     constexpr int PSTRIDE = HD + 2;
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int bh = blockIdx.x, b = bh / heads;
     const int ctx = context_lens[b];
     if (ctx <= 0 || (window_size_left < 0 && (long long)ctx > (long long)block_size * max_blocks_per_seq)) return;

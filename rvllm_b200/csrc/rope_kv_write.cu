@@ -53,6 +53,8 @@ __device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, co
                                                 int num_cache_slots) {
     __shared__ float red[33];
     __shared__ int flag;
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int tok = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
     const int half_head = head_dim / 2, half_rot = rotary_dim / 2;
     if (tok >= num_tokens || (int)blockDim.x != half_head || rotary_dim > head_dim || (rotary_dim & 1)) return;
@@ -124,6 +126,8 @@ rvllm_rope_fp8kv_bf16_kernel(const __nv_bfloat16* q_in, const __nv_bfloat16* k_i
 // activation type; grid = (num_tokens), any block size.
 extern "C" __global__ void embedding_gather_f16_kernel(__half* out, const __half* table, const int* token_ids,
                                                        int hidden, int vocab) {
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int t = blockIdx.x, id = token_ids[t];
     unsigned short* o = reinterpret_cast<unsigned short*>(out) + (size_t)t * hidden;
     const unsigned short* src = reinterpret_cast<const unsigned short*>(table) + (size_t)id * hidden;

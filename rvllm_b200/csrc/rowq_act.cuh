@@ -43,6 +43,8 @@ __device__ __forceinline__ void act_mul_quant_row(uint8_t* __restrict__ out, flo
     __shared__ float red[33];
     __shared__ int bad;
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    rv::pdl_launch();
+    rv::pdl_wait();
     if (out == nullptr || scales == nullptr || gate_up == nullptr || inter <= 0 || (inter & 7) != 0) return;
     const T* g = gate_up + (size_t)row * 2 * inter;
     const T* u = g + inter;

@@ -26,6 +26,8 @@ __device__ __forceinline__ void rmsnorm_quant_row(uint8_t* __restrict__ out, flo
                                                   const T* __restrict__ residual, const T* __restrict__ gamma,
                                                   float eps, int hidden) {
     __shared__ __align__(16) T srow[STAGE_ELEMS];
+    rv::pdl_launch();
+    rv::pdl_wait();
     __shared__ float red[33];
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const size_t base = (size_t)row * hidden;
@@ -118,6 +120,8 @@ template <typename T>
 __device__ __forceinline__ void quant_row(uint8_t* __restrict__ out, float* __restrict__ scales,
                                           const T* __restrict__ in, int dim) {
     __shared__ float red[33];
+    rv::pdl_launch();
+    rv::pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const size_t base = (size_t)row * dim;
     const T* x = in + base;

@@ -49,6 +49,7 @@ def _bind():
     L.rvllm_stack_destroy.restype = None
     L.rvllm_stack_reset.argtypes = [vp, vp]
     L.rvllm_stack_run.argtypes = [vp, i32]
+    L.rvllm_stack_seed_context.argtypes = [vp, i32]
     L.rvllm_stack_run_eager.argtypes = [vp, i32]
     L.rvllm_stack_sync.argtypes = [vp]
     L.rvllm_stack_step_host.argtypes = [vp, vp, vp]
@@ -183,6 +184,9 @@ class DecodeStack:
             assert prompt.shape == (self.cfg["batch"], self.cfg["prompt_len"])
             p = prompt.ctypes.data
         check(self._L.rvllm_stack_reset(self._h, p), "stack reset")
+
+    def seed_context(self, context: int) -> None:
+        check(self._L.rvllm_stack_seed_context(self._h, context), "stack seed context")
 
     def run(self, n: int, eager: bool = False) -> None:
         fn = self._L.rvllm_stack_run_eager if eager else self._L.rvllm_stack_run
