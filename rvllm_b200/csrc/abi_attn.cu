@@ -6,7 +6,15 @@
 #include "host_util.h"
 #include "paged_decode_fp8.cuh"
 
+static int g_target_ctas = rvattn::TARGET_CTAS;
+static int g_min_chunk_tokens = rvattn::MIN_CHUNK_TOKENS;
+
 extern "C" {
+
+void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens) {
+    g_target_ctas = target_ctas > 0 ? target_ctas : rvattn::TARGET_CTAS;
+    g_min_chunk_tokens = min_chunk_tokens > 0 ? min_chunk_tokens : rvattn::MIN_CHUNK_TOKENS;
+}
 // ---------------------------------------------------------------- stage 3: attention
 int rvllm_paged_decode_fp8_validate(int batch_size, int num_heads, int num_kv_heads, int head_dim,
                                     int block_size, int max_blocks_per_seq, int num_blocks_total,
@@ -32,7 +40,7 @@ int rvllm_paged_decode_fp8_validate(int batch_size, int num_heads, int num_kv_he
 }
 
 int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads) {
-    return rvattn::pick_max_chunks(batch_size, num_kv_heads);
+    return rvattn::pick_max_chunks(batch_size, num_kv_heads, g_target_ctas);
 }
 
 uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim) {
@@ -40,7 +48,7 @@ uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int nu
         num_heads / num_kv_heads > 32 ||
         (head_dim != 64 && head_dim != 128 && head_dim != 256 && head_dim != 512))
         return UINT64_MAX;
-    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads);
+    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_target_ctas);
     if (chunks <= 1) return 0;
     unsigned long long v = (unsigned long long)batch_size * (unsigned long long)num_heads;
     if (v > (1ULL << 40)) return UINT64_MAX;
@@ -54,7 +62,7 @@ namespace {
 template <int HD, int GT, typename OutT>
 int launch_attn(const rvattn::Params& p, cudaStream_t s) {
     auto kern = rvattn::paged_decode_fp8_kernel<HD, GT, OutT>;
-    const size_t smem = (size_t)rvattn::WARPS * GT * (HD + 2) * sizeof(float);
+    const size_t smem = rvattn::smem_bytes(HD, GT);
     static bool attr_set = false;  // per kernel instantiation
     if (smem > 48 * 1024 && !attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -68,7 +76,7 @@ int launch_attn(const rvattn::Params& p, cudaStream_t s) {
     if (p.max_chunks > 1) {
         rv_launch((rvattn::paged_decode_fp8_combine_kernel<HD, OutT>), dim3(p.batch * p.heads), dim3(HD < 256 ? HD : 256), 0,
                   s, dim3(1, 1, 1), (const float*)p.workspace, (OutT*)p.out, (const int*)p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq,
-            p.window_size_left, p.max_chunks);
+            p.window_size_left, p.max_chunks, p.min_chunk_tokens);
         rc = rv_launched("paged_decode_fp8_combine");
     }
     return rc;
@@ -113,7 +121,7 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
     if (!rv_aligned(q_fp8, 16) || !rv_aligned(k_cache_fp8, 16) || !rv_aligned(v_cache_fp8, 16))
         return rv_fail(RVLLM_E_INVALID, "q / k_cache / v_cache must be 16-byte aligned");
     if (out_dtype != RVLLM_F16 && out_dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "bad output dtype");
-    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads);
+    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_target_ctas);
     const uint64_t need = rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim);
     if (need == UINT64_MAX) return rv_fail(RVLLM_E_INVALID, "workspace size overflows");
     if (chunks > 1 && (!workspace || !rv_aligned(workspace, sizeof(float)) || (uint64_t)workspace_bytes < need))
@@ -144,6 +152,7 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
     p.num_blocks_total = num_blocks_total;
     p.window_size_left = window_size_left;
     p.max_chunks = chunks;
+    p.min_chunk_tokens = g_min_chunk_tokens;
     cudaStream_t s = (cudaStream_t)stream;
     return out_dtype == RVLLM_F16 ? launch_attn_hd<__half>(p, head_dim, s)
                                   : launch_attn_hd<__nv_bfloat16>(p, head_dim, s);

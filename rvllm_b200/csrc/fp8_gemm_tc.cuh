@@ -336,12 +336,13 @@ struct TcArgs {
 
 inline size_t workspace_bytes(int, int, int) { return 0; }
 
-// Which shapes go to the tensor-core kernel when the caller lets the library choose.
+// Which shapes go to the tensor-core kernel when the caller lets the library choose: all of
+// them.  Measured at M = 1, 32 and 128 on the decode shapes it is as fast or faster than the
+// mma.sync streaming kernel, which stays selectable (impl = 1) as an independent cross-check.
 inline bool prefer_tc(int M, int N, int K) {
-    (void)N;
-    (void)K;
     (void)M;
-    return false;
+    (void)N;
+    return K % 16 == 0;
 }
 
 inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -461,13 +462,15 @@ int launch_epi(const TcArgs& g, int splits, int stages, cudaStream_t s) {
                       : launch_one<BN, EPI_SCALE, __nv_bfloat16>(g, splits, stages, s);
 }
 
+// Split-K factor: aim for ~2.5 CTAs per SM (measured best on the decode shapes: 64 weight
+// tiles -> 6 splits, 42 tiles -> 8, 336 tiles -> 1), keeping at least four K blocks per CTA.
 inline int pick_splits(int M, int N, int K, int bn) {
     const int tiles = ((N + TILE_W - 1) / TILE_W) * ((M + bn - 1) / bn);
     const int kblocks = (K + BK - 1) / BK;
-    int s = (148 + tiles - 1) / tiles;
+    int s = (360 + tiles / 2) / tiles;
+    if (s > 8) s = 8;
     while (s > 1 && kblocks / s < 4) s--;
     if (s < 1) s = 1;
-    if (s > 8) s = 8;
     return s;
 }
 
@@ -481,9 +484,10 @@ inline Tune& tune() {
     return t;
 }
 
-// Ring depth: decode-sized tiles keep two CTAs per SM resident (~100 KB each), so one CTA's
-// prologue / epilogue overlaps the other's streaming; large tiles take the whole SM.
-inline int pick_stages(int bn) { return bn == 16 ? 6 : bn == 32 ? 5 : bn == 64 ? 4 : bn == 128 ? 6 : 4; }
+// Ring depth: a shallow ring (3 stages, ~60 KB for a 32-row batch tile) lets three CTAs share an
+// SM, so one CTA's prologue / epilogue overlaps the others' streaming; measured faster than one
+// deep ring per SM on every decode shape (gate|up at M = 32: 93 % vs 58 % of the HBM peak).
+inline int pick_stages(int bn) { return bn <= 64 ? 3 : bn == 128 ? 3 : 4; }
 
 inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
     if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");

@@ -30,6 +30,29 @@ constexpr int WARPS = THREADS / 32;
 constexpr int MIN_CHUNK_TOKENS = 256;
 constexpr int MAX_CHUNKS = 32;
 constexpr int TARGET_CTAS = 148 * 8;
+constexpr int DEPTH = 8;            // cp.async rounds in flight per warp
+constexpr int STAGE_BYTES = 1088;   // 32 lanes x 16 B of K, the same of V, 8 + 8 row scales
+constexpr int TBL_MAX = 2048;       // block-table entries staged in shared memory per CTA
+
+__host__ __device__ constexpr size_t smem_bytes(int hd, int gt) {
+    return (size_t)WARPS * DEPTH * STAGE_BYTES + TBL_MAX * sizeof(int) >
+                   (size_t)WARPS * gt * (hd + 2) * sizeof(float)
+               ? (size_t)WARPS * DEPTH * STAGE_BYTES + TBL_MAX * sizeof(int)
+               : (size_t)WARPS * gt * (hd + 2) * sizeof(float);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 struct Params {
     const uint8_t* q;
@@ -50,14 +73,15 @@ struct Params {
     int block_size, bs_shift;  // bs_shift = log2(block_size) or -1
     int max_blocks_per_seq, num_blocks_total, window_size_left;
     int max_chunks;
+    int min_chunk_tokens;  // a sequence is cut into ceil(attended / this) chunks, at most max_chunks
 };
 
 // Upper bound on chunks per sequence for a launch shape; the workspace-size query and the
 // launch both use it, so they always agree.
-__host__ __device__ inline int pick_max_chunks(int batch, int kv_heads) {
+inline int pick_max_chunks(int batch, int kv_heads, int target_ctas = TARGET_CTAS) {
     long long d = (long long)batch * kv_heads;
     if (d <= 0) return 0;
-    long long c = (TARGET_CTAS + d - 1) / d;
+    long long c = (target_ctas + d - 1) / d;
     if (c < 1) c = 1;
     if (c > MAX_CHUNKS) c = MAX_CHUNKS;
     return (int)c;
@@ -71,8 +95,8 @@ __device__ __forceinline__ void attend_interval(int ctx, int window, int& start,
         start = ctx - len;
     }
 }
-__device__ __forceinline__ int chunks_for(int attend_len, int max_chunks) {
-    int c = (attend_len + MIN_CHUNK_TOKENS - 1) / MIN_CHUNK_TOKENS;
+__device__ __forceinline__ int chunks_for(int attend_len, int max_chunks, int min_tokens) {
+    int c = (attend_len + min_tokens - 1) / min_tokens;
     c = c < 1 ? 1 : c;
     return c < max_chunks ? c : max_chunks;
 }
@@ -91,7 +115,13 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
     constexpr int RPW = 32 / LPR;   // rows a warp covers per step
     constexpr int STEP = WARPS * RPW;
     constexpr int PSTRIDE = HD + 2;
-    extern __shared__ __align__(16) float sm[];  // [WARPS][GT][HD + 2]
+    // dynamic shared memory: per-warp cp.async ring [WARPS][DEPTH][STAGE_BYTES], then the staged
+    // block table [TBL_MAX]; after the stream the ring is reused as the merge buffer
+    // [WARPS][GT][HD + 2] f32.
+    extern __shared__ __align__(16) uint8_t sm_raw[];
+    float* sm = reinterpret_cast<float*>(sm_raw);
+    uint8_t* ring = sm_raw + (size_t)(threadIdx.x >> 5) * DEPTH * STAGE_BYTES;
+    int* tbl = reinterpret_cast<int*>(sm_raw + (size_t)WARPS * DEPTH * STAGE_BYTES);
     __shared__ unsigned s_bad;  // bit j: q-head j of the tile is invalid; all ones: the whole KV head is
 
     rv::pdl_launch();
@@ -113,7 +143,7 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
     }
     int start, len;
     attend_interval(ctx, p.window_size_left, start, len);
-    const int nchunks = chunks_for(len, p.max_chunks);
+    const int nchunks = chunks_for(len, p.max_chunks, p.min_chunk_tokens);
     if (chunk >= nchunks) return;
     const int chunk_size = (len + nchunks - 1) / nchunks;
     const int t_begin = start + chunk * chunk_size;
@@ -122,6 +152,16 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
     const float k_ds_scalar = k_perslot ? 0.0f : *p.k_descale;
     const float v_ds_scalar = v_perslot ? 0.0f : *p.v_descale;
     const int* table = p.block_tables + (size_t)b * p.max_blocks_per_seq;
+    // stage this chunk's slice of the block table (ring-mapped for sliding layers)
+    const int first_page = p.bs_shift >= 0 ? (t_begin >> p.bs_shift) : (t_begin / p.block_size);
+    const int last_page = p.bs_shift >= 0 ? ((t_end - 1) >> p.bs_shift) : ((t_end - 1) / p.block_size);
+    const bool tbl_in_smem = last_page - first_page + 1 <= TBL_MAX;
+    if (tbl_in_smem)
+        for (int i = tid; i <= last_page - first_page; i += THREADS) {
+            const int page = first_page + i;
+            tbl[i] = __ldg(table + (p.window_size_left >= 0 ? page % p.max_blocks_per_seq : page));
+        }
+    __syncthreads();
 
     for (int h0 = 0; h0 < group; h0 += GT) {
         const int nh = min(GT, group - h0);
@@ -148,73 +188,84 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
             for (int d = 0; d < 16; d++) acc[j][d] = 0.0f;
         }
 
-        for (int base = t_begin + warp * RPW; base < t_end; base += 2 * STEP) {
-            // two row groups in flight per warp
-            uint4 kv[2], vv[2];
-            float ks[2], vs[2];
-            bool ok[2];
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const int tok = base + u * STEP + unit;
-                ok[u] = tok < t_end;
-                kv[u] = make_uint4(0, 0, 0, 0);
-                vv[u] = make_uint4(0, 0, 0, 0);
-                ks[u] = 1.0f;
-                vs[u] = 1.0f;
-                if (ok[u]) {
-                    const int page = p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size);
-                    const int off = tok - page * p.block_size;
+        // ---- pipelined K/V stream: DEPTH rounds of cp.async in flight per warp -------------
+        auto issue = [&](int round) {
+            const int tok = t_begin + (round * WARPS + warp) * RPW + unit;
+            uint8_t* st = ring + (size_t)(round % DEPTH) * STAGE_BYTES;
+            if (tok < t_end) {
+                const int page = p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size);
+                const int off = tok - page * p.block_size;
+                int phys;
+                if (tbl_in_smem) {
+                    phys = tbl[page - first_page];
+                } else {
                     const int tpage = p.window_size_left >= 0 ? page % p.max_blocks_per_seq : page;
-                    const int phys = __ldg(table + tpage);
-                    if (phys < 0 || phys >= p.num_blocks_total) {
-                        bad = 0xffffffffu;
-                        ok[u] = false;
-                    } else {
-                        const size_t sidx = ((size_t)phys * p.block_size + off) * p.kv_heads + kvh;
-                        kv[u] = rv::ld_stream128(p.k_cache + sidx * HD + 16 * sub);
-                        vv[u] = rv::ld_stream128(p.v_cache + sidx * HD + 16 * sub);
-                        ks[u] = k_perslot ? __ldg(p.k_scale_cache + sidx) : k_ds_scalar;
-                        vs[u] = v_perslot ? __ldg(p.v_scale_cache + sidx) : v_ds_scalar;
-                    }
+                    phys = __ldg(table + tpage);
+                }
+                if (phys < 0 || phys >= p.num_blocks_total) {
+                    bad = 0xffffffffu;
+                } else {
+                    const size_t sidx = ((size_t)phys * p.block_size + off) * p.kv_heads + kvh;
+                    cp_async16(st + lane * 16, p.k_cache + sidx * HD + 16 * sub);
+                    cp_async16(st + 512 + lane * 16, p.v_cache + sidx * HD + 16 * sub);
+                    if (k_perslot && sub == 0) cp_async4(st + 1024 + unit * 4, p.k_scale_cache + sidx);
+                    if (v_perslot && sub == 1) cp_async4(st + 1024 + 32 + unit * 4, p.v_scale_cache + sidx);
                 }
             }
+            cp_async_commit();
+        };
+        const int rounds = (t_end - t_begin + STEP - 1) / STEP;
+#pragma unroll 1
+        for (int r = 0; r < DEPTH; r++) issue(r);
+#pragma unroll 1
+        for (int r = 0; r < rounds; r++) {
+            cp_async_wait<DEPTH - 1>();
+            __syncwarp();
+            const uint8_t* st = ring + (size_t)(r % DEPTH) * STAGE_BYTES;
+            const int tok = t_begin + (r * WARPS + warp) * RPW + unit;
+            const bool ok = tok < t_end;
+            const uint4 kv = *reinterpret_cast<const uint4*>(st + lane * 16);
+            const uint4 vv = *reinterpret_cast<const uint4*>(st + 512 + lane * 16);
+            const float ks = k_perslot ? *reinterpret_cast<const float*>(st + 1024 + unit * 4) : k_ds_scalar;
+            const float vs = v_perslot ? *reinterpret_cast<const float*>(st + 1024 + 32 + unit * 4) : v_ds_scalar;
+            __syncwarp();
+            issue(r + DEPTH);  // refill the stage just read
+            float kf[16];
+            dequant16(kv, kf);
+            float dot[GT];
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                float kf[16];
-                dequant16(kv[u], kf);
-                float dot[GT];
+            for (int j = 0; j < GT; j++) {
+                float acc_s = 0.0f;
+#pragma unroll
+                for (int d = 0; d < 16; d++) acc_s = fmaf(q[j][d], kf[d], acc_s);
+                dot[j] = acc_s;
+            }
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1)
+#pragma unroll
+                for (int j = 0; j < GT; j++) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+            if (ok && bad != 0xffffffffu) {
+                if (bad_scale(ks) || bad_scale(vs)) bad = 0xffffffffu;
+                float vf[16];
+                dequant16(vv, vf);
+                const float kscale = ks * p.scale;
 #pragma unroll
                 for (int j = 0; j < GT; j++) {
-                    float s = 0.0f;
+                    const float qk = dot[j] * kscale;
+                    if (!isfinite(qk)) bad |= 1u << j;
+                    const float m_new = fmaxf(m[j], qk);
+                    const float e0 = __expf(m[j] - m_new);
+                    const float e1 = __expf(qk - m_new);
+                    const float ev = e1 * vs;
 #pragma unroll
-                    for (int d = 0; d < 16; d++) s = fmaf(q[j][d], kf[d], s);
-                    dot[j] = s;
-                }
-#pragma unroll
-                for (int o = LPR / 2; o > 0; o >>= 1)
-#pragma unroll
-                    for (int j = 0; j < GT; j++) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
-                if (ok[u]) {
-                    if (bad_scale(ks[u]) || bad_scale(vs[u])) bad = 0xffffffffu;
-                    float vf[16];
-                    dequant16(vv[u], vf);
-                    const float kscale = ks[u] * p.scale;
-#pragma unroll
-                    for (int j = 0; j < GT; j++) {
-                        const float qk = dot[j] * kscale;
-                        if (!isfinite(qk)) bad |= 1u << j;
-                        const float m_new = fmaxf(m[j], qk);
-                        const float e0 = __expf(m[j] - m_new);
-                        const float e1 = __expf(qk - m_new);
-                        const float ev = e1 * vs[u];
-#pragma unroll
-                        for (int d = 0; d < 16; d++) acc[j][d] = fmaf(ev, vf[d], acc[j][d] * e0);
-                        l[j] = l[j] * e0 + e1;
-                        m[j] = m_new;
-                    }
+                    for (int d = 0; d < 16; d++) acc[j][d] = fmaf(ev, vf[d], acc[j][d] * e0);
+                    l[j] = l[j] * e0 + e1;
+                    m[j] = m_new;
                 }
             }
         }
+        cp_async_wait<0>();
+        __syncthreads();  // every warp is done with its ring before the merge buffer overlays it
 
         // merge the row groups of this warp (same sub-lane, different unit)
 #pragma unroll
@@ -286,7 +337,8 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
 template <int HD, typename OutT>
 __global__ void paged_decode_fp8_combine_kernel(const float* __restrict__ workspace, OutT* __restrict__ out,
                                                 const int* __restrict__ context_lens, int heads, int block_size,
-                                                int max_blocks_per_seq, int window_size_left, int max_chunks) {
+                                                int max_blocks_per_seq, int window_size_left, int max_chunks,
+                                                int min_chunk_tokens) {
     constexpr int PSTRIDE = HD + 2;
     rv::pdl_launch();
     rv::pdl_wait();
@@ -295,7 +347,7 @@ __global__ void paged_decode_fp8_combine_kernel(const float* __restrict__ worksp
     if (ctx <= 0 || (window_size_left < 0 && (long long)ctx > (long long)block_size * max_blocks_per_seq)) return;
     int start, len;
     attend_interval(ctx, window_size_left, start, len);
-    const int nchunks = chunks_for(len, max_chunks);
+    const int nchunks = chunks_for(len, max_chunks, min_chunk_tokens);
     if (nchunks <= 1) return;  // the main kernel already wrote the row
     const float* ws = workspace + (size_t)bh * max_chunks * PSTRIDE;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
