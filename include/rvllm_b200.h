@@ -186,6 +186,22 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
                            int num_heads, int num_kv_heads, int head_dim, int block_size,
                            int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream);
 
+/* Attention with its epilogue fused: the chunk partials are combined per token, rounded to the
+ * 16-bit type `round_dtype` exactly as the plain call would store them, and quantised per token
+ * over the whole [heads * head_dim] row — the bytes and scales equal those of
+ * rvllm_paged_decode_fp8 followed by rvllm_quantize_fp8_per_token_launch
+ * (v3/crates/rvllm-runtime/src/layer_exec.rs:326-362,425), with one launch and one 16-bit
+ * round trip less.  out_fp8 [batch, heads*head_dim] u8, out_scale [batch] f32.  The workspace is
+ * always needed: rvllm_paged_decode_quant_workspace_size bytes. */
+uint64_t rvllm_paged_decode_quant_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim);
+int rvllm_paged_decode_fp8_quant(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* out_fp8,
+                                 float* out_scale, int round_dtype, const int32_t* block_tables,
+                                 const int32_t* context_lens, void* workspace, size_t workspace_bytes,
+                                 const float* k_scale_cache, const float* v_scale_cache, const float* q_scale_cache,
+                                 const float* q_descale, const float* k_descale, const float* v_descale, float scale,
+                                 int batch_size, int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                 int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream);
+
 /* ---- 6. neighbours of the path ------------------------------------------------------
  * RoPE + Q quantisation + paged FP8 KV write with per-(slot, head) scales
  * (v3/kernels/fused_rope_partial_fp8kv.cu:54; launcher

@@ -57,3 +57,23 @@ class PagedDecodeFp8Launcher:
                                            p.head_dim, p.block_size, p.max_blocks_per_seq, p.num_blocks_total,
                                            p.window_size_left, _lib.current_stream() if stream is None else stream),
               "paged_decode_fp8")
+
+
+    def quant_workspace_bytes(self) -> int:
+        p = self.params
+        return int(lib().rvllm_paged_decode_quant_workspace_size(p.num_seqs, p.num_heads, p.num_kv_heads, p.head_dim))
+
+    def launch_quant(self, q_fp8, k_cache, v_cache, out_fp8, out_scale, round_dtype, block_tables, context_lens,
+                     workspace, k_scale_cache=None, v_scale_cache=None, q_scale_cache=None, q_descale=None,
+                     k_descale=None, v_descale=None, stream=None) -> None:
+        """Attention + LSE combine + per-token FP8 quantisation of the [heads*head_dim] row in one call."""
+        p = self.params
+        p.validate()
+        check(lib().rvllm_paged_decode_fp8_quant(ptr(q_fp8), ptr(k_cache), ptr(v_cache), ptr(out_fp8), ptr(out_scale),
+                                                 round_dtype, ptr(block_tables), ptr(context_lens), ptr(workspace),
+                                                 workspace.numel() * workspace.element_size(), ptr(k_scale_cache),
+                                                 ptr(v_scale_cache), ptr(q_scale_cache), ptr(q_descale), ptr(k_descale),
+                                                 ptr(v_descale), p.scale, p.num_seqs, p.num_heads, p.num_kv_heads,
+                                                 p.head_dim, p.block_size, p.max_blocks_per_seq, p.num_blocks_total,
+                                                 p.window_size_left, _lib.current_stream() if stream is None else stream),
+              "paged_decode_fp8_quant")

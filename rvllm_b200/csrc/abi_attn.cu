@@ -55,12 +55,24 @@ uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int nu
     return v * (unsigned long long)chunks * (unsigned long long)(head_dim + 2) * sizeof(float);
 }
 
+uint64_t rvllm_paged_decode_quant_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim) {
+    if (rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim) == UINT64_MAX) return UINT64_MAX;
+    const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_target_ctas);
+    return (unsigned long long)batch_size * (unsigned long long)num_heads * (unsigned long long)(chunks < 1 ? 1 : chunks) *
+           (unsigned long long)(head_dim + 2) * sizeof(float);
+}
+
 }  // extern "C"
 
 namespace {
 
+struct QuantOut {
+    uint8_t* fp8 = nullptr;  // when set: fused combine + per-token quantisation instead of a 16-bit output
+    float* scale = nullptr;
+};
+
 template <int HD, int GT, typename OutT>
-int launch_attn(const rvattn::Params& p, cudaStream_t s) {
+int launch_attn(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
     auto kern = rvattn::paged_decode_fp8_kernel<HD, GT, OutT>;
     const size_t smem = rvattn::smem_bytes(HD, GT);
     static bool attr_set = false;  // per kernel instantiation
@@ -73,6 +85,21 @@ int launch_attn(const rvattn::Params& p, cudaStream_t s) {
     rv_launch(kern, grid, dim3(rvattn::THREADS), smem, s, dim3(1, 1, 1), p);
     int rc = rv_launched("paged_decode_fp8");
     if (rc) return rc;
+    if (qo.fp8) {
+        auto qk = rvattn::paged_decode_fp8_combine_quant_kernel<HD, OutT>;
+        const size_t qsmem = (size_t)p.heads * HD * sizeof(float);
+        static bool qattr = false;
+        if (qsmem > 48 * 1024 && !qattr) {
+            if (cudaFuncSetAttribute(qk, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the attention quant pass");
+            qattr = true;
+        }
+        if (qsmem > 160 * 1024) return rv_fail(RVLLM_E_UNSUPPORTED, "heads * head_dim too large for the fused quant pass");
+        rv_launch(qk, dim3(p.batch), dim3(512), qsmem, s, dim3(1, 1, 1), (const float*)p.workspace, qo.fp8, qo.scale,
+                  (const int*)p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq, p.window_size_left,
+                  p.max_chunks, p.min_chunk_tokens);
+        return rv_launched("paged_decode_fp8_combine_quant");
+    }
     if (p.max_chunks > 1) {
         rv_launch((rvattn::paged_decode_fp8_combine_kernel<HD, OutT>), dim3(p.batch * p.heads), dim3(HD < 256 ? HD : 256), 0,
                   s, dim3(1, 1, 1), (const float*)p.workspace, (OutT*)p.out, (const int*)p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq,
@@ -83,20 +110,20 @@ int launch_attn(const rvattn::Params& p, cudaStream_t s) {
 }
 
 template <int HD, typename OutT>
-int launch_attn_gt(const rvattn::Params& p, cudaStream_t s) {
+int launch_attn_gt(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
     const int group = p.heads / p.kv_heads;
-    if (group == 1) return launch_attn<HD, 1, OutT>(p, s);
-    if (group == 2) return launch_attn<HD, 2, OutT>(p, s);
-    return launch_attn<HD, 4, OutT>(p, s);
+    if (group == 1) return launch_attn<HD, 1, OutT>(p, qo, s);
+    if (group == 2) return launch_attn<HD, 2, OutT>(p, qo, s);
+    return launch_attn<HD, 4, OutT>(p, qo, s);
 }
 
 template <typename OutT>
-int launch_attn_hd(const rvattn::Params& p, int head_dim, cudaStream_t s) {
+int launch_attn_hd(const rvattn::Params& p, const QuantOut& qo, int head_dim, cudaStream_t s) {
     switch (head_dim) {
-        case 64: return launch_attn_gt<64, OutT>(p, s);
-        case 128: return launch_attn_gt<128, OutT>(p, s);
-        case 256: return launch_attn_gt<256, OutT>(p, s);
-        default: return launch_attn_gt<512, OutT>(p, s);
+        case 64: return launch_attn_gt<64, OutT>(p, qo, s);
+        case 128: return launch_attn_gt<128, OutT>(p, qo, s);
+        case 256: return launch_attn_gt<256, OutT>(p, qo, s);
+        default: return launch_attn_gt<512, OutT>(p, qo, s);
     }
 }
 
@@ -104,7 +131,7 @@ int launch_attn_hd(const rvattn::Params& p, int head_dim, cudaStream_t s) {
 
 extern "C" {
 
-int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
+static int decode_core(const QuantOut& qo, const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
                            int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
                            void* workspace, size_t workspace_bytes, const float* k_scale_cache,
                            const float* v_scale_cache, const float* q_scale_cache, const float* q_descale,
@@ -114,7 +141,7 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
     int rc = rvllm_paged_decode_fp8_validate(batch_size, num_heads, num_kv_heads, head_dim, block_size,
                                              max_blocks_per_seq, num_blocks_total, window_size_left, scale);
     if (rc) return rc;
-    if (!q_fp8 || !k_cache_fp8 || !v_cache_fp8 || !output || !block_tables || !context_lens)
+    if (!q_fp8 || !k_cache_fp8 || !v_cache_fp8 || (!output && !qo.fp8) || !block_tables || !context_lens)
         return rv_fail(RVLLM_E_INVALID, "null device pointer");
     if ((!q_scale_cache && !q_descale) || (!k_scale_cache && !k_descale) || (!v_scale_cache && !v_descale))
         return rv_fail(RVLLM_E_INVALID, "each of Q, K, V needs a scale cache or a scalar descale");
@@ -122,9 +149,10 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
         return rv_fail(RVLLM_E_INVALID, "q / k_cache / v_cache must be 16-byte aligned");
     if (out_dtype != RVLLM_F16 && out_dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "bad output dtype");
     const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_target_ctas);
-    const uint64_t need = rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim);
+    const uint64_t need = qo.fp8 ? rvllm_paged_decode_quant_workspace_size(batch_size, num_heads, num_kv_heads, head_dim)
+                                 : rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim);
     if (need == UINT64_MAX) return rv_fail(RVLLM_E_INVALID, "workspace size overflows");
-    if (chunks > 1 && (!workspace || !rv_aligned(workspace, sizeof(float)) || (uint64_t)workspace_bytes < need))
+    if ((chunks > 1 || qo.fp8) && (!workspace || !rv_aligned(workspace, sizeof(float)) || (uint64_t)workspace_bytes < need))
         return rv_fail(RVLLM_E_WORKSPACE, "attention workspace missing, misaligned or smaller than the query reports");
     rvattn::Params p;
     p.q = (const uint8_t*)q_fp8;
@@ -153,9 +181,40 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
     p.window_size_left = window_size_left;
     p.max_chunks = chunks;
     p.min_chunk_tokens = g_min_chunk_tokens;
+    p.force_partial = qo.fp8 ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    return out_dtype == RVLLM_F16 ? launch_attn_hd<__half>(p, head_dim, s)
-                                  : launch_attn_hd<__nv_bfloat16>(p, head_dim, s);
+    return out_dtype == RVLLM_F16 ? launch_attn_hd<__half>(p, qo, head_dim, s)
+                                  : launch_attn_hd<__nv_bfloat16>(p, qo, head_dim, s);
+}
+
+int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
+                           int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
+                           void* workspace, size_t workspace_bytes, const float* k_scale_cache,
+                           const float* v_scale_cache, const float* q_scale_cache, const float* q_descale,
+                           const float* k_descale, const float* v_descale, float scale, int batch_size,
+                           int num_heads, int num_kv_heads, int head_dim, int block_size,
+                           int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream) {
+    return decode_core(QuantOut(), q_fp8, k_cache_fp8, v_cache_fp8, output, out_dtype, block_tables, context_lens,
+                       workspace, workspace_bytes, k_scale_cache, v_scale_cache, q_scale_cache, q_descale, k_descale,
+                       v_descale, scale, batch_size, num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                       num_blocks_total, window_size_left, stream);
+}
+
+int rvllm_paged_decode_fp8_quant(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* out_fp8,
+                                 float* out_scale, int round_dtype, const int32_t* block_tables,
+                                 const int32_t* context_lens, void* workspace, size_t workspace_bytes,
+                                 const float* k_scale_cache, const float* v_scale_cache, const float* q_scale_cache,
+                                 const float* q_descale, const float* k_descale, const float* v_descale, float scale,
+                                 int batch_size, int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                 int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream) {
+    if (!out_fp8 || !out_scale) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    QuantOut qo;
+    qo.fp8 = (uint8_t*)out_fp8;
+    qo.scale = out_scale;
+    return decode_core(qo, q_fp8, k_cache_fp8, v_cache_fp8, nullptr, round_dtype, block_tables, context_lens, workspace,
+                       workspace_bytes, k_scale_cache, v_scale_cache, q_scale_cache, q_descale, k_descale, v_descale,
+                       scale, batch_size, num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                       num_blocks_total, window_size_left, stream);
 }
 
 int rvllm_fa_sm89_abi_version(void) { return 2; }

@@ -216,7 +216,7 @@ size_t layout(rvllm_stack* s, uint8_t* base) {
     s->logits = (float*)take((size_t)B * c.vocab * sizeof(float));
     uint64_t aw = 0;
     for (int hd : {c.sliding_head_dim, c.global_head_dim}) {
-        uint64_t w = rvllm_paged_decode_workspace_size(B, c.heads, c.kv_heads, hd);
+        uint64_t w = rvllm_paged_decode_quant_workspace_size(B, c.heads, c.kv_heads, hd);
         aw = w > aw ? w : aw;
     }
     s->attn_ws_bytes = (size_t)aw;
@@ -281,13 +281,13 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                        L.global ? s->slots_global : s->slots_sliding, B, c.heads, c.kv_heads,
                                        L.head_dim, L.head_dim, c.max_context, L.num_blocks * c.block_size, c.dtype,
                                        st));
-        RV_TRY(rvllm_paged_decode_fp8(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype,
-                                      L.global ? s->tables_global : s->tables_sliding, s->ctx_lens, s->attn_ws,
-                                      s->attn_ws_bytes, L.k_scale, L.v_scale, s->q_scale, nullptr, nullptr, nullptr,
-                                      1.0f / sqrtf((float)L.head_dim), B, c.heads, c.kv_heads, L.head_dim,
-                                      c.block_size, L.max_blocks, L.num_blocks, L.window_left, st));
-        const int chunks = rvllm_paged_decode_max_chunks(B, c.kv_heads);
-        RV_TRY(rvllm_quantize_fp8_per_token_launch(B, L.q_dim, s->x_fp8, s->x_scale, s->attn_out, c.dtype, st));
+        // attention with its combine + per-token quantisation fused (bytes equal to the plain
+        // attention call followed by the per-token quantiser)
+        RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->x_fp8, s->x_scale, c.dtype,
+                                            L.global ? s->tables_global : s->tables_sliding, s->ctx_lens, s->attn_ws,
+                                            s->attn_ws_bytes, L.k_scale, L.v_scale, s->q_scale, nullptr, nullptr,
+                                            nullptr, 1.0f / sqrtf((float)L.head_dim), B, c.heads, c.kv_heads,
+                                            L.head_dim, c.block_size, L.max_blocks, L.num_blocks, L.window_left, st));
         RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.o_w, s->x_scale, W.o_scale, s->residual,
                                            B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
         RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
@@ -297,7 +297,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         RV_TRY(rvllm_fused_act_mul_fp8_quant_launch(B, c.ffn, c.act, s->x_fp8, s->x_scale, s->gateup, c.dtype, st));
         RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.down_w, s->x_scale, W.down_scale,
                                            s->residual, B, H, c.ffn, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
-        n += 10 + (chunks > 1 ? 1 : 0);
+        n += 10;
     }
     RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
                                                 s->head.final_norm_gamma, c.dtype, st));

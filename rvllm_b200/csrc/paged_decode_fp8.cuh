@@ -74,6 +74,7 @@ struct Params {
     int max_blocks_per_seq, num_blocks_total, window_size_left;
     int max_chunks;
     int min_chunk_tokens;  // a sequence is cut into ceil(attended / this) chunks, at most max_chunks
+    int force_partial;     // always leave partials in the workspace (the fused combine+quant pass reads them)
 };
 
 // Upper bound on chunks per sequence for a launch shape; the workspace-size query and the
@@ -137,6 +138,14 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
     if (ctx <= 0 || (p.window_size_left < 0 && (long long)ctx > capacity)) {
         if (chunk != 0) return;
         const float fill = ctx == 0 ? 0.0f : CUDART_NAN_F;
+        if (p.force_partial) {
+            for (int i = tid; i < group * PSTRIDE; i += THREADS) {
+                const int hh = i / PSTRIDE, d = i % PSTRIDE;
+                float* ws = p.workspace + (((size_t)b * p.heads + (size_t)kvh * group + hh) * p.max_chunks) * PSTRIDE;
+                ws[d] = d < HD ? fill : (d == HD ? -1e20f : 0.0f);
+            }
+            return;
+        }
         for (int i = tid; i < group * HD; i += THREADS)
             out[((size_t)b * p.heads + (size_t)kvh * group) * HD + i] = rv::T16<OutT>::from_f32(fill);
         return;
@@ -316,7 +325,7 @@ __global__ void __launch_bounds__(THREADS) paged_decode_fp8_kernel(Params p) {
                 M = Mn;
             }
             const int head = kvh * group + h0 + j;
-            if (nchunks == 1) {
+            if (nchunks == 1 && !p.force_partial) {
                 float v = L > 0.0f ? A / L : A;
                 if (any_bad) v = CUDART_NAN_F;
                 out[((size_t)b * p.heads + head) * HD + d] = rv::T16<OutT>::from_f32(v);
@@ -362,6 +371,61 @@ __global__ void paged_decode_fp8_combine_kernel(const float* __restrict__ worksp
             M = Mn;
         }
         out[(size_t)bh * HD + d] = rv::T16<OutT>::from_f32(L > 0.0f ? A / L : A);
+    }
+}
+
+// Fused epilogue of a decode-attention call: LSE-combine every head of one token, round to the
+// 16-bit activation type (so the bytes equal those of combine -> store -> quantize), then the
+// per-token FP8 quantisation of the whole [heads * HD] row (reference: QuantizeFp8PerTokenLaunch
+// after the attention launch, v3/crates/rvllm-runtime/src/layer_exec.rs:425).  grid = (batch),
+// 512 threads, heads * HD floats of dynamic shared memory.  The main kernel ran with
+// force_partial, so every (head, chunk) partial is in the workspace.
+template <int HD, typename OutT>
+__global__ void __launch_bounds__(512)
+paged_decode_fp8_combine_quant_kernel(const float* __restrict__ workspace, uint8_t* __restrict__ out_fp8,
+                                      float* __restrict__ out_scale, const int* __restrict__ context_lens, int heads,
+                                      int block_size, int max_blocks_per_seq, int window_size_left, int max_chunks,
+                                      int min_chunk_tokens) {
+    constexpr int PSTRIDE = HD + 2;
+    extern __shared__ __align__(16) float row[];  // [heads * HD]
+    __shared__ float red[33];
+    rv::pdl_launch();
+    rv::pdl_wait();
+    const int b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const int ctx = context_lens[b];
+    int nchunks = 1;
+    if (!(ctx <= 0 || (window_size_left < 0 && (long long)ctx > (long long)block_size * max_blocks_per_seq))) {
+        int start, len;
+        attend_interval(ctx, window_size_left, start, len);
+        nchunks = chunks_for(len, max_chunks, min_chunk_tokens);
+    }
+    const int dim = heads * HD;
+    float amax = 0.0f;
+    for (int e = tid; e < dim; e += nt) {
+        const int h = e / HD, d = e % HD;
+        const float* ws = workspace + ((size_t)b * heads + h) * max_chunks * PSTRIDE;
+        float M = -1e20f, L = 0.0f, A = 0.0f;
+        for (int c = 0; c < nchunks; c++) {
+            const float* src = ws + (size_t)c * PSTRIDE;
+            const float mc = src[HD], lc = src[HD + 1];
+            const float Mn = fmaxf(M, mc);
+            const float ea = __expf(M - Mn), eb = __expf(mc - Mn);
+            A = A * ea + src[d] * eb;
+            L = L * ea + lc * eb;
+            M = Mn;
+        }
+        const float v = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32(L > 0.0f ? A / L : A));
+        row[e] = v;
+        amax = fmaxf(amax, fabsf(v));
+    }
+    amax = rv::block_max(amax, red);
+    const float scale = rv::row_scale(amax);
+    if (tid == 0) out_scale[b] = scale;
+    const float inv = 1.0f / scale;
+    uint8_t* o = out_fp8 + (size_t)b * dim;
+    for (int v4 = tid; v4 < dim / 4; v4 += nt) {
+        const float4 f = reinterpret_cast<const float4*>(row)[v4];
+        reinterpret_cast<uint32_t*>(o)[v4] = rv::f32x4_to_e4m3x4(f.x * inv, f.y * inv, f.z * inv, f.w * inv);
     }
 }
 

@@ -182,6 +182,34 @@ def test_invalid_data_gives_nan_never_a_fault(orc):
     assert np.isnan(run_ours(c)[0]).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("batch,HD,window,ctxs", [(5, 128, 1023, [0, 1, 700, 3000, 40]), (1, 256, -1, [9000]),
+                                                   (40, 64, -1, list(range(1, 41)))])
+def test_fused_quant_epilogue_equals_attention_then_quantiser(orc, dtype, batch, HD, window, ctxs):
+    """rvllm_paged_decode_fp8_quant == rvllm_paged_decode_fp8 followed by the per-token quantiser,
+    bit for bit (bytes and scales)."""
+    from rvllm_b200.attention import PagedDecodeFp8Launcher, PagedDecodeParams
+    from rvllm_b200.launchers import QuantizeFp8PerTokenLaunch
+    bs, Hh, KVH = 16, 32, 16
+    mb = None if window < 0 else (window + 1 + bs - 1) // bs + 1
+    c = datagen.attention_case(orc, batch, Hh, KVH, HD, bs, ctxs, seed=21, window=window, max_blocks=mb)
+    p = PagedDecodeParams(batch, Hh, KVH, HD, bs, c["max_blocks"], c["num_blocks"], HD ** -0.5, window)
+    La = PagedDecodeFp8Launcher(p)
+    t = {k: dev(c[k]) for k in ("q", "k", "v", "tables", "ctx", "ks", "vs", "qs")}
+    ws = torch.empty(max(La.quant_workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
+    out16 = torch.empty((batch, Hh * HD), dtype=dtype, device="cuda")
+    La.launch(t["q"], t["k"], t["v"], out16, t["tables"], t["ctx"], workspace=ws, k_scale_cache=t["ks"],
+              v_scale_cache=t["vs"], q_scale_cache=t["qs"])
+    b1 = torch.empty((batch, Hh * HD), dtype=torch.uint8, device="cuda")
+    s1 = torch.empty(batch, dtype=torch.float32, device="cuda")
+    QuantizeFp8PerTokenLaunch(batch, Hh * HD).launch(b1, s1, out16)
+    b2, s2 = torch.zeros_like(b1), torch.zeros_like(s1)
+    La.launch_quant(t["q"], t["k"], t["v"], b2, s2, 0 if dtype == torch.float16 else 1, t["tables"], t["ctx"], ws,
+                    k_scale_cache=t["ks"], v_scale_cache=t["vs"], q_scale_cache=t["qs"])
+    torch.cuda.synchronize()
+    assert torch.equal(s1, s2) and torch.equal(b1, b2)
+
+
 def test_launcher_validation_and_workspace_contract():
     # v3/crates/rvllm-attention/src/decode.rs:732-766 and fp8_decode_v2.cu:1015-1037
     from rvllm_b200 import _lib
