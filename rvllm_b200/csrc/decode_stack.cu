@@ -281,13 +281,23 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                        L.global ? s->slots_global : s->slots_sliding, B, c.heads, c.kv_heads,
                                        L.head_dim, L.head_dim, c.max_context, L.num_blocks * c.block_size, c.dtype,
                                        st));
-        // attention with its combine + per-token quantisation fused (bytes equal to the plain
-        // attention call followed by the per-token quantiser)
-        RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->x_fp8, s->x_scale, c.dtype,
-                                            L.global ? s->tables_global : s->tables_sliding, s->ctx_lens, s->attn_ws,
-                                            s->attn_ws_bytes, L.k_scale, L.v_scale, s->q_scale, nullptr, nullptr,
-                                            nullptr, 1.0f / sqrtf((float)L.head_dim), B, c.heads, c.kv_heads,
-                                            L.head_dim, c.block_size, L.max_blocks, L.num_blocks, L.window_left, st));
+        const float sm_scale = 1.0f / sqrtf((float)L.head_dim);
+        const int* tables = L.global ? s->tables_global : s->tables_sliding;
+        if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
+            // split-KV: the combine pass also does the per-token quantisation (same bytes as the
+            // plain attention call followed by the quantiser)
+            RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->x_fp8, s->x_scale, c.dtype, tables,
+                                                s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
+                                                s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads,
+                                                c.kv_heads, L.head_dim, c.block_size, L.max_blocks, L.num_blocks,
+                                                L.window_left, st));
+        } else {
+            RV_TRY(rvllm_paged_decode_fp8(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, tables, s->ctx_lens,
+                                          s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale, s->q_scale, nullptr,
+                                          nullptr, nullptr, sm_scale, B, c.heads, c.kv_heads, L.head_dim, c.block_size,
+                                          L.max_blocks, L.num_blocks, L.window_left, st));
+            RV_TRY(rvllm_quantize_fp8_per_token_launch(B, L.q_dim, s->x_fp8, s->x_scale, s->attn_out, c.dtype, st));
+        }
         RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.o_w, s->x_scale, W.o_scale, s->residual,
                                            B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
         RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
