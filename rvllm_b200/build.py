@@ -37,7 +37,7 @@ PTX_MODULES = {
     "argmax": "greedy_argmax.cu",
     "embedding_gather_f16": "rope_kv_write.cu",
 }
-REVISION = "b200r1a0000"
+REVISION = "b200f8e4d0c1"
 
 
 def _run(cmd):

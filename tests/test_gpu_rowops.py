@@ -265,3 +265,35 @@ def test_argmax_matches_reference_kernel(orc, sym, grid_variant):
         torch.cuda.synchronize()
         got[tag] = out.cpu().numpy()
     assert got["ours"].tolist() == got["ref"].tolist() == orc.argmax_f32(x, orc.MODE_CUDA).tolist()
+
+
+def test_manifest_loader_launch_raw_matches_c_abi(orc):
+    """The verified PTX bundle, loaded and launched through the library's own manifest loader
+    (the KernelLoader::load_ptx -> launch_raw path), gives the bytes the C-ABI launcher gives."""
+    import ctypes as C
+    import os
+    from rvllm_b200 import build
+    from rvllm_b200.launchers import FusedRmsnormFp8QuantLaunch
+    from rvllm_b200.manifest import VerifiedManifest
+    kdir = os.path.join(os.path.dirname(build.LIB), "kernels", "sm_100")
+    digest = open(os.path.join(kdir, "manifest.sha256")).read().split()[0]
+    vm = VerifiedManifest(os.path.join(kdir, "manifest.json"), digest, build.REVISION, "sm_100")
+    mod = vm.load_ptx("fused_rmsnorm_fp8_quant")
+    tokens, hidden = 7, 5376
+    x = dev16(rand16(orc, (tokens, hidden), 1, 77), 1)
+    gamma = dev16(rand16(orc, (hidden,), 1, 78), 1)
+    out = [torch.empty((tokens, hidden), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    sc = [torch.empty(tokens, dtype=torch.float32, device="cuda") for _ in range(2)]
+    vp = C.c_void_p
+    mod.launch_raw("fused_rmsnorm_fp8_quant_bf16_kernel", (tokens,), (1024,), 128,
+                   [(vp, out[0].data_ptr()), (vp, sc[0].data_ptr()), (vp, x.data_ptr()), (vp, gamma.data_ptr()),
+                    (C.c_float, 1e-6), (C.c_int, hidden)])
+    FusedRmsnormFp8QuantLaunch(tokens, hidden, 1e-6).launch(out[1], sc[1], x, gamma)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], out[1]) and torch.equal(sc[0], sc[1])
+    from rvllm_b200 import RvllmError
+    with pytest.raises(RvllmError):
+        mod.function("no_such_kernel")
+    with pytest.raises(RvllmError):
+        mod.launch_raw("fused_rmsnorm_fp8_quant_bf16_kernel", (tokens,), (2048,), 0, [])
+    mod.close()
