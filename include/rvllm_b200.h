@@ -203,6 +203,29 @@ int rvllm_paged_decode_fp8_quant(const void* q_fp8, const void* k_cache_fp8, con
                                  int batch_size, int num_heads, int num_kv_heads, int head_dim, int block_size,
                                  int max_blocks_per_seq, int num_blocks_total, int window_size_left, void* stream);
 
+/* Decode attention without a caller workspace.  No counterpart in the reference: its callers
+ * always own an arena to cut a workspace from.  This entry point is for callers that cannot
+ * allocate device memory at all — a runtime whose memory was split into fixed regions at start-up,
+ * or a plug-in whose host does not let it call the CUDA allocator.  The split-KV partials go into
+ * an 8 MiB scratch array compiled into the library (rvllm_paged_decode_static_scratch_bytes();
+ * every GPU that loads the library holds it until the process exits).  Same arguments, results and
+ * errors as rvllm_paged_decode_fp8 minus workspace / workspace_bytes; a launch whose partials need
+ * more than the built-in scratch is refused with RVLLM_E_WORKSPACE and nothing is launched.  It
+ * calls no allocating routine.  The first call on each device looks up the scratch's device
+ * address (once, with that device current), so make that first call before any stream capture
+ * begins.  All calls on a device share the one array and it keeps the last call's contents
+ * (nothing in it needs clearing between calls): two calls whose kernels overlap on the GPU — on
+ * different streams — race on it; keep them on one stream or order them with events. */
+size_t rvllm_paged_decode_static_scratch_bytes(void);
+int rvllm_paged_decode_fp8_static_scratch(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8,
+                                          void* output, int out_dtype, const int32_t* block_tables,
+                                          const int32_t* context_lens, const float* k_scale_cache,
+                                          const float* v_scale_cache, const float* q_scale_cache,
+                                          const float* q_descale, const float* k_descale, const float* v_descale,
+                                          float scale, int batch_size, int num_heads, int num_kv_heads, int head_dim,
+                                          int block_size, int max_blocks_per_seq, int num_blocks_total,
+                                          int window_size_left, void* stream);
+
 /* ---- 6. neighbours of the path ------------------------------------------------------
  * RoPE + Q quantisation + paged FP8 KV write with per-(slot, head) scales
  * (v3/kernels/fused_rope_partial_fp8kv.cu:54; launcher

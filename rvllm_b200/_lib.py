@@ -76,6 +76,8 @@ SIGNATURES = {
     "rvllm_paged_decode_quant_workspace_size": (_u64, [_i32, _i32, _i32, _i32]),
     "rvllm_paged_decode_fp8_quant": (_i32, [_vp] * 5 + [_i32] + [_vp] * 3 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_paged_decode_fp8": (_i32, [_vp] * 4 + [_i32] + [_vp] * 3 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
+    "rvllm_paged_decode_static_scratch_bytes": (_sz, []),
+    "rvllm_paged_decode_fp8_static_scratch": (_i32, [_vp] * 4 + [_i32] + [_vp] * 2 + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_rope_fp8kv_launch": (_i32, [_vp, _vp, _vp, _i32] + [_vp] * 10 + [_i32] * 8 + [_vp]),
     "rvllm_embedding_gather_launch": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "rvllm_e4m3_encode_f32": (_i32, [_vp, _vp, _sz, _vp]),

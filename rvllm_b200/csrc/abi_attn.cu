@@ -3,6 +3,8 @@
 #include <math.h>
 
 #include "../../include/rvllm_b200.h"
+#include <mutex>
+
 #include "host_util.h"
 #include "paged_decode_fp8_mma.cuh"
 
@@ -228,6 +230,72 @@ int rvllm_paged_decode_fp8_quant(const void* q_fp8, const void* k_cache_fp8, con
     return decode_core(qo, q_fp8, k_cache_fp8, v_cache_fp8, nullptr, round_dtype, block_tables, context_lens, workspace,
                        workspace_bytes, k_scale_cache, v_scale_cache, q_scale_cache, q_descale, k_descale, v_descale,
                        scale, batch_size, num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                       num_blocks_total, window_size_left, stream);
+}
+
+// ---- decode attention for callers that cannot allocate ---------------------------------------
+// The split-KV partials normally live in a workspace the caller allocates.  Some callers have no
+// allocator to ask: a runtime that carved all of its device memory into fixed regions at start-up
+// and has nothing left over, or a plug-in whose host forbids it to call the CUDA allocator
+// (an allocation can synchronise the device and stall every other stream).  For them the
+// partials go into a scratch array that is part of this library's device image.
+constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;  // every GPU that loads the library holds these 8 MiB
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+// Device address of g_static_scratch per device ordinal.  In host code the array's name is only
+// a handle for the runtime, never an address a kernel may use; cudaGetSymbolAddress translates it
+// for the device that is current.
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_addr[MAX_DEVICES] = {nullptr};
+std::mutex g_scratch_mu;
+
+int static_scratch_ptr(float** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        cudaGetLastError();
+        return rv_fail(RVLLM_E_NO_DEVICE, "no current CUDA device (or ordinal above %d)", MAX_DEVICES - 1);
+    }
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    if (!g_scratch_addr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return rv_fail(RVLLM_E_LAUNCH, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        }
+        g_scratch_addr[dev] = (float*)p;
+    }
+    *out = g_scratch_addr[dev];
+    return RVLLM_OK;
+}
+}  // namespace
+
+size_t rvllm_paged_decode_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
+
+int rvllm_paged_decode_fp8_static_scratch(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8,
+                                          void* output, int out_dtype, const int32_t* block_tables,
+                                          const int32_t* context_lens, const float* k_scale_cache,
+                                          const float* v_scale_cache, const float* q_scale_cache,
+                                          const float* q_descale, const float* k_descale, const float* v_descale,
+                                          float scale, int batch_size, int num_heads, int num_kv_heads, int head_dim,
+                                          int block_size, int max_blocks_per_seq, int num_blocks_total,
+                                          int window_size_left, void* stream) {
+    const uint64_t need = rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim);
+    if (need == UINT64_MAX) return rv_fail(RVLLM_E_INVALID, "shape rejected by the workspace query");
+    if (need > STATIC_SCRATCH_BYTES)
+        return rv_fail(RVLLM_E_WORKSPACE,
+                       "this launch needs %llu bytes of split-KV scratch but the built-in scratch holds %llu; use "
+                       "rvllm_paged_decode_fp8 with a caller-allocated workspace",
+                       (unsigned long long)need, (unsigned long long)STATIC_SCRATCH_BYTES);
+    float* scratch = nullptr;
+    int rc = static_scratch_ptr(&scratch);  // first call on a device resolves the address
+    if (rc) return rc;
+    // Nothing in the scratch has to start at zero: every partial a launch reads back was written by
+    // that same launch, so the previous call's contents are simply overwritten.
+    return decode_core(QuantOut(), q_fp8, k_cache_fp8, v_cache_fp8, output, out_dtype, block_tables, context_lens,
+                       scratch, STATIC_SCRATCH_BYTES, k_scale_cache, v_scale_cache, q_scale_cache, q_descale, k_descale,
+                       v_descale, scale, batch_size, num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
                        num_blocks_total, window_size_left, stream);
 }
 
