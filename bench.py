@@ -352,12 +352,9 @@ def run_gpu_arm(args, cfg):
     B = args.batch
     main = run_batch(torch, cfg, weights, B, args.steps, args.warmup, args.e2e_steps, ClockSampler(local), barrier,
                      profiler_range=args.profiler_range, seeded=args.seeded_context)
-    sec = torch.tensor([main["seconds"]], dtype=torch.float64, device="cuda")
-    e2e_ms = torch.tensor([main["e2e"]["ms_per_step"] if "e2e" in main else 0.0], dtype=torch.float64, device="cuda")
-    if dist:
-        dist.all_reduce(sec, op=dist.ReduceOp.MAX)
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    sec = float(sec.item())
+    from rvllm_b200 import replicas
+    sec = replicas.job_seconds(dist, main["seconds"], device="cuda")            # slowest replica
+    e2e_ms_max = replicas.job_seconds(dist, main["e2e"]["ms_per_step"] if "e2e" in main else 0.0, device="cuda")
     value = world * B * args.steps / sec
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -369,8 +366,8 @@ def run_gpu_arm(args, cfg):
     }
     if "e2e" in main:
         e = dict(main["e2e"])
-        e["value"] = world * B / (float(e2e_ms.item()) / 1e3)
-        e["ms_per_step"] = float(e2e_ms.item())
+        e["value"] = world * B / (e2e_ms_max / 1e3)
+        e["ms_per_step"] = e2e_ms_max
         line["e2e"] = e
     step_frac = main["step_bytes"] / (main["seconds"] / args.steps) / 1e9 / peak
     line["step_roofline"] = {"algorithmic_bytes_per_step": main["step_bytes"], "context": main["context_mid"],
