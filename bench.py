@@ -409,6 +409,8 @@ def main():
     ap.add_argument("--all-batches", action="store_true", help="also time batch 1 and 128")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-roofline", action="store_true")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="small case for ncu: only the dominant kernel over 4 gate|up weight matrices (0.9 GB)")
     ap.add_argument("--seeded-context", action="store_true",
                     help="profiling aid: fill the KV caches synthetically instead of running the 512 prefill steps")
     ap.add_argument("--profiler-range", action="store_true",
@@ -418,6 +420,18 @@ def main():
     need = 512 + max(args.warmup, 3) + args.steps + args.e2e_steps + 8
     cfg = gemma31b_shape(args.batch, num_layers=args.layers, gemm_impl=args.gemm_impl,
                          max_context=(need + 255) // 256 * 256, max_steps=need)
+    if args.roofline_only:
+        import torch
+        from rvllm_b200.stack import Weights, _quant_weight
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(3)
+        w = Weights()
+        for _ in range(4):
+            gw, gs = _quant_weight(2 * cfg["ffn"], cfg["hidden"], gen, 0.02)
+            w.layers.append({"gateup_w": gw, "gateup_scale": gs})
+        peak, src = measured_peaks()
+        print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
+        return
     if args.impl == "reference":
         run_reference_arm(args, cfg)
     else:

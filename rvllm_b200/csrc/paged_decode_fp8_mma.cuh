@@ -26,12 +26,15 @@ constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
 constexpr int TILE_TOK = 16;
 
-__host__ __device__ constexpr int mma_depth(int hd) { return hd <= 64 ? 6 : hd <= 128 ? 4 : hd <= 256 ? 3 : 2; }
+// tiles in flight per warp: shallow on purpose — shared memory per CTA decides how many warps an SM
+// holds, and the per-tile dependency chain (MMA -> max -> exp -> P.V) needs many warps to hide
+__host__ __device__ constexpr int mma_depth(int hd) { return hd <= 64 ? 4 : 2; }
+constexpr int MMA_TBL_MAX = 512;  // staged block-table entries per CTA (longer chunks look the table up in L2)
 __host__ __device__ constexpr int mma_stage_bytes(int hd) { return 2 * TILE_TOK * hd + 128; }
 __host__ __device__ constexpr size_t mma_smem_bytes(int hd, int gt) {
-    return (size_t)MMA_WARPS * mma_depth(hd) * mma_stage_bytes(hd) + TBL_MAX * sizeof(int) >
+    return (size_t)MMA_WARPS * mma_depth(hd) * mma_stage_bytes(hd) + MMA_TBL_MAX * sizeof(int) >
                    (size_t)MMA_WARPS * gt * (hd + 2) * sizeof(float)
-               ? (size_t)MMA_WARPS * mma_depth(hd) * mma_stage_bytes(hd) + TBL_MAX * sizeof(int)
+               ? (size_t)MMA_WARPS * mma_depth(hd) * mma_stage_bytes(hd) + MMA_TBL_MAX * sizeof(int)
                : (size_t)MMA_WARPS * gt * (hd + 2) * sizeof(float);
 }
 
@@ -47,7 +50,7 @@ __device__ __forceinline__ void st_zero16(void* smem) {
 }
 
 template <int HD, int GT, typename OutT>
-__global__ void __launch_bounds__(MMA_THREADS) paged_decode_fp8_mma_kernel(Params p) {
+__global__ void __launch_bounds__(MMA_THREADS, (GT <= 2 ? 4 : 3)) paged_decode_fp8_mma_kernel(Params p) {
     static_assert(GT <= 8, "at most 8 query heads per tile (the MMA's column count)");
     constexpr int CH = HD / 64;          // 64-byte chunks per K row
     constexpr int LPR = HD / 16;         // lanes per V row
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(MMA_THREADS) paged_decode_fp8_mma_kernel(Param
     const int* table = p.block_tables + (size_t)b * p.max_blocks_per_seq;
     const int first_page = p.bs_shift >= 0 ? (t_begin >> p.bs_shift) : (t_begin / p.block_size);
     const int last_page = p.bs_shift >= 0 ? ((t_end - 1) >> p.bs_shift) : ((t_end - 1) / p.block_size);
-    const bool tbl_in_smem = last_page - first_page + 1 <= TBL_MAX;
+    const bool tbl_in_smem = last_page - first_page + 1 <= MMA_TBL_MAX;
     if (tbl_in_smem)
         for (int i = tid; i <= last_page - first_page; i += MMA_THREADS) {
             const int page = first_page + i;
