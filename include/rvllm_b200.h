@@ -175,9 +175,10 @@ int rvllm_paged_decode_fp8_validate(int batch_size, int num_heads, int num_kv_he
 uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim);
 int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads);
 /* Overrides for tuning runs (0 restores the default): CTAs the grid aims for, the fewest tokens
- * worth a chunk of their own, and the main-kernel variant (1 = scores on the FP32 pipes,
- * 2 = scores on the FP8 tensor cores).  Process-wide; the workspace query and the launch always
- * use the same values. */
+ * worth a chunk of their own, and the main-kernel variant (1 = both products on the FP32 pipes,
+ * 2 = scores on the FP8 tensor cores and P.V on the FP32 pipes, 3 = both products on the tensor
+ * cores; 0 picks 3 where head_dim <= 256 and the cache has fewer than 2^31 slot rows, else 2).
+ * Process-wide; the workspace query and the launch always use the same values. */
 void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant);
 int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
                            int out_dtype, const int32_t* block_tables, const int32_t* context_lens,

@@ -6,16 +6,17 @@
 #include <mutex>
 
 #include "host_util.h"
-#include "paged_decode_fp8_mma.cuh"
+#include "paged_decode_fp8_tc.cuh"
 
 static int g_target_ctas = rvattn::TARGET_CTAS;
 static int g_min_chunk_tokens = rvattn::MIN_CHUNK_TOKENS;
-static int g_variant = 0;  // 0 automatic (tensor-core scores), 1 FP32-pipe kernel, 2 tensor-core kernel
+static int g_variant = 0;  // 0 automatic (both products on tensor cores where the shape allows), 1 FP32-pipe kernel,
+                           // 2 tensor-core scores + FP32-pipe P.V, 3 both products on tensor cores
 
 extern "C" {
 
 void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant) {
-    g_variant = variant >= 0 && variant <= 2 ? variant : 0;
+    g_variant = variant >= 0 && variant <= 3 ? variant : 0;
     g_target_ctas = target_ctas > 0 ? target_ctas : rvattn::TARGET_CTAS;
     g_min_chunk_tokens = min_chunk_tokens > 0 ? min_chunk_tokens : rvattn::MIN_CHUNK_TOKENS;
 }
@@ -88,6 +89,19 @@ int launch_attn(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
             attr_set = true;
         }
         rv_launch(kern, grid, dim3(rvattn::THREADS), smem, s, dim3(1, 1, 1), p);
+    } else if (g_variant != 2 && HD <= 256 &&
+               (long long)p.num_blocks_total * p.block_size * p.kv_heads < (1ll << 31)) {
+        if constexpr (HD <= 256) {
+            auto kern = rvattn::paged_decode_fp8_tc_kernel<HD, GT, OutT>;
+            const size_t smem = rvattn::tc_smem_bytes(HD, GT);
+            static bool attr_set = false;  // per kernel instantiation
+            if (smem > 48 * 1024 && !attr_set) {
+                if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                    return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
+                attr_set = true;
+            }
+            rv_launch(kern, grid, dim3(rvattn::MMA_THREADS), smem, s, dim3(1, 1, 1), p);
+        }
     } else {
         auto kern = rvattn::paged_decode_fp8_mma_kernel<HD, GT, OutT>;
         const size_t smem = rvattn::mma_smem_bytes(HD, GT);

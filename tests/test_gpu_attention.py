@@ -21,10 +21,10 @@ from tests import ptx_harness as H  # noqa: E402
 ABS_TOL, REL_TOL = 2e-3, 1e-2
 
 
-@pytest.fixture(autouse=True, params=[2, 1], ids=["tensorcore", "fp32pipe"])
+@pytest.fixture(autouse=True, params=[3, 2, 1], ids=["tensorcore", "tcscores", "fp32pipe"])
 def kernel_variant(request):
-    """Every test runs against both main kernels: scores on the FP8 tensor cores (the default)
-    and scores on the FP32 pipes."""
+    """Every test runs against all three main kernels: both products on the tensor cores (the
+    default), scores only on the tensor cores, and everything on the FP32 pipes."""
     from rvllm_b200 import _lib
     _lib.lib().rvllm_paged_decode_tune(0, 0, request.param)
     yield request.param
