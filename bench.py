@@ -238,6 +238,11 @@ def time_steps(torch, stack, n):
     return e0.elapsed_time(e1) / 1e3
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gate|up GEMM, from the ncu capture
+# summarised in profiles/fp8_gemm_tc_gateup_m32.md, keyed by (N, K, M); other shapes were not captured
+NCU_TRAFFIC_BYTES = {(43008, 5376, 32): 235.6e6}
+
+
 def dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src):
     """The gate|up projection is the largest stream of a step (56 % of a layer's weight bytes).
     It is launched alone through the C ABI, cycling over the layers' different weight matrices
@@ -267,7 +272,8 @@ def dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src):
     achieved = algo / sec / 1e9
     return {"bound": "hbm", "kernel": "fp8 GEMM, gate|up shape [%d x %d] x M=%d" % (2 * F, H, B),
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-            "us_per_launch": sec * 1e6, "algorithmic_bytes_per_launch": algo, "traffic": None}
+            "us_per_launch": sec * 1e6, "algorithmic_bytes_per_launch": algo,
+            "traffic": NCU_TRAFFIC_BYTES.get((2 * F, H, B))}
 
 
 def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None, profiler_range=False, seeded=False):
