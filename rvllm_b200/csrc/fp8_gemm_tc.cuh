@@ -291,29 +291,81 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc_fence_before();
     }
     if (S > 1) {
-        cluster.sync();
-        const float* peer[8];
+        // This CTA finishes elements e = split*THREADS + tid (+ k * S*THREADS).  Their scales and residual
+        // values do not depend on the MMAs: fetch the first few before the cluster meets, so that their
+        // latency is not added to the end of the kernel.
+        constexpr int PRE = 4;
+        const int e_first = split * THREADS + (int)threadIdx.x, e_step = S * THREADS;
+        float pre_a[PRE], pre_w[PRE], pre_res[PRE];
 #pragma unroll
-        for (int s = 0; s < 8; s++) peer[s] = s < S ? cluster.map_shared_rank(part, s) : part;
-        for (int e = split * THREADS + threadIdx.x; e < BN * TILE_W; e += S * THREADS) {
-            const int ml = e / TILE_W, r = e % TILE_W;
-            const int m = m0 + ml, n = n0 + r;
-            float sum = 0.0f;
-#pragma unroll
-            for (int s = 0; s < 8; s++)
-                if (s < S) sum += peer[s][e];
-            if (m < p.M && n < p.N) {
-                float val = p.a_scale[m] * (p.w_scale[n] * sum);
-                const size_t o = (size_t)m * p.N + n;
-                if (EPI == EPI_F32) {
-                    reinterpret_cast<float*>(p.out)[o] = val;
-                } else {
-                    if (EPI == EPI_RESIDUAL) val += rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
-                    reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
+        for (int j = 0; j < PRE; j++) {
+            const int e = e_first + j * e_step;
+            pre_a[j] = 0.0f;
+            pre_w[j] = 0.0f;
+            pre_res[j] = 0.0f;
+            if (e < BN * TILE_W) {
+                const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
+                if (m < p.M && n < p.N) {
+                    pre_a[j] = p.a_scale[m];
+                    pre_w[j] = p.w_scale[n];
+                    if (EPI == EPI_RESIDUAL)
+                        pre_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
                 }
             }
         }
         cluster.sync();
+        const float* peer[8];
+#pragma unroll
+        for (int s = 0; s < 8; s++) peer[s] = s < S ? cluster.map_shared_rank(part, s) : part;
+        // same association as the unsplit epilogue: a_scale * (w_scale * sum)
+        auto finish = [&](int e, float sum, float as, float ws, bool have_res, float res) {
+            const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
+            if (m < p.M && n < p.N) {
+                const size_t o = (size_t)m * p.N + n;
+                float val = as * (ws * sum);
+                if (EPI == EPI_F32) {
+                    reinterpret_cast<float*>(p.out)[o] = val;
+                } else {
+                    if (EPI == EPI_RESIDUAL)
+                        val += have_res ? res : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                    reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
+                }
+            }
+        };
+        float sums[PRE];
+#pragma unroll
+        for (int j = 0; j < PRE; j++) {
+            const int e = e_first + j * e_step;
+            float sum = 0.0f;
+            if (e < BN * TILE_W) {
+#pragma unroll
+                for (int s = 0; s < 8; s++)
+                    if (s < S) sum += peer[s][e];
+            }
+            sums[j] = sum;
+        }
+        int e_rest_done = 0;
+        if (e_first + PRE * e_step >= BN * TILE_W) {
+            // every peer read of this CTA is done: let the others leave as soon as they are done too
+            asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+            e_rest_done = 1;
+        }
+#pragma unroll
+        for (int j = 0; j < PRE; j++) {
+            const int e = e_first + j * e_step;
+            if (e < BN * TILE_W) finish(e, sums[j], pre_a[j], pre_w[j], true, pre_res[j]);
+        }
+        for (int e = e_first + PRE * e_step; e < BN * TILE_W; e += e_step) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; s++)
+                if (s < S) sum += peer[s][e];
+            const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
+            const bool in = m < p.M && n < p.N;
+            finish(e, sum, in ? p.a_scale[m] : 0.0f, in ? p.w_scale[n] : 0.0f, false, 0.0f);
+        }
+        if (!e_rest_done) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
     __syncthreads();
     if (warp == 1) {
