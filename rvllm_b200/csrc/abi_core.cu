@@ -152,6 +152,20 @@ int rvllm_fused_act_mul_fp8_quant_launch(uint32_t num_tokens, uint32_t intermedi
     cudaStream_t s = (cudaStream_t)stream;
     uint8_t* o = (uint8_t*)out_fp8;
     int I = (int)intermediate;
+    // Few long rows (a decode batch): spread each row over a cluster of CTAs.  Same bytes and scales.
+    const uint32_t cl = num_tokens <= 128 ? 8u : (num_tokens <= 256 ? 4u : (num_tokens <= 512 ? 2u : 1u));
+    if (cl > 1 && intermediate >= 4096 && num_tokens <= 65535) {
+        dim3 cgrid(cl, num_tokens), cblock(rvact::CLUSTER_THREADS), cdim(cl, 1, 1);
+        if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16)
+            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_SILU, __half>, cgrid, cblock, 0, s, cdim, o, scale, (const __half*)gate_up, I);
+        else if (act == RVLLM_ACT_SILU)
+            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_SILU, __nv_bfloat16>, cgrid, cblock, 0, s, cdim, o, scale, (const __nv_bfloat16*)gate_up, I);
+        else if (dtype == RVLLM_F16)
+            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_GELU, __half>, cgrid, cblock, 0, s, cdim, o, scale, (const __half*)gate_up, I);
+        else
+            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_GELU, __nv_bfloat16>, cgrid, cblock, 0, s, cdim, o, scale, (const __nv_bfloat16*)gate_up, I);
+        return rv_launched("fused_act_mul_fp8_quant (cluster)");
+    }
     if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16)
         rv_launch(fused_silu_mul_fp8_quant_kernel, dim3(grid), dim3(block), 128, s, dim3(1, 1, 1), o, scale, (const __half*)gate_up, I);
     else if (act == RVLLM_ACT_SILU)

@@ -10,6 +10,8 @@
 // too long for that are recomputed from L2 instead of being refused.  A non-finite
 // product makes the row's scale NaN, as in the reference.
 #pragma once
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace rvact {
@@ -101,6 +103,96 @@ __device__ __forceinline__ void act_mul_quant_row(uint8_t* __restrict__ out, flo
         w.y = rv::f32x4_to_e4m3x4(y[4] * inv, y[5] * inv, y[6] * inv, y[7] * inv);
         reinterpret_cast<uint2*>(o)[v] = w;
     }
+}
+
+// The same row operation spread over a thread-block cluster: CL CTAs share one row, each owns a
+// contiguous slice of it, and the row's absmax / non-finite flag are combined through distributed
+// shared memory.  A decode batch has only a few dozen rows, so one CTA per row leaves most SMs idle
+// and the row's 2 * I values crawl through a single SM; with eight CTAs per row the kernel is a
+// short HBM/L2 burst instead.  max() is order-independent and the per-element arithmetic is the
+// one above, so bytes and scales are identical to the one-CTA-per-row kernel.
+// Geometry: grid = (CL, num_tokens), cluster = (CL, 1, 1), block = CLUSTER_THREADS.
+constexpr int CLUSTER_THREADS = 256;
+constexpr int CLUSTER_CACHE_VECS = 4;  // slices up to 4 * 256 * 8 = 8192 elements stay in registers
+
+template <int ACT, typename T>
+__global__ void __launch_bounds__(CLUSTER_THREADS)
+act_mul_quant_cluster_kernel(uint8_t* __restrict__ out, float* __restrict__ scales, const T* __restrict__ gate_up, int inter) {
+    namespace cg = cooperative_groups;
+    __shared__ float red[33];
+    __shared__ int bad;
+    __shared__ float share[2];  // this CTA's {absmax, non-finite flag}, read by its cluster peers
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank(), cl = (int)cluster.num_blocks();
+    const int row = blockIdx.y, tid = threadIdx.x;
+    rv::pdl_launch();
+    rv::pdl_wait();
+    const T* g = gate_up + (size_t)row * 2 * inter;
+    const T* u = g + inter;
+    uint8_t* o = out + (size_t)row * inter;
+    if (tid == 0) bad = 0;
+    __syncthreads();
+    const int nvec = inter >> 3;
+    const int v_lo = (int)((long long)nvec * rank / cl), v_hi = (int)((long long)nvec * (rank + 1) / cl);
+    float cache[CLUSTER_CACHE_VECS * 8];
+    float amax = 0.0f;
+    bool nonfinite = false;
+    int c = 0;
+    for (int v = v_lo + tid; v < v_hi; v += CLUSTER_THREADS, c++) {
+        float y[8];
+        mul8<ACT, T>(rv::ldg128(reinterpret_cast<const uint4*>(g) + v),
+                     rv::ldg128(reinterpret_cast<const uint4*>(u) + v), y);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            nonfinite |= !isfinite(y[j]);
+            amax = fmaxf(amax, fabsf(y[j]));
+        }
+        if (c < CLUSTER_CACHE_VECS) {
+#pragma unroll
+            for (int k = 0; k < CLUSTER_CACHE_VECS; k++)
+                if (k == c) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) cache[k * 8 + j] = y[j];
+                }
+        }
+    }
+    if (nonfinite) atomicExch(&bad, 1);
+    amax = rv::block_max(amax, red);  // barriers inside order the flag as well
+    if (tid == 0) {
+        share[0] = amax;
+        share[1] = bad ? 1.0f : 0.0f;
+    }
+    cluster.sync();
+    float row_max = 0.0f, row_bad = 0.0f;
+    for (int r = 0; r < cl; r++) {
+        const float* peer = cluster.map_shared_rank(share, r);
+        row_max = fmaxf(row_max, peer[0]);
+        row_bad = fmaxf(row_bad, peer[1]);
+    }
+    cluster.barrier_arrive();  // done with the peers' memory; they may leave once everyone has arrived
+    const float scale = row_bad != 0.0f ? CUDART_NAN_F : rv::row_scale(row_max);
+    if (rank == 0 && tid == 0) scales[row] = scale;
+    const float inv = 1.0f / scale;
+    c = 0;
+    for (int v = v_lo + tid; v < v_hi; v += CLUSTER_THREADS, c++) {
+        float y[8];
+        if (c < CLUSTER_CACHE_VECS) {
+#pragma unroll
+            for (int k = 0; k < CLUSTER_CACHE_VECS; k++)
+                if (k == c) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) y[j] = cache[k * 8 + j];
+                }
+        } else {
+            mul8<ACT, T>(rv::ldg128(reinterpret_cast<const uint4*>(g) + v),
+                         rv::ldg128(reinterpret_cast<const uint4*>(u) + v), y);
+        }
+        uint2 w;
+        w.x = rv::f32x4_to_e4m3x4(y[0] * inv, y[1] * inv, y[2] * inv, y[3] * inv);
+        w.y = rv::f32x4_to_e4m3x4(y[4] * inv, y[5] * inv, y[6] * inv, y[7] * inv);
+        reinterpret_cast<uint2*>(o)[v] = w;
+    }
+    cluster.barrier_wait();
 }
 
 }  // namespace rvact

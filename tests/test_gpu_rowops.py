@@ -229,6 +229,32 @@ def test_quantize_and_add_variant_bit_exact_vs_reference_kernel(orc):
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("dtype,suffix", [(0, "_kernel"), (1, "_bf16_kernel")])
+@pytest.mark.parametrize("act,stem,sym", [(0, "fused_silu_fp8_quant", "fused_silu_mul_fp8_quant"),
+                                          (1, "fused_gelu_mul_fp8_quant", "fused_gelu_mul_fp8_quant")])
+@pytest.mark.parametrize("tokens,inter", [(32, 21504), (3, 73728), (130, 4096), (300, 8200)])
+def test_act_mul_quant_cluster_launch_equals_one_cta_per_row(orc, dtype, suffix, act, stem, sym, tokens, inter):
+    """The C launcher spreads each row of a small batch over a cluster of CTAs; the PTX entry point
+    keeps the reference geometry of one CTA per row.  Bytes and scale bits must be identical,
+    including a row with a non-finite product (NaN scale)."""
+    from rvllm_b200.launchers import FusedActMulFp8QuantLaunch
+    gu_np = rand16(orc, (tokens, 2 * inter), dtype, 31 + inter, 2.0)
+    gu = dev16(gu_np, dtype)
+    gu[tokens - 1, inter + 5] = float("inf")
+    out_a = torch.empty((tokens, inter), dtype=torch.uint8, device="cuda")
+    scale_a = torch.empty(tokens, dtype=torch.float32, device="cuda")
+    FusedActMulFp8QuantLaunch(tokens, inter, act).launch(out_a, scale_a, gu)
+    out_b = torch.empty_like(out_a)
+    scale_b = torch.empty_like(scale_a)
+    H.ours(stem).launch(sym + suffix, (tokens,), (min(inter - inter % 32, 1024),), 128,
+                        [H.P(out_b), H.P(scale_b), H.P(gu), H.I(inter)])
+    torch.cuda.synchronize()
+    sa, sb = scale_a.cpu().numpy(), scale_b.cpu().numpy()
+    assert np.isnan(sa[-1]) and np.isnan(sb[-1])
+    assert np.array_equal(sa[:-1].view(np.uint32), sb[:-1].view(np.uint32))
+    assert np.array_equal(out_a.cpu().numpy()[:-1], out_b.cpu().numpy()[:-1])
+
+
 @needs_ref
 @pytest.mark.parametrize("stem,sym", [("fused_silu_fp8_quant", "fused_silu_mul_fp8_quant_kernel"),
                                       ("fused_gelu_mul_fp8_quant", "fused_gelu_mul_fp8_quant_kernel")])
