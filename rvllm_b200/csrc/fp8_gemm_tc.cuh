@@ -536,10 +536,12 @@ inline Tune& tune() {
     return t;
 }
 
-// Ring depth: a shallow ring (3 stages, ~60 KB for a 32-row batch tile) lets three CTAs share an
-// SM, so one CTA's prologue / epilogue overlaps the others' streaming; measured faster than one
-// deep ring per SM on every decode shape (gate|up at M = 32: 93 % vs 58 % of the HBM peak).
-inline int pick_stages(int bn) { return bn <= 64 ? 3 : bn == 128 ? 3 : 4; }
+// Ring depth: a shallow ring lets three CTAs share an SM, so one CTA's prologue / epilogue overlaps
+// the others' streaming; measured faster than a deeper ring with fewer CTAs per SM on every decode
+// shape (gate|up at M = 32: 93 % vs 58 % of the HBM peak with 3 vs 8 stages; at M = 128: 77 % vs
+// 56 % with 2 vs 3 stages).  ~60-66 KB per CTA either way: 3 stages of 20-24 KB up to a 64-row batch
+// tile, 2 stages of 32 KB for a 128-row one.
+inline int pick_stages(int bn) { return bn <= 64 ? 3 : bn == 128 ? 2 : 4; }
 
 inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
     if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");
