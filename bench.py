@@ -276,6 +276,59 @@ def dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src):
             "traffic": NCU_TRAFFIC_BYTES.get((2 * F, H, B))}
 
 
+def attention_case(torch, cfg, B, ctx, peak, peak_src):
+    """The decode-attention kernel alone at the bench's two layer shapes (sliding: head_dim 128,
+    window 1024; global: head_dim 256), batch B, context ctx, seeded random cache bytes and shuffled
+    block tables, through the C ABI.  Cycles over enough cache copies to exceed L2; timed with CUDA
+    events on the launching stream.  A small case for ncu, and a kernel-level roofline line."""
+    from rvllm_b200.attention import PagedDecodeFp8Launcher, PagedDecodeParams
+    H, KVH, bs = cfg["heads"], cfg["kv_heads"], cfg["block_size"]
+    tdt = torch.float16 if cfg["dtype"] == 0 else torch.bfloat16
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    out = []
+    for tag, HD, window in (("sliding", cfg["sliding_head_dim"], cfg["sliding_window"] - 1),
+                            ("global", cfg["global_head_dim"], -1)):
+        att = min(ctx, window + 1) if window >= 0 else ctx
+        mb = (window + 1 + bs - 1) // bs + 1 if window >= 0 else (ctx + bs - 1) // bs + 1
+        nblk = B * mb
+        per_copy = 2 * B * att * KVH * HD
+        copies = min(6, max(2, int(300e6 // per_copy) + 1))
+        ks = [torch.randint(0, 120, (nblk, bs, KVH, HD), dtype=torch.uint8, device="cuda", generator=gen) for _ in range(copies)]
+        vs = [torch.randint(0, 120, (nblk, bs, KVH, HD), dtype=torch.uint8, device="cuda", generator=gen) for _ in range(copies)]
+        sc = torch.full((nblk * bs * KVH,), 0.01, dtype=torch.float32, device="cuda")
+        q = torch.randint(0, 120, (B, H, HD), dtype=torch.uint8, device="cuda", generator=gen)
+        qs = torch.full((B * H,), 0.01, dtype=torch.float32, device="cuda")
+        tables = torch.randperm(nblk, device="cuda", generator=gen).to(torch.int32).reshape(B, mb).contiguous()
+        ctxs = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        o = torch.empty((B, H, HD), dtype=tdt, device="cuda")
+        p = PagedDecodeParams(B, H, KVH, HD, bs, mb, nblk, HD ** -0.5, window)
+        ws = torch.empty(max(p.workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
+        la = PagedDecodeFp8Launcher(p)
+
+        def launch(i):
+            la.launch(q, ks[i % copies], vs[i % copies], o, tables, ctxs, workspace=ws, k_scale_cache=sc,
+                      v_scale_cache=sc, q_scale_cache=qs)
+        for i in range(4):
+            launch(i)
+        torch.cuda.synchronize()
+        n = 8 * copies
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / 1e3 / n
+        algo = B * att * KVH * (2 * HD + 8)  # K and V rows plus their two f32 scales, per attended token and KV head
+        out.append({"kernel": "paged decode attention, %s layer shape (head_dim %d)" % (tag, HD), "batch": B, "context": ctx,
+                    "attended": att, "bound": "hbm", "achieved": algo / sec / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": algo / sec / 1e9 / peak, "peak_source": peak_src, "us_per_launch": sec * 1e6,
+                    "algorithmic_bytes_per_launch": algo, "max_chunks": p.max_chunks()})
+        del ks, vs
+    return out
+
+
 def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None, profiler_range=False, seeded=False):
     import numpy as np
     from rvllm_b200.stack import DecodeStack
@@ -417,6 +470,9 @@ def main():
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--roofline-only", action="store_true",
                     help="small case for ncu: only the dominant kernel over 4 gate|up weight matrices (0.9 GB)")
+    ap.add_argument("--attention-only", action="store_true",
+                    help="small case for ncu: only the decode-attention kernel at the two layer shapes")
+    ap.add_argument("--context", type=int, default=576, help="context length of --attention-only")
     ap.add_argument("--seeded-context", action="store_true",
                     help="profiling aid: fill the KV caches synthetically instead of running the 512 prefill steps")
     ap.add_argument("--profiler-range", action="store_true",
@@ -437,6 +493,11 @@ def main():
             w.layers.append({"gateup_w": gw, "gateup_scale": gs})
         peak, src = measured_peaks()
         print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
+        return
+    if args.attention_only:
+        import torch
+        peak, src = measured_peaks()
+        print(json.dumps({"attention": attention_case(torch, cfg, args.batch, args.context, peak, src)}))
         return
     if args.impl == "reference":
         run_reference_arm(args, cfg)

@@ -763,6 +763,7 @@ int orc_rope_fp8kv(const uint16_t *q_in, const uint16_t *k_in, const uint16_t *v
             for (int h = 0; h < nh; h++) {
                 const uint16_t *row = src + (size_t)t * in_stride + (size_t)h * head_dim;
                 float amax = 0.0f;
+                int invalid = 0; /* any non-finite post-RoPE value: NaN scale (fused_rope_partial_fp8kv.cu:133-137,178-198) */
                 for (int i = 0; i < hh; i++) {
                     float a = orc_h2f(row[i], dtype), b = orc_h2f(row[i + hh], dtype);
                     if (i < hr) {
@@ -774,9 +775,10 @@ int orc_rope_fp8kv(const uint16_t *q_in, const uint16_t *k_in, const uint16_t *v
                         lo[i] = a;
                         hi[i] = b;
                     }
-                    amax = fmaxf(amax, fmaxf(fabsf(lo[i]), fabsf(hi[i])));
+                    if (!isfinite(lo[i]) || !isfinite(hi[i])) invalid = 1;
+                    else amax = fmaxf(amax, fmaxf(fabsf(lo[i]), fabsf(hi[i])));
                 }
-                float sc = fmaxf(amax / FP8_MAX, 1e-12f), inv = 1.0f / sc;
+                float sc = invalid ? NAN : fmaxf(amax / FP8_MAX, 1e-12f), inv = 1.0f / sc;
                 if (pass == 0) {
                     q_scale_cache[(size_t)t * heads + h] = sc;
                     uint8_t *o = q_fp8 + ((size_t)t * heads + h) * head_dim;
@@ -796,9 +798,13 @@ int orc_rope_fp8kv(const uint16_t *q_in, const uint16_t *k_in, const uint16_t *v
                     }
                     const uint16_t *vrow = v_in + (size_t)t * in_stride + (size_t)h * head_dim;
                     float vmax = 0.0f;
-                    for (int i = 0; i < head_dim; i++)
-                        vmax = fmaxf(vmax, fabsf(orc_h2f(vrow[i], dtype)));
-                    float vs = fmaxf(vmax / FP8_MAX, 1e-12f), vinv = 1.0f / vs;
+                    int vinvalid = 0; /* same rule for V (fused_rope_partial_fp8kv.cu:192-199) */
+                    for (int i = 0; i < head_dim; i++) {
+                        float x = orc_h2f(vrow[i], dtype);
+                        if (!isfinite(x)) vinvalid = 1;
+                        else vmax = fmaxf(vmax, fabsf(x));
+                    }
+                    float vs = vinvalid ? NAN : fmaxf(vmax / FP8_MAX, 1e-12f), vinv = 1.0f / vs;
                     v_scale_cache[sidx] = vs;
                     uint8_t *vo = v_cache + sidx * head_dim;
                     for (int i = 0; i < head_dim; i++)

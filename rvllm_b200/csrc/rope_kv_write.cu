@@ -15,34 +15,17 @@
 
 namespace {
 
-template <typename T>
-__device__ __forceinline__ void rope_pair(const T* row, const T* cos_t, const T* sin_t, int pos, int tid,
-                                          int half_head, int half_rot, float& lo, float& hi) {
-    const float a = rv::T16<T>::to_f32(row[tid]), b = rv::T16<T>::to_f32(row[tid + half_head]);
-    if (tid < half_rot) {
-        const float c = rv::T16<T>::to_f32(cos_t[(size_t)pos * half_rot + tid]);
-        const float s = rv::T16<T>::to_f32(sin_t[(size_t)pos * half_rot + tid]);
-        lo = a * c - b * s;
-        hi = a * s + b * c;
-    } else {
-        lo = a;
-        hi = b;
-    }
+// |lo|, |hi| -> their max, or +inf when either is not finite (an absmax of finite values is never
+// +inf, so the reduction below carries the "any non-finite" vote in the same number)
+__device__ __forceinline__ float pair_amax(float lo, float hi) {
+    return (!isfinite(lo) || !isfinite(hi)) ? CUDART_INF_F : fmaxf(fabsf(lo), fabsf(hi));
 }
+__device__ __forceinline__ float scale_of(float amax) { return isinf(amax) ? CUDART_NAN_F : rv::row_scale(amax); }
 
-// block-wide max of a non-negative value plus an "any non-finite" vote
-__device__ __forceinline__ float pair_scale(float lo, float hi, float* red, int* flag) {
-    const bool nf = !isfinite(lo) || !isfinite(hi);
-    const float pm = nf ? 0.0f : fmaxf(fabsf(lo), fabsf(hi));
-    if (threadIdx.x == 0) *flag = 0;
-    __syncthreads();
-    if (nf) atomicExch(flag, 1);
-    const float amax = rv::block_max(pm, red);
-    const float sc = *flag ? CUDART_NAN_F : rv::row_scale(amax);
-    __syncthreads();
-    return sc;
-}
-
+// One CTA per (token, head): Q head `head` and, while head < kv_heads, K and V head `head`.  Every
+// global load is issued before the first reduction, and the three absmax reductions share one pass
+// and one barrier, so a CTA pays two dependent memory round trips (position -> cos/sin) instead of
+// one per operand.
 template <typename T>
 __device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, const T* v_in, int in_stride,
                                                 uint8_t* q_fp8, uint8_t* k_cache, uint8_t* v_cache,
@@ -51,38 +34,66 @@ __device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, co
                                                 const int* slot_mapping, int num_tokens, int heads, int kv_heads,
                                                 int head_dim, int rotary_dim, int max_positions,
                                                 int num_cache_slots) {
-    __shared__ float red[33];
-    __shared__ int flag;
+    __shared__ float red[8][3];
     rv::pdl_launch();
     rv::pdl_wait();
     const int tok = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
     const int half_head = head_dim / 2, half_rot = rotary_dim / 2;
     if (tok >= num_tokens || (int)blockDim.x != half_head || rotary_dim > head_dim || (rotary_dim & 1)) return;
     const int pos = positions[tok];
+    const int slot = slot_mapping[tok];
+    const bool do_q = head < heads;
+    const bool do_kv = head < kv_heads && slot >= 0 && slot < num_cache_slots;
+    float qa = 0.0f, qb = 0.0f, ka = 0.0f, kb = 0.0f, va = 0.0f, vb = 0.0f;
+    if (do_q) {
+        const T* row = q_in + (size_t)tok * in_stride + (size_t)head * head_dim;
+        qa = rv::T16<T>::to_f32(row[tid]);
+        qb = rv::T16<T>::to_f32(row[tid + half_head]);
+    }
+    if (do_kv) {
+        const T* krow = k_in + (size_t)tok * in_stride + (size_t)head * head_dim;
+        const T* vrow = v_in + (size_t)tok * in_stride + (size_t)head * head_dim;
+        ka = rv::T16<T>::to_f32(krow[tid]);
+        kb = rv::T16<T>::to_f32(krow[tid + half_head]);
+        va = rv::T16<T>::to_f32(vrow[tid]);
+        vb = rv::T16<T>::to_f32(vrow[tid + half_head]);
+    }
     if (pos < 0 || pos >= max_positions) return;
-
-    if (head < heads) {
-        float lo, hi;
-        rope_pair<T>(q_in + (size_t)tok * in_stride + (size_t)head * head_dim, cos_t, sin_t, pos, tid, half_head,
-                     half_rot, lo, hi);
-        const float sc = pair_scale(lo, hi, red, &flag);
+    float qlo = qa, qhi = qb, klo = ka, khi = kb;
+    if (tid < half_rot) {
+        const float c = rv::T16<T>::to_f32(cos_t[(size_t)pos * half_rot + tid]);
+        const float s = rv::T16<T>::to_f32(sin_t[(size_t)pos * half_rot + tid]);
+        qlo = qa * c - qb * s;
+        qhi = qa * s + qb * c;
+        klo = ka * c - kb * s;
+        khi = ka * s + kb * c;
+    }
+    float mq = rv::warp_max(pair_amax(qlo, qhi)), mk = rv::warp_max(pair_amax(klo, khi)),
+          mv = rv::warp_max(pair_amax(va, vb));
+    const int warp = tid >> 5, nwarps = ((int)blockDim.x + 31) >> 5;
+    if ((tid & 31) == 0) {
+        red[warp][0] = mq;
+        red[warp][1] = mk;
+        red[warp][2] = mv;
+    }
+    __syncthreads();
+    mq = mk = mv = 0.0f;
+    for (int w = 0; w < nwarps; w++) {
+        mq = fmaxf(mq, red[w][0]);
+        mk = fmaxf(mk, red[w][1]);
+        mv = fmaxf(mv, red[w][2]);
+    }
+    if (do_q) {
+        const float sc = scale_of(mq);
         if (tid == 0) q_scale_cache[(size_t)tok * heads + head] = sc;
         const float inv = 1.0f / sc;
         uint8_t* o = q_fp8 + ((size_t)tok * heads + head) * head_dim;
-        o[tid] = rv::f32_to_e4m3(lo * inv);
-        o[tid + half_head] = rv::f32_to_e4m3(hi * inv);
+        o[tid] = rv::f32_to_e4m3(qlo * inv);
+        o[tid + half_head] = rv::f32_to_e4m3(qhi * inv);
     }
-    if (head < kv_heads) {
-        const int slot = slot_mapping[tok];
-        if (slot < 0 || slot >= num_cache_slots) return;
+    if (do_kv) {
         const size_t sidx = (size_t)slot * kv_heads + head;
-        float klo, khi;
-        rope_pair<T>(k_in + (size_t)tok * in_stride + (size_t)head * head_dim, cos_t, sin_t, pos, tid, half_head,
-                     half_rot, klo, khi);
-        const float ksc = pair_scale(klo, khi, red, &flag);
-        const T* vrow = v_in + (size_t)tok * in_stride + (size_t)head * head_dim;
-        const float vlo = rv::T16<T>::to_f32(vrow[tid]), vhi = rv::T16<T>::to_f32(vrow[tid + half_head]);
-        const float vsc = pair_scale(vlo, vhi, red, &flag);
+        const float ksc = scale_of(mk), vsc = scale_of(mv);
         if (tid == 0) {
             k_scale_cache[sidx] = ksc;
             v_scale_cache[sidx] = vsc;
@@ -92,8 +103,8 @@ __device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, co
         uint8_t* vo = v_cache + sidx * head_dim;
         ko[tid] = rv::f32_to_e4m3(klo * kinv);
         ko[tid + half_head] = rv::f32_to_e4m3(khi * kinv);
-        vo[tid] = rv::f32_to_e4m3(vlo * vinv);
-        vo[tid + half_head] = rv::f32_to_e4m3(vhi * vinv);
+        vo[tid] = rv::f32_to_e4m3(va * vinv);
+        vo[tid + half_head] = rv::f32_to_e4m3(vb * vinv);
     }
 }
 

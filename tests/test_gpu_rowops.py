@@ -323,3 +323,56 @@ def test_manifest_loader_launch_raw_matches_c_abi(orc):
     with pytest.raises(RvllmError):
         mod.launch_raw("fused_rmsnorm_fp8_quant_bf16_kernel", (tokens,), (2048,), 0, [])
     mod.close()
+
+
+# --------------------------------------------------------------------------- rope + paged KV write
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(32, 16, 128, 128), (32, 16, 256, 64), (8, 4, 64, 64),
+                                                           (4, 4, 512, 128)])
+def test_rope_fp8kv_matches_oracle(orc, dtype, heads, kv_heads, head_dim, rotary):
+    """RoPE + Q quantisation + paged FP8 KV write against the CPU oracle: Q bytes and scales, and
+    the K/V cache bytes and per-slot scales, including a token whose slot is out of range (no
+    cache write), a position out of range (nothing written for that token) and a non-finite K
+    element (NaN scale for that slot and head only)."""
+    from rvllm_b200 import launchers
+    T, slots, max_pos = 6, 40, 64
+    g = np.random.default_rng(head_dim + heads + dtype)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv_f = (g.standard_normal((T, width)) * 1.5).astype(np.float32)
+    qkv_f[2, heads * head_dim + head_dim + 3] = np.inf            # K head 1 of token 2
+    qkv = orc.to_bits16(qkv_f, dtype)
+    ang = g.uniform(0, 6.28, (max_pos, rotary // 2)).astype(np.float32)
+    cos, sin = orc.to_bits16(np.cos(ang), dtype), orc.to_bits16(np.sin(ang), dtype)
+    positions = np.array([0, 5, 63, 7, 64, 9], np.int32)          # token 4: position out of range
+    slot_mapping = np.array([3, 39, 17, -1, 8, 21], np.int32)      # token 3: no cache slot
+    kc0 = g.integers(0, 255, (slots, kv_heads, head_dim), dtype=np.uint8)
+    vc0 = g.integers(0, 255, (slots, kv_heads, head_dim), dtype=np.uint8)
+    ks0 = g.uniform(0.1, 1, slots * kv_heads).astype(np.float32)
+    vs0 = g.uniform(0.1, 1, slots * kv_heads).astype(np.float32)
+    kc, vc, ks, vs = kc0.copy(), vc0.copy(), ks0.copy(), vs0.copy()
+    want_q, want_qs = orc.rope_fp8kv(qkv, heads, kv_heads, head_dim, rotary, cos, sin, positions, slot_mapping,
+                                     kc, vc, ks, vs, dtype)
+    d = lambda a: torch.from_numpy(a.copy()).cuda()
+    q8 = torch.full((T, heads, head_dim), 0xAB, dtype=torch.uint8, device="cuda")
+    qs = torch.full((T, heads), -7.0, dtype=torch.float32, device="cuda")
+    dkc, dvc, dks, dvs = d(kc0), d(vc0), d(ks0), d(vs0)
+    launchers.rope_fp8kv(dev16(qkv, dtype), heads, kv_heads, head_dim, rotary, dev16(cos, dtype), dev16(sin, dtype),
+                         d(positions), d(slot_mapping), q8, qs, dkc, dvc, dks, dvs)
+    torch.cuda.synchronize()
+    live = positions < max_pos                                     # rows the kernel may write
+    got_q, got_qs = q8.cpu().numpy(), qs.cpu().numpy()
+    assert (got_q[~live] == 0xAB).all() and (got_qs[~live] == -7.0).all()
+    np.testing.assert_array_equal(got_qs[live].view(np.uint32), want_qs[live].view(np.uint32))
+    np.testing.assert_array_equal(got_q[live], want_q[live])
+    got_k, got_v = dkc.cpu().numpy(), dvc.cpu().numpy()
+    # the row quantised with a NaN scale holds NaN codes (0x7f or 0xff: the sign of a NaN is not defined)
+    assert ((got_k[17, 1] & 0x7F) == 0x7F).all() and ((kc[17, 1] & 0x7F) == 0x7F).all()
+    got_k[17, 1] = kc[17, 1]
+    np.testing.assert_array_equal(got_k, kc)
+    np.testing.assert_array_equal(got_v, vc)
+    for got, want in ((dks, ks), (dvs, vs)):
+        got = got.cpu().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want))       # NaN payloads differ between C and CUDA
+        fin = ~np.isnan(want)
+        np.testing.assert_array_equal(got[fin].view(np.uint32), want[fin].view(np.uint32))
+    assert np.isnan(ks[17 * kv_heads + 1]) and not np.isnan(vs[17 * kv_heads + 1])
