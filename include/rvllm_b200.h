@@ -130,6 +130,10 @@ int rvllm_fp8_gemm_tc_status(int* status, int reset);
 /* Overrides of the tcgen05 kernel's automatic choices, for tuning runs: TMA ring depth
  * (2..8) and split-K factor (1..8); 0 restores the automatic choice.  Process-wide. */
 void rvllm_fp8_gemm_tc_tune(int stages, int splits);
+/* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
+ * CTA's receive buffer when the batch tile has at most 32 rows, else pulled out of the peers' rings),
+ * 1 always pull.  Both sum in cluster-rank order, so their results are bitwise equal. */
+void rvllm_fp8_gemm_tc_reduce(int mode);
 
 /* gate|up projection + act(gate)*up + per-token FP8 re-quantisation in one call
  * (reference: GEMM at layer_exec.rs:484-494 followed by FusedSiluMulFp8QuantLaunch :509).

@@ -62,6 +62,7 @@ SIGNATURES = {
     "rvllm_fp8_gemm_gateup_workspace": (_sz, [_i32, _i32, _i32]),
     "rvllm_fp8_gemm_tc_status": (_i32, [C.POINTER(_i32), _i32]),
     "rvllm_fp8_gemm_tc_tune": (None, [_i32, _i32]),
+    "rvllm_fp8_gemm_tc_reduce": (None, [_i32]),
     "rvllm_fa_sm89_abi_version": (_i32, []),
     "fa_sm89_fp8_output_dtype": (_i32, []),
     "fa_sm89_fp8_output_element_size": (_i32, []),

@@ -223,6 +223,8 @@ void rvllm_fp8_gemm_tc_tune(int stages, int splits) {
     rvtc::tune().splits = splits;
 }
 
+void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 ? 1 : 0; }
+
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {
     if (M <= 0 || I <= 0 || K <= 0) return 0;
     const size_t stage = ((size_t)M * 2 * (size_t)I * 2 + 255) & ~(size_t)255;

@@ -63,6 +63,7 @@ struct TcParams {
     int M, N, K;
     int kblocks;  // ceil(K / BK)
     int stages;   // depth of the TMA ring (2..MAX_STAGES); sets the shared-memory footprint
+    int push;     // split-K partials are pushed into the finishing CTA's receive buffer (behind the ring)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -102,6 +103,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// Cluster barrier halves and a 4-byte store into a cluster peer's shared memory.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ void st_peer_f32(uint32_t local_saddr, uint32_t rank, float v) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "st.shared::cluster.f32 [ra], %2;\n\t}" ::"r"(local_saddr), "r"(rank), "f"(v)
         : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
@@ -159,7 +170,11 @@ template <int BN> struct Cfg {
     // stages needed so that the split-K partial tile [BN][128] f32 fits in the (idle) ring
     static constexpr int MIN_STAGES = (TILE_W * BN * 4 + STAGE_BYTES - 1) / STAGE_BYTES < 2
                                           ? 2 : (TILE_W * BN * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
-    static constexpr int smem_bytes(int stages) { return 1024 /*alignment slack*/ + HEADER_BYTES + stages * STAGE_BYTES; }
+    // receive buffer of the push reduction: [S][ceil(BN / S)][TILE_W] f32, S * ceil(BN / S) <= BN + 7
+    static constexpr int RECV_BYTES = (BN + 7) * TILE_W * 4;
+    static constexpr int smem_bytes(int stages, bool push = false) {
+        return 1024 /*alignment slack*/ + HEADER_BYTES + stages * STAGE_BYTES + (push ? RECV_BYTES : 0);
+    }
 };
 
 template <int BN, int EPI, typename OutT>
@@ -197,6 +212,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    const bool push = S > 1 && p.push != 0;
+    if (push) cluster_arrive();  // "this CTA runs": peers wait for it (long since complete) before their first remote store
 
     if (warp == 0) {
         if (lane == 0) {
@@ -248,6 +265,87 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     rv::pdl_wait();  // scales and the residual come from predecessors; also keeps completion ordered
 
     // ---- epilogue ----------------------------------------------------------------------
+    if (push) {
+        // Split-K, push form.  Batch column c of the tile is finished by the CTA of cluster rank c % S.
+        // Every CTA stores its partial of column c straight into that CTA's receive buffer (slot = its
+        // own rank), the cluster meets once, and each CTA sums the S slots of its columns in rank order:
+        // one barrier, no remote loads, bitwise reproducible.  Measured ~2.5 us per launch less than
+        // pulling the partials out of the peers' rings (two barriers and a remote-load round trip).
+        float* recv = reinterpret_cast<float*>(ring + (size_t)STAGES * C::STAGE_BYTES);  // [S][LC][TILE_W]
+        const int LC = (BN + S - 1) / S;
+        constexpr int PRE = 3;
+        float pre_a[PRE], pre_w[PRE], pre_res[PRE];
+#pragma unroll
+        for (int j = 0; j < PRE; j++) {  // scales and residual of this thread's first output elements
+            const int e = (int)threadIdx.x + j * THREADS;
+            const int col = (e / TILE_W) * S + split;
+            const int m = m0 + col, n = n0 + e % TILE_W;
+            pre_a[j] = pre_w[j] = pre_res[j] = 0.0f;
+            if (e < LC * TILE_W && col < BN && m < p.M && n < p.N) {
+                pre_a[j] = p.a_scale[m];
+                pre_w[j] = p.w_scale[n];
+                if (EPI == EPI_RESIDUAL)
+                    pre_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
+            }
+        }
+        cluster_wait();  // every CTA of the cluster is running
+        if (warp >= EPI_WARP0) {
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            bool ready = true;
+            if (nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+            tc_fence_after();
+            const uint32_t slot = smem_u32(recv) + (uint32_t)((split * LC) * TILE_W + r) * 4u;  // [split][0][r]
+            uint32_t owner = 0, lc_off = 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t v[16];
+                if (nkb > 0 && ready) {
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    st_peer_f32(slot + lc_off, owner, __uint_as_float(v[j]));
+                    if (++owner == (uint32_t)S) {
+                        owner = 0;
+                        lc_off += TILE_W * 4;
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+        cluster_arrive();
+        cluster_wait();
+        auto finish = [&](int e, bool pre, float as_p, float ws_p, float res_p) {
+            const int lc = e / TILE_W, r = e % TILE_W;
+            const int col = lc * S + split;
+            const int m = m0 + col, n = n0 + r;
+            if (e >= LC * TILE_W || col >= BN || m >= p.M || n >= p.N) return;
+            float sum = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < 8; sp++)
+                if (sp < S) sum += recv[(size_t)(sp * LC + lc) * TILE_W + r];
+            const float as = pre ? as_p : p.a_scale[m];
+            const float ws = pre ? ws_p : p.w_scale[n];
+            float val = as * (ws * sum);  // same association as the unsplit epilogue
+            const size_t o = (size_t)m * p.N + n;
+            if (EPI == EPI_F32) {
+                reinterpret_cast<float*>(p.out)[o] = val;
+            } else {
+                if (EPI == EPI_RESIDUAL)
+                    val += pre ? res_p : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
+            }
+        };
+#pragma unroll
+        for (int j = 0; j < PRE; j++) finish((int)threadIdx.x + j * THREADS, true, pre_a[j], pre_w[j], pre_res[j]);
+#pragma unroll 1
+        for (int e = (int)threadIdx.x + PRE * THREADS; e < LC * TILE_W; e += THREADS) finish(e, false, 0.0f, 0.0f, 0.0f);
+    } else {
     float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32, only when S > 1
     if (warp >= EPI_WARP0) {
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32 * quarter ...
@@ -367,6 +465,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (!e_rest_done) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
+    }
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
@@ -452,6 +551,17 @@ inline bool cached_map(CUtensorMap* out, const void* base, int rows, int K, int 
     return true;
 }
 
+// Experiment hooks (0 = automatic): ring depth and split-K factor.
+struct Tune {
+    int stages = 0;
+    int splits = 0;
+    int reduce = 0;  // 1: force the pull form of the split-K reduction
+};
+inline Tune& tune() {
+    static Tune t;
+    return t;
+}
+
 template <int BN, int EPI, typename OutT>
 int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s) {
     using C = Cfg<BN>;
@@ -459,14 +569,19 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s) {
     if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || !cached_map(&ma, g.a, g.M, g.K, BN))
         return rvhost::fail_msg(-2, "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
     auto kern = fp8_gemm_tc_kernel<BN, EPI, OutT>;
-    if (stages < C::MIN_STAGES) stages = C::MIN_STAGES;
+    // Split-K with a small batch tile: push reduction (needs its receive buffer behind the ring);
+    // otherwise the partial tile is parked in the ring itself, which must be large enough for it.
+    const bool push = splits > 1 && BN <= 32 && tune().reduce != 1;
+    const int min_stages = push ? 2 : C::MIN_STAGES;
+    if (stages < min_stages) stages = min_stages;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    while (stages > C::MIN_STAGES && C::smem_bytes(stages) > 227 * 1024) stages--;
+    while (stages > min_stages && C::smem_bytes(stages, push) > 227 * 1024) stages--;
     static bool attr_set = false;  // per kernel instantiation: allow the largest ring once
     if (!attr_set) {
         int most = MAX_STAGES;
-        while (most > C::MIN_STAGES && C::smem_bytes(most) > 227 * 1024) most--;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(most)) != cudaSuccess)
+        const bool may_push = BN <= 32;  // the largest footprint this instantiation can be launched with
+        while (most > C::MIN_STAGES && C::smem_bytes(most, may_push) > 227 * 1024) most--;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(most, may_push)) != cudaSuccess)
             return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
         attr_set = true;
     }
@@ -480,10 +595,11 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s) {
     p.K = g.K;
     p.kblocks = (g.K + BK - 1) / BK;
     p.stages = stages;
+    p.push = push ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((g.N + TILE_W - 1) / TILE_W, splits, (g.M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = C::smem_bytes(stages);
+    cfg.dynamicSmemBytes = C::smem_bytes(stages, push);
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -526,22 +642,15 @@ inline int pick_splits(int M, int N, int K, int bn) {
     return s;
 }
 
-// Experiment hooks (0 = automatic): ring depth and split-K factor.
-struct Tune {
-    int stages = 0;
-    int splits = 0;
-};
-inline Tune& tune() {
-    static Tune t;
-    return t;
-}
-
 // Ring depth: a shallow ring lets three CTAs share an SM, so one CTA's prologue / epilogue overlaps
 // the others' streaming; measured faster than a deeper ring with fewer CTAs per SM on every decode
 // shape (gate|up at M = 32: 93 % vs 58 % of the HBM peak with 3 vs 8 stages; at M = 128: 77 % vs
 // 56 % with 2 vs 3 stages).  ~60-66 KB per CTA either way: 3 stages of 20-24 KB up to a 64-row batch
 // tile, 2 stages of 32 KB for a 128-row one.
-inline int pick_stages(int bn) { return bn <= 64 ? 3 : bn == 128 ? 2 : 4; }
+inline int pick_stages(int bn, int splits) {
+    if (bn <= 32 && splits > 1) return 2;  // leaves room for the push reduction's receive buffer at 3 CTAs / SM
+    return bn <= 64 ? 3 : bn == 128 ? 2 : 4;
+}
 
 inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
     if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");
@@ -550,7 +659,7 @@ inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
     const int kblocks = (g.K + BK - 1) / BK;
     if (splits > kblocks) splits = kblocks;
     if (splits > 8) splits = 8;
-    const int stages = tune().stages > 0 ? tune().stages : pick_stages(bn);
+    const int stages = tune().stages > 0 ? tune().stages : pick_stages(bn, splits);
     switch (bn) {
         case 16: return launch_epi<16>(g, splits, stages, s);
         case 32: return launch_epi<32>(g, splits, stages, s);

@@ -127,6 +127,34 @@ def test_gemm_is_deterministic_and_linear_in_scales(orc, impl):
     assert torch.equal(o3, o1 * 2.0)  # power-of-two rescaling commutes with rounding
 
 
+@pytest.mark.parametrize("M", [1, 7, 32])
+@pytest.mark.parametrize("splits", [2, 3, 5, 7, 8])
+@pytest.mark.parametrize("mode", ["scale", "residual", "f32"])
+def test_split_k_push_and_pull_reductions_are_bitwise_equal(orc, M, splits, mode):
+    """Inside a split-K cluster the partial tiles are either pushed into the finishing CTA's
+    receive buffer or pulled out of the peers' rings.  Both sum in cluster-rank order, so every
+    output bit must agree, and both must match the oracle."""
+    from rvllm_b200 import _lib
+    N, K = 1336, 2176  # ragged last weight tile (1336 = 10 * 128 + 56), 17 K blocks: uneven split ranges
+    a, a_s, w, w_s, cols, want = case(orc, M, N, K, seed=6)
+    dt = torch.float32 if mode == "f32" else torch.bfloat16
+    res = None
+    if mode == "residual":
+        res = torch.from_numpy(np.random.default_rng(8).standard_normal((M, N)).astype(np.float32)).to(dt).cuda()
+    outs = []
+    try:
+        for reduce_mode in (0, 1):
+            _lib.lib().rvllm_fp8_gemm_tc_tune(0, splits)
+            _lib.lib().rvllm_fp8_gemm_tc_reduce(reduce_mode)
+            outs.append(run(TC, a, a_s, w, w_s, dt, residual=res))
+    finally:
+        _lib.lib().rvllm_fp8_gemm_tc_tune(0, 0)
+        _lib.lib().rvllm_fp8_gemm_tc_reduce(0)
+    assert torch.equal(outs[0], outs[1])
+    ref = want + (res.float().cpu().numpy() if res is not None else 0.0)
+    close(outs[0].float().cpu().numpy(), ref)
+
+
 def test_both_families_agree(orc):
     M, N, K = 32, 8192, 5376
     a, a_s, w, w_s, cols, want = case(orc, M, N, K, seed=4, n_cols=64)
