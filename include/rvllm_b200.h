@@ -184,6 +184,10 @@ int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads);
  * cores; 0 picks 3 where head_dim <= 256 and the cache has fewer than 2^31 slot rows, else 2).
  * Process-wide; the workspace query and the launch always use the same values. */
 void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant);
+/* Variant 4 is the tcgen05 / TMA main kernel (head_dim 128 or 256, at most 8 query heads per KV
+ * head, pages of 8..128 tokens that divide 128).  Its waits on mbarriers are bounded; this reads
+ * (and optionally clears) the word that records the first wait that gave up: 0 = none. */
+int rvllm_paged_decode_tc_status(int* status, int reset);
 int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
                            int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
                            void* workspace, size_t workspace_bytes, const float* k_scale_cache,

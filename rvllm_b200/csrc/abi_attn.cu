@@ -7,6 +7,7 @@
 
 #include "host_util.h"
 #include "paged_decode_fp8_tc.cuh"
+#include "paged_decode_fp8_umma.cuh"
 
 static int g_target_ctas = rvattn::TARGET_CTAS;
 static int g_min_chunk_tokens = rvattn::MIN_CHUNK_TOKENS;
@@ -16,7 +17,7 @@ static int g_variant = 0;  // 0 automatic (both products on tensor cores where t
 extern "C" {
 
 void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant) {
-    g_variant = variant >= 0 && variant <= 3 ? variant : 0;
+    g_variant = variant >= 0 && variant <= 4 ? variant : 0;
     g_target_ctas = target_ctas > 0 ? target_ctas : rvattn::TARGET_CTAS;
     g_min_chunk_tokens = min_chunk_tokens > 0 ? min_chunk_tokens : rvattn::MIN_CHUNK_TOKENS;
 }
@@ -60,6 +61,11 @@ uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int nu
     return v * (unsigned long long)chunks * (unsigned long long)(head_dim + 2) * sizeof(float);
 }
 
+int rvllm_paged_decode_tc_status(int* status, int reset) {
+    if (!status) return rv_fail(RVLLM_E_INVALID, "null status pointer");
+    return rvua::read_status(status, reset != 0) ? rv_fail(RVLLM_E_LAUNCH, "cannot read the attention status word") : RVLLM_OK;
+}
+
 uint64_t rvllm_paged_decode_quant_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim) {
     if (rvllm_paged_decode_workspace_size(batch_size, num_heads, num_kv_heads, head_dim) == UINT64_MAX) return UINT64_MAX;
     const int chunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_target_ctas);
@@ -76,10 +82,51 @@ struct QuantOut {
     float* scale = nullptr;
 };
 
+// tcgen05 / TMA main kernel (head_dim 128 or 256, up to 8 query heads per KV head)
+template <int HD, int GT, typename OutT>
+int launch_umma(const rvattn::Params& p, cudaStream_t s) {
+    if constexpr (HD == 128 || HD == 256) {
+        CUtensorMap mk, mv;
+        const long long slots = (long long)p.num_blocks_total * p.block_size;
+        if (!rvua::cache_map(&mk, p.k_cache, slots, p.kv_heads, HD, p.block_size) ||
+            !rvua::cache_map(&mv, p.v_cache, slots, p.kv_heads, HD, p.block_size))
+            return rv_fail(RVLLM_E_LAUNCH, "cuTensorMapEncodeTiled failed for the KV cache");
+        auto kern = rvua::paged_decode_fp8_umma_kernel<HD, GT, OutT>;
+        const int smem = rvua::Cfg<HD>::smem_bytes();
+        static bool attr_set = false;  // per kernel instantiation
+        if (!attr_set) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
+            attr_set = true;
+        }
+        rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)smem, s, dim3(1, 1, 1), mk, mv, p);
+        return rv_launched("paged_decode_fp8 (tcgen05)");
+    } else {
+        return rv_fail(RVLLM_E_UNSUPPORTED, "tcgen05 decode attention needs head_dim 128 or 256");
+    }
+}
+
+template <int HD, int GT, typename OutT>
+int launch_main(const rvattn::Params& p, cudaStream_t s) {
+    dim3 grid(p.kv_heads, p.max_chunks, p.batch);
+    if (g_variant == 4 && rvua::supports(p, HD)) {
+        const int group = p.heads / p.kv_heads;
+        if (group <= 1) return launch_umma<HD, 1, OutT>(p, s);
+        if (group <= 2) return launch_umma<HD, 2, OutT>(p, s);
+        if (group <= 4) return launch_umma<HD, 4, OutT>(p, s);
+        return launch_umma<HD, 8, OutT>(p, s);
+    }
+    return 1;  // not handled here
+}
+
 template <int HD, int GT, typename OutT>
 int launch_attn(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
     dim3 grid(p.kv_heads, p.max_chunks, p.batch);
-    if (g_variant == 1) {
+    int handled = launch_main<HD, GT, OutT>(p, s);
+    if (handled < 0) return handled;
+    if (handled == 0) {
+        // launched by launch_main
+    } else if (g_variant == 1) {
         auto kern = rvattn::paged_decode_fp8_kernel<HD, GT, OutT>;
         const size_t smem = rvattn::smem_bytes(HD, GT);
         static bool attr_set = false;  // per kernel instantiation

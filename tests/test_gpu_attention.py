@@ -21,14 +21,19 @@ from tests import ptx_harness as H  # noqa: E402
 ABS_TOL, REL_TOL = 2e-3, 1e-2
 
 
-@pytest.fixture(autouse=True, params=[3, 2, 1], ids=["tensorcore", "tcscores", "fp32pipe"])
+@pytest.fixture(autouse=True, params=[4, 3, 2, 1], ids=["tcgen05", "tensorcore", "tcscores", "fp32pipe"])
 def kernel_variant(request):
-    """Every test runs against all three main kernels: both products on the tensor cores (the
-    default), scores only on the tensor cores, and everything on the FP32 pipes."""
+    """Every test runs against all four main kernels: tcgen05 / TMA (falls back to the next one for
+    shapes it does not take), both products on mma.sync tensor cores, scores only on the tensor
+    cores, and everything on the FP32 pipes."""
+    import ctypes
     from rvllm_b200 import _lib
     _lib.lib().rvllm_paged_decode_tune(0, 0, request.param)
     yield request.param
     _lib.lib().rvllm_paged_decode_tune(0, 0, 0)
+    st = ctypes.c_int(0)
+    assert _lib.lib().rvllm_paged_decode_tc_status(ctypes.byref(st), 1) == 0
+    assert st.value == 0, f"a bounded wait in the tcgen05 attention kernel ran out (site {st.value >> 16})"
 
 
 def dev(x):
