@@ -473,6 +473,8 @@ def main():
     ap.add_argument("--attention-only", action="store_true",
                     help="small case for ncu: only the decode-attention kernel at the two layer shapes")
     ap.add_argument("--context", type=int, default=576, help="context length of --attention-only")
+    ap.add_argument("--attention-variant", type=int, default=0,
+                    help="decode-attention main kernel: 0 automatic, 1 FP32 pipes, 2/3 mma.sync, 4 tcgen05")
     ap.add_argument("--seeded-context", action="store_true",
                     help="profiling aid: fill the KV caches synthetically instead of running the 512 prefill steps")
     ap.add_argument("--profiler-range", action="store_true",
@@ -494,6 +496,9 @@ def main():
         peak, src = measured_peaks()
         print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
         return
+    if args.impl != "reference" and args.attention_variant != 0:
+        from rvllm_b200 import _lib
+        _lib.lib().rvllm_paged_decode_tune(0, 0, args.attention_variant)
     if args.attention_only:
         import torch
         peak, src = measured_peaks()

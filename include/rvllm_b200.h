@@ -180,8 +180,8 @@ uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int nu
 int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads);
 /* Overrides for tuning runs (0 restores the default): CTAs the grid aims for, the fewest tokens
  * worth a chunk of their own, and the main-kernel variant (1 = both products on the FP32 pipes,
- * 2 = scores on the FP8 tensor cores and P.V on the FP32 pipes, 3 = both products on the tensor
- * cores; 0 picks 3 where head_dim <= 256 and the cache has fewer than 2^31 slot rows, else 2).
+ * 2 = scores on mma.sync FP8 tensor cores and P.V on the FP32 pipes, 3 = both products on mma.sync,
+ * 4 = tcgen05 / TMEM / TMA; 0 picks 4 where the shape allows it, else 3, else 2).
  * Process-wide; the workspace query and the launch always use the same values. */
 void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant);
 /* Variant 4 is the tcgen05 / TMA main kernel (head_dim 128 or 256, at most 8 query heads per KV

@@ -11,8 +11,8 @@
 
 static int g_target_ctas = rvattn::TARGET_CTAS;
 static int g_min_chunk_tokens = rvattn::MIN_CHUNK_TOKENS;
-static int g_variant = 0;  // 0 automatic (both products on tensor cores where the shape allows), 1 FP32-pipe kernel,
-                           // 2 tensor-core scores + FP32-pipe P.V, 3 both products on tensor cores
+static int g_variant = 0;  // 0 automatic (tcgen05 kernel where the shape allows, else 3, else 2), 1 FP32-pipe kernel,
+                           // 2 mma.sync scores + FP32-pipe P.V, 3 both products on mma.sync, 4 tcgen05 / TMA
 
 extern "C" {
 
@@ -109,7 +109,7 @@ int launch_umma(const rvattn::Params& p, cudaStream_t s) {
 template <int HD, int GT, typename OutT>
 int launch_main(const rvattn::Params& p, cudaStream_t s) {
     dim3 grid(p.kv_heads, p.max_chunks, p.batch);
-    if (g_variant == 4 && rvua::supports(p, HD)) {
+    if ((g_variant == 4 || g_variant == 0) && rvua::supports(p, HD)) {
         const int group = p.heads / p.kv_heads;
         if (group <= 1) return launch_umma<HD, 1, OutT>(p, s);
         if (group <= 2) return launch_umma<HD, 2, OutT>(p, s);

@@ -233,6 +233,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
     for (int i = tid; i < (C::P_BYTES + C::Q_BYTES) / 16; i += THREADS)  // zero P and Q tiles (padding rows stay zero)
         reinterpret_cast<uint4*>(p_tile)[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();  // the zeroes must be visible to the tensor core's (async-proxy) reads
     rv::pdl_wait();
 
     // ---- sequence geometry (same rules as the other variants) ----
@@ -277,20 +278,24 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
     const int nh = group < GT ? group : GT;  // query heads of this KV head (the launcher guarantees group <= GT)
-    if (active) {
-        // Q codes of the KV head's query heads -> B operand panels (K-major, swizzled by hand)
-        for (int i = tid; i < nh * (HD / 16); i += THREADS) {
-            const int n = i / (HD / 16), c = i % (HD / 16), h = c >> 3, cc = c & 7;
-            const uint4 v = rv::ldg128(p.q + ((size_t)b * p.heads + (size_t)kvh * group + n) * HD + c * 16);
-            *reinterpret_cast<uint4*>(q_tile + h * (NQ * PANEL) + n * PANEL + ((cc ^ (n & 7)) << 4)) = v;
+    if (warp != 0) {
+        // The producer warp goes straight to its loads; the other five warps stage Q meanwhile.
+        if (active) {
+            // Q codes of the KV head's query heads -> B operand panels (K-major, swizzled by hand)
+            for (int i = tid - 32; i < nh * (HD / 16); i += THREADS - 32) {
+                const int n = i / (HD / 16), c = i % (HD / 16), h = c >> 3, cc = c & 7;
+                const uint4 v = rv::ldg128(p.q + ((size_t)b * p.heads + (size_t)kvh * group + n) * HD + c * 16);
+                *reinterpret_cast<uint4*>(q_tile + h * (NQ * PANEL) + n * PANEL + ((cc ^ (n & 7)) << 4)) = v;
+            }
         }
+        fence_proxy_async();  // P / Q tiles were written through the generic proxy; the MMAs read them through the async one
+        asm volatile("bar.sync 2, 160;" ::: "memory");
     }
-    fence_proxy_async();  // P / Q tiles were written through the generic proxy; the MMAs read them through the async one
-    __syncthreads();
 
     const int last_page_tok = active ? ((t_end - 1) / bs) * bs : 0;
-    auto phys_of = [&](int tok, bool& bad_page) -> int {  // physical block of the page holding `tok`
-        const int page = tok / bs;
+    // physical block of the page holding `tok` (integer divisions only off the common power-of-two path)
+    auto phys_of = [&](int tok, bool& bad_page) -> int {
+        const int page = p.bs_shift >= 0 ? (tok >> p.bs_shift) : tok / bs;
         const int ph = __ldg(table + (p.window_size_left >= 0 ? page % p.max_blocks_per_seq : page));
         if ((unsigned)ph >= (unsigned)p.num_blocks_total) {
             bad_page = true;
@@ -300,74 +305,104 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     };
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0 && ntiles > 0) {
-            const int ppt = TOK / bs;  // pages per tile
+        // ------------------------------------------------------------------ producer (whole warp)
+        // Lane j owns page j of every tile: one table load and one TMA per lane and panel, issued side
+        // by side, instead of one thread walking the pages (serial address arithmetic and TMA issue
+        // cost ~2 us per tile that way, more than the loads themselves).
+        if (ntiles > 0) {
+            const int ppt = TOK / bs;  // pages per tile (<= 16)
             bool alive = true, bad_page = false;
             int g = 0;
             for (int i = 0; i < ntiles && alive; i++) {
                 const int tok_tile = tile0 + i * TOK;
-                int z[16];
-#pragma unroll
-                for (int j = 0; j < 16; j++)
-                    if (j < ppt) z[j] = phys_of(min(tok_tile + j * bs, last_page_tok), bad_page) * bs;
+                int z = 0;
+                if (lane < ppt) z = phys_of(min(tok_tile + lane * bs, last_page_tok), bad_page) * bs;
 #pragma unroll 1
                 for (int u = 0; u < UPT && alive; u++, g++) {
                     const int slot = g % NUNITS, use = g / NUNITS;
-                    if (use > 0) alive = mbar_wait(empty + slot, (uint32_t)(use - 1) & 1u, 1);
+                    if (use > 0) {
+                        if (lane == 0) alive = mbar_wait(empty + slot, (uint32_t)(use - 1) & 1u, 1);
+                        alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
+                    }
                     if (!alive) break;
-                    const CUtensorMap* map = u < HALVES ? &map_k : &map_v;
-                    const int x = (u % HALVES) * PANEL;
-                    uint8_t* dst = ring + (size_t)slot * UNIT;
-                    mbar_expect_tx(full + slot, UNIT);
-#pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        if (j < ppt) tma_load_3d(dst + (size_t)j * bs * PANEL, map, x, kvh, z[j], full + slot);
+                    if (lane == 0) mbar_expect_tx(full + slot, UNIT);
+                    __syncwarp();
+                    if (lane < ppt)
+                        tma_load_3d(ring + (size_t)slot * UNIT + (size_t)lane * bs * PANEL, u < HALVES ? &map_k : &map_v,
+                                    (u % HALVES) * PANEL, kvh, z, full + slot);
                 }
             }
-            if (bad_page) atomicOr(s_bad, 0xffffffffu);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0 && ntiles > 0) {
             constexpr uint32_t idesc_qk = instr_desc(NQ, false), idesc_pv = instr_desc(NP, true);
             const uint64_t qdesc = desc_kmajor(smem_u32(q_tile)), pdesc = desc_kmajor(smem_u32(p_tile));
+            // Issue whichever product has its inputs first: the score MMA of the next tile (its K panels
+            // have landed and its TMEM buffer is free) or the second product of the oldest open tile (its P
+            // tile is written and its V panels have landed).  Waiting for one in program order would hold
+            // the other back, and with it the release of the ring units the producer is waiting for.
+            int next_qk = 0, next_pv = 0;
+            uint32_t idle = 0;
             bool alive = true;
-            auto scores = [&](int i) {  // tile i: K panels x Q panels -> score buffer i & 1
-                if (i >= 2) alive = mbar_wait(s_free + (i & 1), (uint32_t)((i >> 1) - 1) & 1u, 2);
-                for (int h = 0; h < HALVES && alive; h++) {
-                    const int g = i * UPT + h, slot = g % NUNITS;
-                    alive = mbar_wait(full + slot, (uint32_t)(g / NUNITS) & 1u, 3);
-                    if (!alive) break;
-                    tc_fence_after();
-                    const uint64_t kdesc = desc_kmajor(smem_u32(ring + (size_t)slot * UNIT));
-                    const uint64_t qd = qdesc + (uint64_t)((h * NQ * PANEL) >> 4);
+            while (next_pv < ntiles && alive) {
+                bool did = false;
+                // (at most one tile ahead of the second product: the previous occupant of tile j's K units is
+                //  tile j-2's V, consumed by PV(j-2) — looking further ahead would let a parity wait on the
+                //  unit's barrier alias with a phase that is still loading)
+                if (next_qk < ntiles && next_qk <= next_pv + 1) {
+                    const int i = next_qk;
+                    bool ok = i < 2 || mbar_try_wait(s_free + (i & 1), (uint32_t)((i >> 1) - 1) & 1u);
+                    for (int h = 0; h < HALVES && ok; h++) {
+                        const int g = i * UPT + h;
+                        ok = mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
+                    }
+                    if (ok) {
+                        tc_fence_after();
+                        for (int h = 0; h < HALVES; h++) {
+                            const int slot = (i * UPT + h) % NUNITS;
+                            const uint64_t kdesc = desc_kmajor(smem_u32(ring + (size_t)slot * UNIT));
+                            const uint64_t qd = qdesc + (uint64_t)((h * NQ * PANEL) >> 4);
 #pragma unroll
-                    for (int k = 0; k < PANEL / 32; k++)
-                        umma_f8(tmem_base + (uint32_t)(i & 1) * NQ, kdesc + (uint64_t)(2 * k), qd + (uint64_t)(2 * k), idesc_qk,
-                                (h > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(empty + slot);
+                            for (int k = 0; k < PANEL / 32; k++)
+                                umma_f8(tmem_base + (uint32_t)(i & 1) * NQ, kdesc + (uint64_t)(2 * k), qd + (uint64_t)(2 * k),
+                                        idesc_qk, (h > 0 || k > 0) ? 1u : 0u);
+                            umma_commit(empty + slot);
+                        }
+                        umma_commit(s_ready + (i & 1));
+                        next_qk++;
+                        did = true;
+                    }
                 }
-                if (alive) umma_commit(s_ready + (i & 1));
-            };
-            scores(0);
-            for (int i = 0; i < ntiles && alive; i++) {
-                if (i + 1 < ntiles) scores(i + 1);
-                if (!alive) break;
-                alive = mbar_wait(p_ready, (uint32_t)i & 1u, 4);
-                for (int h = 0; h < HALVES && alive; h++) {
-                    const int g = i * UPT + HALVES + h, slot = g % NUNITS;
-                    alive = mbar_wait(full + slot, (uint32_t)(g / NUNITS) & 1u, 5);
-                    if (!alive) break;
-                    tc_fence_after();
-                    const uint64_t vdesc = desc_mnmajor(smem_u32(ring + (size_t)slot * UNIT));
+                if (next_pv < next_qk) {
+                    const int i = next_pv;
+                    bool ok = mbar_try_wait(p_ready, (uint32_t)i & 1u);
+                    for (int h = 0; h < HALVES && ok; h++) {
+                        const int g = i * UPT + HALVES + h;
+                        ok = mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
+                    }
+                    if (ok) {
+                        tc_fence_after();
+                        for (int h = 0; h < HALVES; h++) {
+                            const int slot = (i * UPT + HALVES + h) % NUNITS;
+                            const uint64_t vdesc = desc_mnmajor(smem_u32(ring + (size_t)slot * UNIT));
 #pragma unroll
-                    for (int k = 0; k < TOK / 32; k++)  // 32 tokens (rows of 128 B) per MMA
-                        umma_f8(tmem_base + C::O_COL + (uint32_t)h * NP, vdesc + (uint64_t)((32 * PANEL * k) >> 4),
-                                pdesc + (uint64_t)(2 * k), idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(empty + slot);
+                            for (int k = 0; k < TOK / 32; k++)  // 32 tokens (rows of 128 B) per MMA
+                                umma_f8(tmem_base + C::O_COL + (uint32_t)h * NP, vdesc + (uint64_t)((32 * PANEL * k) >> 4),
+                                        pdesc + (uint64_t)(2 * k), idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+                            umma_commit(empty + slot);
+                        }
+                        umma_commit(pv_done);
+                        next_pv++;
+                        did = true;
+                    }
                 }
-                if (alive) umma_commit(pv_done);
+                if (did) {
+                    idle = 0;
+                } else if (++idle > WAIT_LIMIT) {
+                    atomicCAS(&g_status, 0, (2 << 16) | (int)(blockIdx.x & 0xffff));
+                    alive = false;
+                }
             }
         }
     } else if (ntiles > 0) {
@@ -401,9 +436,10 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
             valid = i < ntiles && tok >= t_begin && tok < t_end;
             ks = k_scalar;
             vs = v_scalar;
-            if (valid && (k_perslot || v_perslot)) {
+            if (valid) {
                 bool bad_page = false;
                 const int ph = phys_of(tok, bad_page);
+                if (bad_page) bad = 0xffffffffu;  // a table entry outside the cache poisons the whole row
                 const size_t sidx = ((size_t)ph * bs + (tok % bs)) * p.kv_heads + kvh;
                 if (k_perslot) ks = __ldg(p.k_scale_cache + sidx);
                 if (v_perslot) vs = __ldg(p.v_scale_cache + sidx);
@@ -602,7 +638,8 @@ inline bool cache_map(CUtensorMap* out, const void* base, long long slots, int k
     cuuint32_t box[3] = {(cuuint32_t)PANEL, 1u, (cuuint32_t)bs};
     cuuint32_t estr[3] = {1, 1, 1};
     if (fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+           CU_TENSOR_MAP_SWIZZLE_128B, hd <= 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, *out);
