@@ -292,7 +292,6 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         asm volatile("bar.sync 2, 160;" ::: "memory");
     }
 
-    const int last_page_tok = active ? ((t_end - 1) / bs) * bs : 0;
     // physical block of the page holding `tok` (integer divisions only off the common power-of-two path)
     auto phys_of = [&](int tok, bool& bad_page) -> int {
         const int page = p.bs_shift >= 0 ? (tok >> p.bs_shift) : tok / bs;
@@ -315,8 +314,11 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
             int g = 0;
             for (int i = 0; i < ntiles && alive; i++) {
                 const int tok_tile = tile0 + i * TOK;
+                // pages of the tile that hold attended tokens; the rest are not fetched (their rows of the
+                // unit keep stale bytes: masked in the scores, zeroed by the softmax warps for the V panels)
+                const int np = min(ppt, (t_end - tok_tile + bs - 1) / bs);
                 int z = 0;
-                if (lane < ppt) z = phys_of(min(tok_tile + lane * bs, last_page_tok), bad_page) * bs;
+                if (lane < np) z = phys_of(tok_tile + lane * bs, bad_page) * bs;
 #pragma unroll 1
                 for (int u = 0; u < UPT && alive; u++, g++) {
                     const int slot = g % NUNITS, use = g / NUNITS;
@@ -325,9 +327,9 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                         alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
                     }
                     if (!alive) break;
-                    if (lane == 0) mbar_expect_tx(full + slot, UNIT);
+                    if (lane == 0) mbar_expect_tx(full + slot, (uint32_t)(np * bs * PANEL));
                     __syncwarp();
-                    if (lane < ppt)
+                    if (lane < np)
                         tma_load_3d(ring + (size_t)slot * UNIT + (size_t)lane * bs * PANEL, u < HALVES ? &map_k : &map_v,
                                     (u % HALVES) * PANEL, kvh, z, full + slot);
                 }
