@@ -188,6 +188,9 @@ void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant)
  * head, pages of 8..128 tokens that divide 128).  Its waits on mbarriers are bounded; this reads
  * (and optionally clears) the word that records the first wait that gave up: 0 = none. */
 int rvllm_paged_decode_tc_status(int* status, int reset);
+/* Depth of the tcgen05 kernel's K/V ring in 16 KB units (2..8 for head_dim 128, 3..8 for 256);
+ * 0 restores the automatic choice.  Tuning aid, process-wide. */
+void rvllm_paged_decode_ring(int units);
 int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
                            int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
                            void* workspace, size_t workspace_bytes, const float* k_scale_cache,

@@ -11,6 +11,7 @@
 
 static int g_target_ctas = rvattn::TARGET_CTAS;
 static int g_min_chunk_tokens = rvattn::MIN_CHUNK_TOKENS;
+static int g_ring_units = 0;  // tcgen05 kernel: K/V ring depth in 16 KB units, 0 = automatic
 static int g_variant = 0;  // 0 automatic (tcgen05 kernel where the shape allows, else 3, else 2), 1 FP32-pipe kernel,
                            // 2 mma.sync scores + FP32-pipe P.V, 3 both products on mma.sync, 4 tcgen05 / TMA
 
@@ -61,6 +62,8 @@ uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int nu
     return v * (unsigned long long)chunks * (unsigned long long)(head_dim + 2) * sizeof(float);
 }
 
+void rvllm_paged_decode_ring(int units) { g_ring_units = units > 0 ? units : 0; }
+
 int rvllm_paged_decode_tc_status(int* status, int reset) {
     if (!status) return rv_fail(RVLLM_E_INVALID, "null status pointer");
     return rvua::read_status(status, reset != 0) ? rv_fail(RVLLM_E_LAUNCH, "cannot read the attention status word") : RVLLM_OK;
@@ -92,14 +95,18 @@ int launch_umma(const rvattn::Params& p, cudaStream_t s) {
             !rvua::cache_map(&mv, p.v_cache, slots, p.kv_heads, HD, p.block_size))
             return rv_fail(RVLLM_E_LAUNCH, "cuTensorMapEncodeTiled failed for the KV cache");
         auto kern = rvua::paged_decode_fp8_umma_kernel<HD, GT, OutT>;
-        const int smem = rvua::Cfg<HD>::smem_bytes();
+        using C = rvua::Cfg<HD>;
         static bool attr_set = false;  // per kernel instantiation
         if (!attr_set) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(rvua::MAX_UNITS)) != cudaSuccess)
                 return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
             attr_set = true;
         }
-        rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)smem, s, dim3(1, 1, 1), mk, mv, p);
+        int units = g_ring_units > 0 ? g_ring_units : rvua::pick_units<HD>((long long)p.kv_heads * p.max_chunks * p.batch);
+        if (units < C::MIN_UNITS) units = C::MIN_UNITS;
+        if (units > rvua::MAX_UNITS) units = rvua::MAX_UNITS;
+        rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)C::smem_bytes(units), s,
+                  dim3(1, 1, 1), mk, mv, p, units);
         return rv_launched("paged_decode_fp8 (tcgen05)");
     } else {
         return rv_fail(RVLLM_E_UNSUPPORTED, "tcgen05 decode attention needs head_dim 128 or 256");

@@ -164,16 +164,17 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool a_mn) {
     return (1u << 4) | (a_mn ? (1u << 15) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+constexpr int MAX_UNITS = 8;
 template <int HD> struct Cfg {
     static constexpr int HALVES = HD / PANEL;            // 128-byte panels per K or V tile
     static constexpr int UPT = 2 * HALVES;               // ring units per tile: K panels, then V panels
-    static constexpr int NUNITS = HALVES == 1 ? 3 : 6;   // ring depth in units
+    static constexpr int MIN_UNITS = HALVES == 1 ? 2 : 3;     // both K panels plus one more must fit
     static constexpr int TMEM_COLS = HALVES == 1 ? 64 : 128;  // scores 2 x 16, then HALVES x 32 accumulator columns
     static constexpr int O_COL = 32;
     static constexpr int P_BYTES = NP * PANEL;           // 4 KB
     static constexpr int Q_BYTES = HALVES * NQ * PANEL;  // 2 KB per panel
     static constexpr int AUX_BYTES = 1024;               // barriers, TMEM holder, reduction scratch
-    static constexpr int smem_bytes() { return 1024 + NUNITS * UNIT + P_BYTES + Q_BYTES + AUX_BYTES; }
+    static constexpr int smem_bytes(int units) { return 1024 + units * UNIT + P_BYTES + Q_BYTES + AUX_BYTES; }
 };
 
 // Three-term E4M3 expansion of x in [0, 256]: x ~= hi + mid + lo with relative error ~2^-12.
@@ -187,11 +188,13 @@ __device__ __forceinline__ void split3(float x, uint8_t& hi, uint8_t& mid, uint8
 
 template <int HD, int GT, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
-paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p) {
+paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p,
+                             int nunits) {
     static_assert(HD == 128 || HD == 256, "one or two 128-byte panels per cache row");
     static_assert(GT >= 1 && GT <= 8, "up to 8 query heads share the score tile");
     using C = Cfg<HD>;
-    constexpr int HALVES = C::HALVES, UPT = C::UPT, NUNITS = C::NUNITS;
+    constexpr int HALVES = C::HALVES, UPT = C::UPT;
+    const int NUNITS = nunits;  // ring depth in 16 KB units (sets the shared-memory footprint: CTAs per SM vs look-ahead)
     constexpr int PSTRIDE = HD + 2;
     extern __shared__ uint8_t raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -200,8 +203,8 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     uint8_t* q_tile = p_tile + C::P_BYTES;                 // HALVES x [16 rows][128 B], swizzled
     uint8_t* aux = q_tile + C::Q_BYTES;
     uint64_t* full = reinterpret_cast<uint64_t*>(aux);     // [NUNITS] TMA landed
-    uint64_t* empty = full + NUNITS;                       // [NUNITS] MMAs that read the unit are done
-    uint64_t* s_ready = empty + NUNITS;                    // [2] score tile in TMEM
+    uint64_t* empty = full + MAX_UNITS;                    // [NUNITS] MMAs that read the unit are done
+    uint64_t* s_ready = empty + MAX_UNITS;                    // [2] score tile in TMEM
     uint64_t* s_free = s_ready + 2;                        // [2] softmax has read the score tile
     uint64_t* p_ready = s_free + 2;                        // P tile written (and accumulator rescaled)
     uint64_t* pv_done = p_ready + 1;                       // the tile's second product has completed
@@ -347,17 +350,23 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
             int next_qk = 0, next_pv = 0;
             uint32_t idle = 0;
             bool alive = true;
+            // A unit's barrier may only be polled once the unit's previous occupant has been consumed here:
+            // a parity wait cannot tell "this use has landed" from "the use before last has", so polling
+            // while the previous use is still loading would report the data as present.
+            auto prev_consumed = [&](int g) {
+                g -= NUNITS;
+                if (g < 0) return true;
+                const int tile = g / UPT;
+                return g % UPT < HALVES ? tile < next_qk : tile < next_pv;
+            };
             while (next_pv < ntiles && alive) {
                 bool did = false;
-                // (at most one tile ahead of the second product: the previous occupant of tile j's K units is
-                //  tile j-2's V, consumed by PV(j-2) — looking further ahead would let a parity wait on the
-                //  unit's barrier alias with a phase that is still loading)
-                if (next_qk < ntiles && next_qk <= next_pv + 1) {
+                if (next_qk < ntiles && next_qk <= next_pv + 2) {  // the score tile in TMEM is double buffered
                     const int i = next_qk;
                     bool ok = i < 2 || mbar_try_wait(s_free + (i & 1), (uint32_t)((i >> 1) - 1) & 1u);
                     for (int h = 0; h < HALVES && ok; h++) {
                         const int g = i * UPT + h;
-                        ok = mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
+                        ok = prev_consumed(g) && mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
                     }
                     if (ok) {
                         tc_fence_after();
@@ -381,7 +390,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                     bool ok = mbar_try_wait(p_ready, (uint32_t)i & 1u);
                     for (int h = 0; h < HALVES && ok; h++) {
                         const int g = i * UPT + HALVES + h;
-                        ok = mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
+                        ok = prev_consumed(g) && mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
                     }
                     if (ok) {
                         tc_fence_after();
@@ -654,6 +663,19 @@ inline bool supports(const Params& p, int head_dim) {
     const int group = p.heads / p.kv_heads;
     return (head_dim == 128 || head_dim == 256) && group <= 8 && p.block_size >= 8 && p.block_size <= TOK &&
            TOK % p.block_size == 0 && (long long)p.num_blocks_total * p.block_size < (1ll << 31);
+}
+
+// Ring depth.  A shallow ring lets more CTAs share an SM (the footprint is 8 KB + 16 KB per unit), a
+// deep one lets a CTA run further ahead of its softmax.  Small launches are lifetime-bound: take the
+// deepest ring with which every CTA of the grid is resident at once; large ones stream: take the deep ring.
+template <int HD> inline int pick_units(long long ctas) {
+    using C = Cfg<HD>;
+    const int deep = C::HALVES == 1 ? 3 : 6;
+    for (int units = deep; units >= C::MIN_UNITS; units--) {
+        const long long per_sm = (228 * 1024) / (C::smem_bytes(units) + 1024);
+        if (per_sm * 148 >= ctas) return units;
+    }
+    return deep;
 }
 
 inline int read_status(int* out, bool reset) {
