@@ -314,7 +314,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         if (ntiles > 0) {
             const int ppt = TOK / bs;  // pages per tile (<= 16)
             bool alive = true, bad_page = false;
-            int g = 0;
+            int slot = 0, use = 0;  // ring position of the next unit (kept incrementally: NUNITS is a run-time value)
             for (int i = 0; i < ntiles && alive; i++) {
                 const int tok_tile = tile0 + i * TOK;
                 // pages of the tile that hold attended tokens; the rest are not fetched (their rows of the
@@ -323,8 +323,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 int z = 0;
                 if (lane < np) z = phys_of(tok_tile + lane * bs, bad_page) * bs;
 #pragma unroll 1
-                for (int u = 0; u < UPT && alive; u++, g++) {
-                    const int slot = g % NUNITS, use = g / NUNITS;
+                for (int u = 0; u < UPT && alive; u++) {
                     if (use > 0) {
                         if (lane == 0) alive = mbar_wait(empty + slot, (uint32_t)(use - 1) & 1u, 1);
                         alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
@@ -335,6 +334,10 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                     if (lane < np)
                         tma_load_3d(ring + (size_t)slot * UNIT + (size_t)lane * bs * PANEL, u < HALVES ? &map_k : &map_v,
                                     (u % HALVES) * PANEL, kvh, z, full + slot);
+                    if (++slot == NUNITS) {
+                        slot = 0;
+                        use++;
+                    }
                 }
             }
         }
@@ -350,6 +353,16 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
             int next_qk = 0, next_pv = 0;
             uint32_t idle = 0;
             bool alive = true;
+            // ring position (slot, use count) of the first K panel of tile next_qk and of the first V panel of
+            // tile next_pv, advanced incrementally: NUNITS is a run-time value, and this loop polls
+            int q_slot = 0, q_use = 0, v_slot = HALVES % NUNITS, v_use = HALVES / NUNITS;
+            auto advance = [&](int& slot, int& use) {
+                slot += UPT;
+                while (slot >= NUNITS) {
+                    slot -= NUNITS;
+                    use++;
+                }
+            };
             // A unit's barrier may only be polled once the unit's previous occupant has been consumed here:
             // a parity wait cannot tell "this use has landed" from "the use before last has", so polling
             // while the previous use is still loading would report the data as present.
@@ -364,47 +377,63 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 if (next_qk < ntiles && next_qk <= next_pv + 2) {  // the score tile in TMEM is double buffered
                     const int i = next_qk;
                     bool ok = i < 2 || mbar_try_wait(s_free + (i & 1), (uint32_t)((i >> 1) - 1) & 1u);
-                    for (int h = 0; h < HALVES && ok; h++) {
-                        const int g = i * UPT + h;
-                        ok = prev_consumed(g) && mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
+                    int slot[HALVES];
+#pragma unroll
+                    for (int h = 0; h < HALVES; h++) {
+                        int sl = q_slot + h, us = q_use;
+                        if (sl >= NUNITS) {
+                            sl -= NUNITS;
+                            us++;
+                        }
+                        slot[h] = sl;
+                        ok = ok && prev_consumed(i * UPT + h) && mbar_try_wait(full + sl, (uint32_t)us & 1u);
                     }
                     if (ok) {
                         tc_fence_after();
+#pragma unroll
                         for (int h = 0; h < HALVES; h++) {
-                            const int slot = (i * UPT + h) % NUNITS;
-                            const uint64_t kdesc = desc_kmajor(smem_u32(ring + (size_t)slot * UNIT));
+                            const uint64_t kdesc = desc_kmajor(smem_u32(ring + (size_t)slot[h] * UNIT));
                             const uint64_t qd = qdesc + (uint64_t)((h * NQ * PANEL) >> 4);
 #pragma unroll
                             for (int k = 0; k < PANEL / 32; k++)
                                 umma_f8(tmem_base + (uint32_t)(i & 1) * NQ, kdesc + (uint64_t)(2 * k), qd + (uint64_t)(2 * k),
                                         idesc_qk, (h > 0 || k > 0) ? 1u : 0u);
-                            umma_commit(empty + slot);
+                            umma_commit(empty + slot[h]);
                         }
                         umma_commit(s_ready + (i & 1));
                         next_qk++;
+                        advance(q_slot, q_use);
                         did = true;
                     }
                 }
                 if (next_pv < next_qk) {
                     const int i = next_pv;
                     bool ok = mbar_try_wait(p_ready, (uint32_t)i & 1u);
-                    for (int h = 0; h < HALVES && ok; h++) {
-                        const int g = i * UPT + HALVES + h;
-                        ok = prev_consumed(g) && mbar_try_wait(full + g % NUNITS, (uint32_t)(g / NUNITS) & 1u);
+                    int slot[HALVES];
+#pragma unroll
+                    for (int h = 0; h < HALVES; h++) {
+                        int sl = v_slot + h, us = v_use;
+                        if (sl >= NUNITS) {
+                            sl -= NUNITS;
+                            us++;
+                        }
+                        slot[h] = sl;
+                        ok = ok && prev_consumed(i * UPT + HALVES + h) && mbar_try_wait(full + sl, (uint32_t)us & 1u);
                     }
                     if (ok) {
                         tc_fence_after();
+#pragma unroll
                         for (int h = 0; h < HALVES; h++) {
-                            const int slot = (i * UPT + HALVES + h) % NUNITS;
-                            const uint64_t vdesc = desc_mnmajor(smem_u32(ring + (size_t)slot * UNIT));
+                            const uint64_t vdesc = desc_mnmajor(smem_u32(ring + (size_t)slot[h] * UNIT));
 #pragma unroll
                             for (int k = 0; k < TOK / 32; k++)  // 32 tokens (rows of 128 B) per MMA
                                 umma_f8(tmem_base + C::O_COL + (uint32_t)h * NP, vdesc + (uint64_t)((32 * PANEL * k) >> 4),
                                         pdesc + (uint64_t)(2 * k), idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-                            umma_commit(empty + slot);
+                            umma_commit(empty + slot[h]);
                         }
                         umma_commit(pv_done);
                         next_pv++;
+                        advance(v_slot, v_use);
                         did = true;
                     }
                 }
@@ -665,17 +694,31 @@ inline bool supports(const Params& p, int head_dim) {
            TOK % p.block_size == 0 && (long long)p.num_blocks_total * p.block_size < (1ll << 31);
 }
 
-// Ring depth.  A shallow ring lets more CTAs share an SM (the footprint is 8 KB + 16 KB per unit), a
-// deep one lets a CTA run further ahead of its softmax.  Small launches are lifetime-bound: take the
-// deepest ring with which every CTA of the grid is resident at once; large ones stream: take the deep ring.
+// Ring depth.  A shallow ring lets more CTAs share an SM (the footprint is 8-10 KB + 16 KB per unit), a
+// deep one lets a CTA run further ahead of its softmax.  The choice minimises
+// ceil(CTAs / resident CTAs) x (relative time of one wave), with the per-wave weights measured on the
+// decode shapes (batch 8 / 32 / 128, contexts 576 to 4096).
 template <int HD> inline int pick_units(long long ctas) {
     using C = Cfg<HD>;
-    const int deep = C::HALVES == 1 ? 3 : 6;
-    for (int units = deep; units >= C::MIN_UNITS; units--) {
-        const long long per_sm = (228 * 1024) / (C::smem_bytes(units) + 1024);
-        if (per_sm * 148 >= ctas) return units;
+    struct Cand {
+        int units;
+        double wave;
+    };
+    static const Cand c128[] = {{2, 1.25}, {3, 1.0}, {4, 0.87}, {6, 0.74}};
+    static const Cand c256[] = {{4, 1.15}, {6, 1.0}};
+    const Cand* cand = C::HALVES == 1 ? c128 : c256;
+    const int n = C::HALVES == 1 ? 4 : 2;
+    int best = cand[0].units;
+    double best_cost = 1e300;
+    for (int i = 0; i < n; i++) {
+        const long long slots = ((228 * 1024) / (C::smem_bytes(cand[i].units) + 1024)) * 148ll;
+        const double cost = (double)((ctas + slots - 1) / slots) * cand[i].wave;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = cand[i].units;
+        }
     }
-    return deep;
+    return best;
 }
 
 inline int read_status(int* out, bool reset) {
