@@ -121,11 +121,12 @@ act_mul_quant_cluster_kernel(uint8_t* __restrict__ out, float* __restrict__ scal
     namespace cg = cooperative_groups;
     __shared__ float red[33];
     __shared__ int bad;
-    __shared__ float share[2];  // this CTA's {absmax, non-finite flag}, read by its cluster peers
+    __shared__ float share[16];  // {absmax, non-finite flag} of each of the (at most 8) CTAs of the cluster
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank(), cl = (int)cluster.num_blocks();
     const int row = blockIdx.y, tid = threadIdx.x;
     rv::pdl_launch();
+    cluster.barrier_arrive();  // "this CTA runs": awaited (long since complete) before the first store into a peer
     rv::pdl_wait();
     const T* g = gate_up + (size_t)row * 2 * inter;
     const T* u = g + inter;
@@ -158,18 +159,20 @@ act_mul_quant_cluster_kernel(uint8_t* __restrict__ out, float* __restrict__ scal
     }
     if (nonfinite) atomicExch(&bad, 1);
     amax = rv::block_max(amax, red);  // barriers inside order the flag as well
-    if (tid == 0) {
-        share[0] = amax;
-        share[1] = bad ? 1.0f : 0.0f;
+    // Every CTA stores its {absmax, flag} into slot `rank` of every peer's table and the cluster meets
+    // once (one barrier round trip instead of meet, read remotely, meet again before leaving).
+    cluster.barrier_wait();
+    if (tid < cl) {
+        float* peer = cluster.map_shared_rank(share, tid);
+        peer[2 * rank] = amax;
+        peer[2 * rank + 1] = bad ? 1.0f : 0.0f;
     }
     cluster.sync();
     float row_max = 0.0f, row_bad = 0.0f;
     for (int r = 0; r < cl; r++) {
-        const float* peer = cluster.map_shared_rank(share, r);
-        row_max = fmaxf(row_max, peer[0]);
-        row_bad = fmaxf(row_bad, peer[1]);
+        row_max = fmaxf(row_max, share[2 * r]);
+        row_bad = fmaxf(row_bad, share[2 * r + 1]);
     }
-    cluster.barrier_arrive();  // done with the peers' memory; they may leave once everyone has arrived
     const float scale = row_bad != 0.0f ? CUDART_NAN_F : rv::row_scale(row_max);
     if (rank == 0 && tid == 0) scales[row] = scale;
     const float inv = 1.0f / scale;
@@ -192,7 +195,6 @@ act_mul_quant_cluster_kernel(uint8_t* __restrict__ out, float* __restrict__ scal
         w.y = rv::f32x4_to_e4m3x4(y[4] * inv, y[5] * inv, y[6] * inv, y[7] * inv);
         reinterpret_cast<uint2*>(o)[v] = w;
     }
-    cluster.barrier_wait();
 }
 
 }  // namespace rvact
