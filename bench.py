@@ -121,36 +121,40 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm (oracle port)
-def cpu_step_sample(cfg, B, ctx, seed=0):
+def cpu_step_sample(cfg, B, ctx, seed=0, min_seconds=0.0):
     """Times the path on the host cores with the CPU oracle, on a bounded sample of one decode
     step: one sliding and one global layer's full chain (norm+quant, QKV, attention at context
     `ctx`, quant, O+residual, norm+quant, gate|up, act+quant, down+residual) at batch B, and the
-    LM head + argmax on 1/16 of the vocabulary.  Returns (estimated seconds for a whole step,
+    LM head + argmax on 1/16 of the vocabulary.  The sample is repeated (same buffers) until
+    `min_seconds` of timed work have been done.  Returns (estimated seconds for a whole step,
     seconds actually spent, description).  Random bytes stand in for weights: timing does not
     depend on values."""
     import numpy as np
     import oracle as orc
 
-    g = np.random.default_rng(seed)
     H, F, V = cfg["hidden"], cfg["ffn"], cfg["vocab"]
     dt = cfg["dtype"]
+    key = (B, ctx, cfg["num_layers"], H, F, V, dt)
+    if key in _SAMPLE_CACHE:  # the buffers of an earlier step of the same run: timing does not depend on values
+        chains, n_sliding, n_global, vs = _SAMPLE_CACHE[key]
+        return _run_sample(chains, n_sliding, n_global, V, vs, B, ctx, min_seconds)
+    g = np.random.default_rng(seed)
 
     def rbytes(*shape):
         b = g.integers(0, 256, shape, dtype=np.uint8)
         b[(b & 0x7F) == 0x7F] ^= 1
         return b
 
-    spent = {}
     n_global = sum(1 for l in range(cfg["num_layers"]) if cfg["global_every"] and (l + 1) % cfg["global_every"] == 0)
     n_sliding = cfg["num_layers"] - n_global
     resid = orc.to_bits16(g.standard_normal((B, H)).astype(np.float32), dt)
     gamma = orc.to_bits16(np.ones(H, np.float32), dt)
+    chains = {}
     for kind, is_global in (("sliding", False), ("global", True)):
         if (n_global if is_global else n_sliding) == 0:
-            spent[kind] = 0.0
             continue
         s = layer_shapes(cfg, is_global)
-        hd, q_dim, kv_dim = s["hd"], s["q_dim"], s["kv_dim"]
+        hd, q_dim = s["hd"], s["q_dim"]
         w = {name: (rbytes(N, K), np.full(N, 1e-3, np.float32)) for name, N, K, _ in s["gemms"]}
         ctx_eff = ctx if is_global else min(ctx, cfg["sliding_window"])
         bs = cfg["block_size"]
@@ -160,30 +164,53 @@ def cpu_step_sample(cfg, B, ctx, seed=0):
         ksc = np.full(nblk * bs * cfg["kv_heads"], 0.01, np.float32)
         tables = g.permutation(nblk).astype(np.int32).reshape(B, mb)
         ctxs = np.full(B, ctx_eff, np.int32)
-        t0 = time.perf_counter()
-        x8, xs = orc.rmsnorm_fp8_quant(resid, gamma, cfg["rms_eps"], dt)
-        qkv = orc.fp8_gemm(x8, w["qkv"][0], xs, w["qkv"][1], out_kind=dt)
-        q8, qs = orc.quantize_fp8_per_token(np.ascontiguousarray(qkv[:, :q_dim]).reshape(B * cfg["heads"], hd), dt)
-        att = orc.paged_decode_fp8(q8.reshape(B, cfg["heads"], hd), kc, vc, tables, ctxs, hd ** -0.5, cfg["heads"],
-                                   cfg["kv_heads"], hd, bs, k_scale_cache=ksc, v_scale_cache=ksc, q_scale_cache=qs,
-                                   dtype=dt, num_blocks_total=nblk)
-        a8, a_s = orc.quantize_fp8_per_token(att.reshape(B, q_dim), dt)
-        r2 = orc.fp8_gemm(a8, w["o"][0], a_s, w["o"][1], residual=resid, out_kind=dt)
-        x8, xs = orc.rmsnorm_fp8_quant(r2, gamma, cfg["rms_eps"], dt)
-        gu = orc.fp8_gemm(x8, w["gateup"][0], xs, w["gateup"][1], out_kind=dt)
-        h8, hs = orc.act_mul_fp8_quant(gu, cfg["act"], dt)
-        orc.fp8_gemm(h8, w["down"][0], hs, w["down"][1], residual=r2, out_kind=dt)
-        spent[kind] = time.perf_counter() - t0
+
+        def chain(w=w, hd=hd, q_dim=q_dim, kc=kc, vc=vc, ksc=ksc, tables=tables, ctxs=ctxs, bs=bs, nblk=nblk):
+            t0 = time.perf_counter()
+            x8, xs = orc.rmsnorm_fp8_quant(resid, gamma, cfg["rms_eps"], dt)
+            qkv = orc.fp8_gemm(x8, w["qkv"][0], xs, w["qkv"][1], out_kind=dt)
+            q8, qs = orc.quantize_fp8_per_token(np.ascontiguousarray(qkv[:, :q_dim]).reshape(B * cfg["heads"], hd), dt)
+            att = orc.paged_decode_fp8(q8.reshape(B, cfg["heads"], hd), kc, vc, tables, ctxs, hd ** -0.5, cfg["heads"],
+                                       cfg["kv_heads"], hd, bs, k_scale_cache=ksc, v_scale_cache=ksc, q_scale_cache=qs,
+                                       dtype=dt, num_blocks_total=nblk)
+            a8, a_s = orc.quantize_fp8_per_token(att.reshape(B, q_dim), dt)
+            r2 = orc.fp8_gemm(a8, w["o"][0], a_s, w["o"][1], residual=resid, out_kind=dt)
+            x8, xs = orc.rmsnorm_fp8_quant(r2, gamma, cfg["rms_eps"], dt)
+            gu = orc.fp8_gemm(x8, w["gateup"][0], xs, w["gateup"][1], out_kind=dt)
+            h8, hs = orc.act_mul_fp8_quant(gu, cfg["act"], dt)
+            orc.fp8_gemm(h8, w["down"][0], hs, w["down"][1], residual=r2, out_kind=dt)
+            return time.perf_counter() - t0
+        chains[kind] = chain
     vs = max(V // 16, 1)
     wl = rbytes(vs, H)
-    x8, xs = orc.rmsnorm_fp8_quant(resid, gamma, cfg["rms_eps"], dt)
-    t0 = time.perf_counter()
-    logits = orc.fp8_gemm(x8, wl, xs, np.full(vs, 1e-3, np.float32), out_kind=2)
-    orc.argmax_f32(logits)
-    spent["head"] = time.perf_counter() - t0
-    est = spent["sliding"] * n_sliding + spent["global"] * n_global + spent["head"] * (V / vs)
-    desc = (f"1 sliding + 1 global layer chain at batch {B}, context {ctx}, and LM head + argmax on 1/16 of the vocabulary; "
-            f"step time = {n_sliding} x sliding + {n_global} x global + 16 x head slice")
+    x8h, xsh = orc.rmsnorm_fp8_quant(resid, gamma, cfg["rms_eps"], dt)
+
+    def head():
+        t0 = time.perf_counter()
+        logits = orc.fp8_gemm(x8h, wl, xsh, np.full(vs, 1e-3, np.float32), out_kind=2)
+        orc.argmax_f32(logits)
+        return time.perf_counter() - t0
+    chains["head"] = head
+    _SAMPLE_CACHE[key] = (chains, n_sliding, n_global, vs)
+    return _run_sample(chains, n_sliding, n_global, V, vs, B, ctx, min_seconds)
+
+
+_SAMPLE_CACHE = {}
+
+
+def _run_sample(chains, n_sliding, n_global, V, vs, B, ctx, min_seconds):
+    spent = {k: 0.0 for k in chains}
+    passes = 0
+    while True:
+        for k, fn in chains.items():
+            spent[k] += fn()
+        passes += 1
+        if sum(spent.values()) >= min_seconds or passes >= 200:
+            break
+    mean = {k: v / passes for k, v in spent.items()}
+    est = mean.get("sliding", 0.0) * n_sliding + mean.get("global", 0.0) * n_global + mean["head"] * (V / vs)
+    desc = (f"{passes} passes over: 1 sliding + 1 global layer chain at batch {B}, context {ctx}, and LM head + argmax on "
+            f"1/16 of the vocabulary; step time = {n_sliding} x sliding + {n_global} x global + 16 x head slice")
     return est, sum(spent.values()), desc
 
 
@@ -199,8 +226,9 @@ def run_reference_arm(args, cfg):
     orc.build()
     B = args.batch
     times = []
+    per_step = max(0.3, min(4.0, 150.0 / (args.warmup + args.steps)))  # the whole run stays within a few minutes
     for i in range(args.warmup + args.steps):
-        est, spent, desc = cpu_step_sample(cfg, B, ctx=cfg["prompt_len"], seed=i)
+        est, spent, desc = cpu_step_sample(cfg, B, ctx=cfg["prompt_len"], seed=i, min_seconds=per_step)
         if i >= args.warmup:
             times.append(est)
     est = sum(times) / len(times)
@@ -438,7 +466,7 @@ def run_gpu_arm(args, cfg):
         if world == 1 and not args.no_cpu_baseline:
             import oracle as orc
             orc.build()
-            est, spent, desc = cpu_step_sample(cfg, B, ctx=cfg["prompt_len"])
+            est, spent, desc = cpu_step_sample(cfg, B, ctx=cfg["prompt_len"], min_seconds=12.0)
             line["cpu_baseline"] = {"value": B / est, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
                                     "sample": desc, "sample_seconds": spent}
         if world == 1 and args.all_batches:
