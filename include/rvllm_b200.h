@@ -188,6 +188,9 @@ void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant)
  * head, pages of 8..128 tokens that divide 128).  Its waits on mbarriers are bounded; this reads
  * (and optionally clears) the word that records the first wait that gave up: 0 = none. */
 int rvllm_paged_decode_tc_status(int* status, int reset);
+/* Which main kernel (1-4, as in rvllm_paged_decode_tune) a launch of this shape runs under the
+ * current settings; negative on bad arguments. */
+int rvllm_paged_decode_kernel_for(int num_heads, int num_kv_heads, int head_dim, int block_size, int num_blocks_total);
 /* Depth of the tcgen05 kernel's K/V ring in 16 KB units (2..8 for head_dim 128, 3..8 for 256);
  * 0 restores the automatic choice.  Tuning aid, process-wide. */
 void rvllm_paged_decode_ring(int units);

@@ -18,7 +18,7 @@ mkdir -p "$OUT"
 for f in kernels/fused_rmsnorm_fp8_quant.cu kernels/fused_silu_fp8_quant.cu kernels/argmax.cu \
          v3/kernels/fused_gelu_mul_fp8_quant.cu v3/kernels/fp8_channelscale_gemv_ktiled.cu \
          v3/kernels/fp8_channelscale_gemv_splitk.cu v3/kernels/f32_to_f16_sat.cu \
-         v3/kernels/fused_rope_partial_fp8kv.cu kernels/embedding_gather_f16.cu; do
+         v3/kernels/fused_rope_partial_fp8kv.cu kernels/embedding_gather_f16.cu kernels/flash_attention.cu; do
     stem=$(basename "$f" .cu)
     if [ ! -f "$OUT/$stem.ptx" ] || [ "$REF/$f" -nt "$OUT/$stem.ptx" ]; then
         "$NVCC" -ptx -arch=sm_100 -O3 -lineinfo -ccbin /usr/bin/g++ "$REF/$f" -o "$OUT/$stem.ptx"

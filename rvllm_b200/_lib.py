@@ -76,6 +76,7 @@ SIGNATURES = {
     "rvllm_paged_decode_tune": (None, [_i32, _i32, _i32]),
     "rvllm_paged_decode_tc_status": (_i32, [_vp, _i32]),
     "rvllm_paged_decode_ring": (None, [_i32]),
+    "rvllm_paged_decode_kernel_for": (_i32, [_i32] * 5),
     "rvllm_paged_decode_quant_workspace_size": (_u64, [_i32, _i32, _i32, _i32]),
     "rvllm_paged_decode_fp8_quant": (_i32, [_vp] * 5 + [_i32] + [_vp] * 3 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_paged_decode_fp8": (_i32, [_vp] * 4 + [_i32] + [_vp] * 3 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),

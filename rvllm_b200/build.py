@@ -36,6 +36,7 @@ PTX_MODULES = {
     "fused_gelu_mul_fp8_quant": "rowq_gelu.cu",
     "argmax": "greedy_argmax.cu",
     "embedding_gather_f16": "rope_kv_write.cu",
+    "flash_attention": "fa2_decode_fp8kv.cu",
 }
 REVISION = "b200f8e4d0c1"
 

@@ -62,6 +62,21 @@ uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int nu
     return v * (unsigned long long)chunks * (unsigned long long)(head_dim + 2) * sizeof(float);
 }
 
+int rvllm_paged_decode_kernel_for(int num_heads, int num_kv_heads, int head_dim, int block_size, int num_blocks_total) {
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return rv_fail(RVLLM_E_INVALID, "bad head counts");
+    rvattn::Params p = {};
+    p.heads = num_heads;
+    p.kv_heads = num_kv_heads;
+    p.block_size = block_size;
+    p.num_blocks_total = num_blocks_total;
+    if ((g_variant == 4 || g_variant == 0) && rvua::supports(p, head_dim)) return 4;
+    if (g_variant == 1) return 1;
+    if (g_variant != 2 && head_dim <= 256 &&
+        (long long)num_blocks_total * block_size * num_kv_heads < (1ll << 31))
+        return 3;
+    return 2;
+}
+
 void rvllm_paged_decode_ring(int units) { g_ring_units = units > 0 ? units : 0; }
 
 int rvllm_paged_decode_tc_status(int* status, int reset) {

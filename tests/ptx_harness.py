@@ -47,6 +47,12 @@ class PtxModule:
                                      f"cuModuleGetFunction({name})")
         return self._fns[name]
 
+    def set_max_dynamic_smem(self, name: str, nbytes: int) -> None:
+        """What the reference's launch_raw does before a launch that needs more than 48 KiB."""
+        _check(self._drv.cuFuncSetAttribute(self.function(name),
+                                            self._drv.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                            int(nbytes)), f"cuFuncSetAttribute({name})")
+
     def launch(self, name, grid, block, smem, args, stream=None):
         """args: list of (ctype, value); tensors are passed as (c_void_p, tensor.data_ptr())."""
         import torch
@@ -64,6 +70,10 @@ class PtxModule:
 
 def P(t):
     return (ctypes.c_void_p, t.data_ptr())
+
+
+def NULL():
+    return (ctypes.c_void_p, 0)
 
 
 def I(v):

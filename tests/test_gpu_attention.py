@@ -279,3 +279,130 @@ def test_against_reference_split_kv_kernel(orc, HD, window, bs):
     got = run_ours(c)
     assert_close(got, ref_out)
     assert_close(ref_out, run_oracle(orc, c, precise=True))  # and the oracle agrees with the reference itself
+
+
+# ---- tcgen05 / TMA kernel: the shapes it takes, beyond the grids above -----------------------------
+UMMA_SHAPES = [
+    # heads, kv_heads, head_dim, block_size, contexts, window
+    (32, 16, 128, 8, [1, 127, 128, 129, 700], -1),        # 16 pages per tile; tile-boundary contexts
+    (32, 16, 128, 32, [33, 1500, 4097], -1),
+    (16, 2, 128, 64, [64, 65, 2000], -1),                  # 8 query heads per KV head
+    (16, 4, 256, 128, [128, 129, 3000], -1),               # one page per tile, 4 query heads per KV head
+    (8, 8, 256, 16, [5, 900], -1),                         # 1 query head per KV head
+    (32, 16, 128, 16, [1024, 1025, 5000, 17], 1023),       # sliding window over a ring of pages, window start mid-page
+    (32, 16, 256, 32, [300, 40000], -1),                   # split-KV: several chunks per sequence
+    (12, 4, 128, 16, [777, 2048], 511),                    # 3 query heads per KV head (padded to 4)
+]
+
+
+@pytest.mark.parametrize("recipe", ["normal", "bytes"])
+@pytest.mark.parametrize("H_,KVH,HD,bs,ctxs,window", UMMA_SHAPES)
+def test_tcgen05_kernel_shapes(orc, kernel_variant, recipe, H_, KVH, HD, bs, ctxs, window):
+    """Page sizes 8..128, 1..8 query heads per KV head, tile-boundary contexts, ring paging and
+    split-KV on the tcgen05 kernel (the selection query must say that it is the one that runs)."""
+    from rvllm_b200 import _lib
+    if kernel_variant != 4:
+        pytest.skip("covers the tcgen05 kernel only")
+    c = datagen.attention_case(orc, len(ctxs), H_, KVH, HD, bs, ctxs, seed=99 + HD + bs, window=window, recipe=recipe)
+    assert _lib.lib().rvllm_paged_decode_kernel_for(H_, KVH, HD, bs, c["num_blocks"]) == 4
+    got = run_ours(c)
+    assert_close(got, run_oracle(orc, c, precise=True))
+
+
+def test_tcgen05_kernel_is_the_default_for_the_bench_shapes():
+    from rvllm_b200 import _lib
+    L = _lib.lib()
+    L.rvllm_paged_decode_tune(0, 0, 0)
+    assert L.rvllm_paged_decode_kernel_for(32, 16, 128, 16, 4096) == 4
+    assert L.rvllm_paged_decode_kernel_for(32, 16, 256, 16, 4096) == 4
+    assert L.rvllm_paged_decode_kernel_for(32, 16, 64, 16, 4096) == 3     # head_dim 64: mma.sync kernel
+    assert L.rvllm_paged_decode_kernel_for(32, 4, 512, 16, 4096) == 2     # head_dim 512
+    assert L.rvllm_paged_decode_kernel_for(32, 2, 128, 16, 4096) == 3     # 16 query heads per KV head
+    assert L.rvllm_paged_decode_kernel_for(32, 16, 128, 1, 4096) == 3     # one-token pages
+
+
+@pytest.mark.parametrize("units", [2, 3, 4, 6, 8])
+def test_tcgen05_ring_depths_agree(orc, kernel_variant, units):
+    """Every ring depth gives the same bytes: the depth only changes when loads are issued."""
+    from rvllm_b200 import _lib
+    if kernel_variant != 4:
+        pytest.skip("covers the tcgen05 kernel only")
+    L = _lib.lib()
+    outs = []
+    for HD in (128, 256):
+        c = datagen.attention_case(orc, 3, 32, 16, HD, 16, [1, 640, 2500], seed=5 + HD)
+        L.rvllm_paged_decode_ring(0)
+        ref = run_ours(c)
+        L.rvllm_paged_decode_ring(units)
+        try:
+            got = run_ours(c)
+        finally:
+            L.rvllm_paged_decode_ring(0)
+        assert np.array_equal(got, ref)
+
+
+# ---- PTX entry point flash_attention_2_decode_fp8kv_kernel (the name Gemma bring-up launches on sm_100) ----
+FA2_SHAPES = [(32, 16, 128, 16, [1, 300, 1500], 1023), (32, 16, 256, 16, [17, 2000], -1), (8, 8, 64, 32, [5, 700], -1),
+              (16, 4, 512, 16, [129, 1000], -1), (12, 4, 128, 8, [64, 900], 255)]
+
+
+def _fa2_launch(mod, c, out, window, kw=None):
+    """Caller-side geometry of the reference launcher: grid (num_seqs, num_heads), block 128, dynamic
+    shared memory (2*16*head_dim + 16 + 4) floats (v3/crates/rvllm-attention/src/decode.rs:572-630)."""
+    hd = c["head_dim"]
+    smem = (2 * 16 * hd + 16 + 4) * 4
+    t = {k: dev(c[k]) for k in ("q", "k", "v", "ks", "vs", "qs", "tables", "ctx")}
+    if smem > 48 * 1024:
+        mod.set_max_dynamic_smem("flash_attention_2_decode_fp8kv_kernel", smem)
+    mod.launch("flash_attention_2_decode_fp8kv_kernel", (c["batch"], c["heads"]), (128,), smem,
+               [H.P(out), H.P(t["q"]), H.P(t["k"]), H.P(t["v"]), H.P(t["ks"]), H.P(t["vs"]), H.P(t["qs"]), H.NULL(), H.NULL(),
+                H.P(t["tables"]), H.P(t["ctx"]), H.NULL(), H.F(c.get("scale", hd ** -0.5)), H.I(c["heads"]),
+                H.I(c["kv_heads"]), H.I(hd), H.I(c["block_size"]), H.I(c["max_blocks"]), H.I(window),
+                H.I(c["num_blocks"])])
+    torch.cuda.synchronize()
+    return t
+
+
+@pytest.mark.parametrize("H_,KVH,HD,bs,ctxs,window", FA2_SHAPES)
+def test_fa2_ptx_entry_matches_oracle(orc, kernel_variant, H_, KVH, HD, bs, ctxs, window):
+    if kernel_variant != 4:
+        pytest.skip("independent of the shared-object kernel variants: run once")
+    # linear block table (this entry point has no ring): max_blocks covers the whole context
+    c = datagen.attention_case(orc, len(ctxs), H_, KVH, HD, bs, ctxs, seed=7 + HD, window=-1)
+    out = torch.full((len(ctxs), H_, HD), 123.0, dtype=torch.float16, device="cuda")
+    _fa2_launch(H.ours("flash_attention"), c, out, window)
+    want = run_oracle(orc, c, precise=True, window=window)
+    assert_close(out.float().cpu().numpy(), want)
+
+
+def test_fa2_ptx_entry_leaves_bad_rows_untouched_and_poisons_bad_scales(orc, kernel_variant):
+    if kernel_variant != 4:
+        pytest.skip("independent of the shared-object kernel variants: run once")
+    c = datagen.attention_case(orc, 4, 8, 4, 128, 16, [0, 200, 300, 100], seed=3)
+    c["tables"][2, 3] = c["num_blocks"] + 5        # page outside the cache -> row untouched
+    c["ks"] = c["ks"].copy()
+    slot = int(c["tables"][3, 1]) * 16 + 2          # an attended token of sequence 3: bad K scale -> NaN row
+    c["ks"][slot * 4:(slot + 1) * 4] = -1.0
+    out = torch.full((4, 8, 128), 123.0, dtype=torch.float16, device="cuda")
+    _fa2_launch(H.ours("flash_attention"), c, out, -1)
+    got = out.float().cpu().numpy()
+    assert (got[0] == 123.0).all() and (got[2] == 123.0).all()
+    assert np.isnan(got[3]).all()
+    c_ok = dict(c)
+    want = run_oracle(orc, c_ok, precise=True)
+    assert_close(got[1:2], want[1:2])
+
+
+@pytest.mark.skipif(not H.have_reference() or not os.path.exists(os.path.join(H.REF_DIR, "flash_attention.ptx")),
+                    reason="reference kernels not compiled")
+def test_fa2_ptx_entry_against_reference_kernel(orc, kernel_variant):
+    """Same launch, same inputs: the reference's own kernel of that name and ours."""
+    if kernel_variant != 4:
+        pytest.skip("independent of the shared-object kernel variants: run once")
+    c = datagen.attention_case(orc, 3, 32, 16, 128, 16, [40, 700, 1300], seed=11)
+    outs = []
+    for mod in (H.reference("flash_attention"), H.ours("flash_attention")):
+        out = torch.full((3, 32, 128), 123.0, dtype=torch.float16, device="cuda")
+        _fa2_launch(mod, c, out, 1023)
+        outs.append(out.float().cpu().numpy())
+    assert_close(outs[1], outs[0].astype(np.float64), abs_tol=1e-3, rel_tol=5e-3)
