@@ -130,6 +130,17 @@ int rvllm_fp8_gemm_tc_status(int* status, int reset);
 /* Overrides of the tcgen05 kernel's automatic choices, for tuning runs: TMA ring depth
  * (2..8) and split-K factor (1..8); 0 restores the automatic choice.  Process-wide. */
 void rvllm_fp8_gemm_tc_tune(int stages, int splits);
+/* QKV projection with RoPE, per-(token, head) Q quantisation and the paged FP8 K/V write (per-(slot,
+ * kv_head) scales) done in the GEMM's epilogue: the result of rvllm_fp8_gemm_channelscale into a
+ * [M, (heads + 2*kv_heads)*128] 16-bit buffer followed by rvllm_rope_fp8kv_launch with rotary_dim =
+ * head_dim, bit for bit, without the buffer and without the second launch.  head_dim must be 128 (one
+ * 128-row weight tile is one head) and M <= 32; returns RVLLM_E_UNSUPPORTED for shapes it does not
+ * take (use the two calls).  dtype: the 16-bit type of the implied intermediate and of the tables. */
+int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const float* a_scale, const float* w_scale, int M,
+                                  int K, int heads, int kv_heads, int head_dim, int dtype, void* q_fp8, float* q_scale,
+                                  void* k_cache, void* v_cache, float* k_scale_cache, float* v_scale_cache,
+                                  const void* cos_table, const void* sin_table, const int32_t* positions,
+                                  const int32_t* slot_mapping, int max_positions, int num_cache_slots, void* stream);
 /* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
  * CTA's receive buffer when the batch tile has at most 32 rows, else pulled out of the peers' rings),
  * 1 always pull.  Both sum in cluster-rank order, so their results are bitwise equal. */

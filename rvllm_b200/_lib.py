@@ -63,6 +63,7 @@ SIGNATURES = {
     "rvllm_fp8_gemm_tc_status": (_i32, [C.POINTER(_i32), _i32]),
     "rvllm_fp8_gemm_tc_tune": (None, [_i32, _i32]),
     "rvllm_fp8_gemm_tc_reduce": (None, [_i32]),
+    "rvllm_fp8_gemm_qkv_rope_fp8kv": (_i32, [_vp] * 4 + [_i32] * 6 + [_vp] * 10 + [_i32] * 2 + [_vp]),
     "rvllm_fa_sm89_abi_version": (_i32, []),
     "fa_sm89_fp8_output_dtype": (_i32, []),
     "fa_sm89_fp8_output_element_size": (_i32, []),

@@ -223,6 +223,37 @@ void rvllm_fp8_gemm_tc_tune(int stages, int splits) {
     rvtc::tune().splits = splits;
 }
 
+int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const float* a_scale, const float* w_scale, int M,
+                                  int K, int heads, int kv_heads, int head_dim, int dtype, void* q_fp8, float* q_scale,
+                                  void* k_cache, void* v_cache, float* k_scale_cache, float* v_scale_cache,
+                                  const void* cos_table, const void* sin_table, const int32_t* positions,
+                                  const int32_t* slot_mapping, int max_positions, int num_cache_slots, void* stream) {
+    if (head_dim != 128) return rv_fail(RVLLM_E_UNSUPPORTED, "fused QKV epilogue: head_dim must be 128 (one weight tile per head)");
+    if (M <= 0 || K <= 0 || heads <= 0 || kv_heads <= 0 || max_positions <= 0 || num_cache_slots <= 0)
+        return rv_fail(RVLLM_E_INVALID, "M, K, heads, kv_heads, max_positions, num_cache_slots must be > 0");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    if (!a_fp8 || !w_fp8 || !a_scale || !w_scale || !q_fp8 || !q_scale || !k_cache || !v_cache || !k_scale_cache ||
+        !v_scale_cache || !cos_table || !sin_table || !positions || !slot_mapping)
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (!rv_aligned(a_fp8, 16) || !rv_aligned(w_fp8, 16)) return rv_fail(RVLLM_E_INVALID, "a / w must be 16-byte aligned");
+    rvtc::TcArgs t = {};
+    t.out = nullptr;
+    t.out_kind = dtype;
+    t.a = a_fp8;
+    t.w = w_fp8;
+    t.a_scale = a_scale;
+    t.w_scale = w_scale;
+    t.residual = nullptr;
+    t.M = M;
+    t.N = (heads + 2 * kv_heads) * 128;
+    t.K = K;
+    rvtc::RopeKv rk = {(uint8_t*)q_fp8, q_scale, (uint8_t*)k_cache, (uint8_t*)v_cache, k_scale_cache, v_scale_cache,
+                       cos_table, sin_table, positions, slot_mapping, heads, kv_heads, max_positions, num_cache_slots};
+    const int rc = rvtc::launch_qkv_rope(t, rk, dtype == RVLLM_F16 ? 0 : 1, (cudaStream_t)stream);
+    if (rc == -3) return RVLLM_E_UNSUPPORTED;  // message already recorded
+    return rc;
+}
+
 void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 ? 1 : 0; }
 
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {

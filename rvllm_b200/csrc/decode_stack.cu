@@ -272,15 +272,30 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         const int es = 2;
         RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
                                                     W.attn_norm_gamma, c.dtype, st));
-        RV_TRY(rvllm_fp8_gemm_channelscale(s->qkv, c.dtype, s->x_fp8, W.qkv_w, s->x_scale, W.qkv_scale, nullptr, B,
-                                           L.qkv_n, H, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
-        const char* qkv = (const char*)s->qkv;
-        RV_TRY(rvllm_rope_fp8kv_launch(qkv, qkv + (size_t)es * L.q_dim, qkv + (size_t)es * (L.q_dim + L.kv_dim),
-                                       L.qkv_n, s->q_fp8, L.k_cache, L.v_cache, L.k_scale, L.v_scale, s->q_scale,
-                                       L.global ? s->cos_g : s->cos_s, L.global ? s->sin_g : s->sin_s, s->positions,
-                                       L.global ? s->slots_global : s->slots_sliding, B, c.heads, c.kv_heads,
-                                       L.head_dim, L.head_dim, c.max_context, L.num_blocks * c.block_size, c.dtype,
-                                       st));
+        // QKV projection, RoPE, Q quantisation and the paged KV write: one launch where the library
+        // takes the shape (head_dim 128, batch <= 32, tensor-core GEMM), else the GEMM and the RoPE kernel
+        int fused = RVLLM_E_UNSUPPORTED;
+        if (L.head_dim == 128 && c.gemm_impl != 1)
+            fused = rvllm_fp8_gemm_qkv_rope_fp8kv(s->x_fp8, W.qkv_w, s->x_scale, W.qkv_scale, B, H, c.heads, c.kv_heads,
+                                                  L.head_dim, c.dtype, s->q_fp8, s->q_scale, L.k_cache, L.v_cache,
+                                                  L.k_scale, L.v_scale, L.global ? s->cos_g : s->cos_s,
+                                                  L.global ? s->sin_g : s->sin_s, s->positions,
+                                                  L.global ? s->slots_global : s->slots_sliding, c.max_context,
+                                                  L.num_blocks * c.block_size, st);
+        if (fused == RVLLM_E_UNSUPPORTED) {
+            RV_TRY(rvllm_fp8_gemm_channelscale(s->qkv, c.dtype, s->x_fp8, W.qkv_w, s->x_scale, W.qkv_scale, nullptr, B,
+                                               L.qkv_n, H, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
+            const char* qkv = (const char*)s->qkv;
+            RV_TRY(rvllm_rope_fp8kv_launch(qkv, qkv + (size_t)es * L.q_dim, qkv + (size_t)es * (L.q_dim + L.kv_dim),
+                                           L.qkv_n, s->q_fp8, L.k_cache, L.v_cache, L.k_scale, L.v_scale, s->q_scale,
+                                           L.global ? s->cos_g : s->cos_s, L.global ? s->sin_g : s->sin_s,
+                                           s->positions, L.global ? s->slots_global : s->slots_sliding, B, c.heads,
+                                           c.kv_heads, L.head_dim, L.head_dim, c.max_context,
+                                           L.num_blocks * c.block_size, c.dtype, st));
+            n++;
+        } else {
+            RV_TRY(fused);
+        }
         const float sm_scale = 1.0f / sqrtf((float)L.head_dim);
         const int* tables = L.global ? s->tables_global : s->tables_sliding;
         if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
@@ -307,7 +322,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         RV_TRY(rvllm_fused_act_mul_fp8_quant_launch(B, c.ffn, c.act, s->x_fp8, s->x_scale, s->gateup, c.dtype, st));
         RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.down_w, s->x_scale, W.down_scale,
                                            s->residual, B, H, c.ffn, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
-        n += 10;
+        n += 9;
     }
     RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
                                                 s->head.final_norm_gamma, c.dtype, st));

@@ -55,6 +55,21 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 __device__ int g_status = 0;  // 0 ok; otherwise (site << 16 | detail) of the first wait that gave up
 
+// Extra operands of the fused QKV epilogue (EPI_QKV_ROPE): what the RoPE + KV-write kernel takes.
+struct RopeKv {
+    uint8_t* q_fp8;          // [M, heads, 128] E4M3
+    float* q_scale;          // [M, heads]
+    uint8_t* k_cache;        // paged [slots, kv_heads, 128] E4M3
+    uint8_t* v_cache;
+    float* k_scale;          // [slots, kv_heads]
+    float* v_scale;
+    const void* cos_t;       // [max_positions, 64] in the activation type
+    const void* sin_t;
+    const int* positions;    // [M]
+    const int* slot_mapping; // [M]
+    int heads, kv_heads, max_positions, num_cache_slots;
+};
+
 struct TcParams {
     const float* a_scale;
     const float* w_scale;
@@ -64,6 +79,7 @@ struct TcParams {
     int kblocks;  // ceil(K / BK)
     int stages;   // depth of the TMA ring (2..MAX_STAGES); sets the shared-memory footprint
     int push;     // split-K partials are pushed into the finishing CTA's receive buffer (behind the ring)
+    RopeKv rope;  // EPI_QKV_ROPE only
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -159,7 +175,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
     return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
 }
 
-constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2;
+constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2, EPI_QKV_ROPE = 3;
 
 constexpr int MAX_STAGES = 8;
 constexpr int HEADER_BYTES = 1024;  // barriers + TMEM address holder, in front of the ring
@@ -320,6 +336,75 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         cluster_arrive();
         cluster_wait();
+        if constexpr (EPI == EPI_QKV_ROPE) {
+            // Fused QKV epilogue.  The weight tile is one head (128 output channels): this CTA holds, for
+            // each batch column it finishes, the whole head of one token.  Round to the activation type (the
+            // bytes the unfused GEMM would have stored), rotate (half-split pairs d, d + 64), take the head's
+            // absmax, quantise, and write Q / the paged K or V cache with their scales — the arithmetic of
+            // the RoPE + KV-write kernel (v3/kernels/fused_rope_partial_fp8kv.cu:54-214), without the 16-bit
+            // round trip through HBM and without the extra launch.  64 threads per token, 3 tokens at a time.
+            __shared__ float s_amax[3][2];
+            const RopeKv& rk = p.rope;
+            const int tile = blockIdx.x;                       // == head index over Q heads, then K heads, then V heads
+            const int kind = tile < rk.heads ? 0 : (tile < rk.heads + rk.kv_heads ? 1 : 2);
+            const int head = kind == 0 ? tile : (kind == 1 ? tile - rk.heads : tile - rk.heads - rk.kv_heads);
+            const int grp = (int)threadIdx.x >> 6, d = (int)threadIdx.x & 63;
+            const float ws_lo = p.w_scale[n0 + d], ws_hi = p.w_scale[n0 + d + 64];
+            for (int lc0 = 0; lc0 < LC; lc0 += 3) {            // uniform trip count: the barriers below are block-wide
+                const int lc = lc0 + grp;
+                const int col = lc * S + split, m = m0 + col;
+                const bool live = lc < LC && col < BN && m < p.M;
+                float lo = 0.0f, hi = 0.0f;
+                int pos = -1;
+                if (live) {
+                    float sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+                    for (int sp = 0; sp < 8; sp++)
+                        if (sp < S) {
+                            sum_lo += recv[(size_t)(sp * LC + lc) * TILE_W + d];
+                            sum_hi += recv[(size_t)(sp * LC + lc) * TILE_W + d + 64];
+                        }
+                    const float as = p.a_scale[m];
+                    const float a = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32_sat(as * (ws_lo * sum_lo)));
+                    const float b = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32_sat(as * (ws_hi * sum_hi)));
+                    pos = rk.positions[m];
+                    lo = a;
+                    hi = b;
+                    if (kind != 2 && pos >= 0 && pos < rk.max_positions) {
+                        const float c = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.cos_t)[(size_t)pos * 64 + d]);
+                        const float sn = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.sin_t)[(size_t)pos * 64 + d]);
+                        lo = a * c - b * sn;
+                        hi = a * sn + b * c;
+                    }
+                }
+                // head absmax over the group's 64 threads (+inf carries "a value was not finite")
+                float am = (!isfinite(lo) || !isfinite(hi)) ? CUDART_INF_F : fmaxf(fabsf(lo), fabsf(hi));
+                am = rv::warp_max(am);
+                if ((threadIdx.x & 31) == 0) s_amax[grp][(threadIdx.x >> 5) & 1] = am;
+                __syncthreads();
+                am = fmaxf(s_amax[grp][0], s_amax[grp][1]);
+                __syncthreads();
+                if (live && pos >= 0 && pos < rk.max_positions) {
+                    const float sc = isinf(am) ? CUDART_NAN_F : fmaxf(am / 448.0f, 1e-12f);
+                    const float inv = 1.0f / sc;
+                    if (kind == 0) {
+                        uint8_t* o = rk.q_fp8 + ((size_t)m * rk.heads + head) * TILE_W;
+                        o[d] = rv::f32_to_e4m3(lo * inv);
+                        o[d + 64] = rv::f32_to_e4m3(hi * inv);
+                        if (d == 0) rk.q_scale[(size_t)m * rk.heads + head] = sc;
+                    } else {
+                        const int slot = rk.slot_mapping[m];
+                        if (slot >= 0 && slot < rk.num_cache_slots) {
+                            const size_t sidx = (size_t)slot * rk.kv_heads + head;
+                            uint8_t* o = (kind == 1 ? rk.k_cache : rk.v_cache) + sidx * TILE_W;
+                            o[d] = rv::f32_to_e4m3(lo * inv);
+                            o[d + 64] = rv::f32_to_e4m3(hi * inv);
+                            if (d == 0) (kind == 1 ? rk.k_scale : rk.v_scale)[sidx] = sc;
+                        }
+                    }
+                }
+            }
+        } else {
         auto finish = [&](int e, bool pre, float as_p, float ws_p, float res_p) {
             const int lc = e / TILE_W, r = e % TILE_W;
             const int col = lc * S + split;
@@ -345,7 +430,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int j = 0; j < PRE; j++) finish((int)threadIdx.x + j * THREADS, true, pre_a[j], pre_w[j], pre_res[j]);
 #pragma unroll 1
         for (int e = (int)threadIdx.x + PRE * THREADS; e < LC * TILE_W; e += THREADS) finish(e, false, 0.0f, 0.0f, 0.0f);
-    } else {
+        }
+    } else if (EPI != EPI_QKV_ROPE) {  // (the fused QKV epilogue exists in the push form only; the host launches no other)
     float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32, only when S > 1
     if (warp >= EPI_WARP0) {
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32 * quarter ...
@@ -563,7 +649,7 @@ inline Tune& tune() {
 }
 
 template <int BN, int EPI, typename OutT>
-int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s) {
+int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const RopeKv* rope = nullptr) {
     using C = Cfg<BN>;
     CUtensorMap mw, ma;
     if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || !cached_map(&ma, g.a, g.M, g.K, BN))
@@ -596,6 +682,9 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s) {
     p.kblocks = (g.K + BK - 1) / BK;
     p.stages = stages;
     p.push = push ? 1 : 0;
+    p.rope = rope ? *rope : RopeKv{};
+    if (EPI == EPI_QKV_ROPE && (!push || !rope))
+        return rvhost::fail_msg(-3, "the fused QKV epilogue needs a split-K launch with a batch tile of at most 32 rows");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((g.N + TILE_W - 1) / TILE_W, splits, (g.M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
@@ -652,14 +741,25 @@ inline int pick_stages(int bn, int splits) {
     return bn <= 64 ? 3 : bn == 128 ? 2 : 4;
 }
 
+// The launch plan of a shape: batch tile, split-K factor, ring depth.
+struct Plan {
+    int bn, splits, stages, kblocks;
+};
+inline Plan plan_for(int M, int N, int K) {
+    Plan pl;
+    pl.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    pl.splits = tune().splits > 0 ? tune().splits : pick_splits(M, N, K, pl.bn);
+    pl.kblocks = (K + BK - 1) / BK;
+    if (pl.splits > pl.kblocks) pl.splits = pl.kblocks;
+    if (pl.splits > 8) pl.splits = 8;
+    pl.stages = tune().stages > 0 ? tune().stages : pick_stages(pl.bn, pl.splits);
+    return pl;
+}
+
 inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
     if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");
-    int bn = g.M <= 16 ? 16 : g.M <= 32 ? 32 : g.M <= 64 ? 64 : g.M <= 128 ? 128 : 256;
-    int splits = tune().splits > 0 ? tune().splits : pick_splits(g.M, g.N, g.K, bn);
-    const int kblocks = (g.K + BK - 1) / BK;
-    if (splits > kblocks) splits = kblocks;
-    if (splits > 8) splits = 8;
-    const int stages = tune().stages > 0 ? tune().stages : pick_stages(bn, splits);
+    const Plan pl = plan_for(g.M, g.N, g.K);
+    const int bn = pl.bn, splits = pl.splits, stages = pl.stages;
     switch (bn) {
         case 16: return launch_epi<16>(g, splits, stages, s);
         case 32: return launch_epi<32>(g, splits, stages, s);
@@ -667,6 +767,21 @@ inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
         case 128: return launch_epi<128>(g, splits, stages, s);
         default: return launch_epi<256>(g, splits, stages, s);
     }
+}
+
+// QKV projection with RoPE, Q quantisation and the paged FP8 KV write in the epilogue.  head_dim is 128
+// (one weight tile per head), N = (heads + 2 * kv_heads) * 128, M <= 32.  dtype: 0 f16, 1 bf16 (the type
+// the unfused GEMM would have stored, and of the cos / sin tables).  -3: shape not taken, use the two kernels.
+inline int launch_qkv_rope(const TcArgs& g, const RopeKv& rk, int dtype, cudaStream_t s) {
+    if (g.K % 16 != 0 || g.M > 32 || g.N != (rk.heads + 2 * rk.kv_heads) * TILE_W)
+        return rvhost::fail_msg(-3, "fused QKV epilogue: shape not taken");
+    const Plan pl = plan_for(g.M, g.N, g.K);
+    if (pl.splits < 2 || tune().reduce == 1) return rvhost::fail_msg(-3, "fused QKV epilogue: needs the split-K push form");
+    if (pl.bn == 16)
+        return dtype == 0 ? launch_one<16, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
+                          : launch_one<16, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+    return dtype == 0 ? launch_one<32, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
+                      : launch_one<32, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
 }
 
 inline int read_status(int* out, bool reset) {

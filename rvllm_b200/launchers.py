@@ -144,6 +144,23 @@ def rope_fp8kv(qkv, heads, kv_heads, head_dim, rotary_dim, cos, sin, positions, 
                                         _stream(stream)), "rope_fp8kv")
 
 
+def qkv_rope_fp8kv(a_fp8, w_fp8, a_scale, w_scale, heads, kv_heads, head_dim, cos, sin, positions, slot_mapping, q_fp8,
+                   q_scale, k_cache, v_cache, k_scale_cache, v_scale_cache, stream=None) -> bool:
+    """QKV projection with RoPE + Q quantisation + paged FP8 KV write in the GEMM epilogue.  Returns
+    False when the library does not take the shape (the caller then runs the GEMM and rope_fp8kv)."""
+    from ._lib import RvllmError
+    M, K = a_fp8.shape
+    slots = k_scale_cache.numel() // kv_heads
+    rc = lib().rvllm_fp8_gemm_qkv_rope_fp8kv(ptr(a_fp8), ptr(w_fp8), ptr(a_scale), ptr(w_scale), M, K, heads, kv_heads,
+                                             head_dim, _dtype_code(cos), ptr(q_fp8), ptr(q_scale), ptr(k_cache),
+                                             ptr(v_cache), ptr(k_scale_cache), ptr(v_scale_cache), ptr(cos), ptr(sin),
+                                             ptr(positions), ptr(slot_mapping), cos.shape[0], slots, _stream(stream))
+    if rc == -3:
+        return False
+    check(rc, "fp8_gemm_qkv_rope_fp8kv")
+    return True
+
+
 def embedding_gather(out, table, token_ids, stream=None) -> None:
     vocab, hidden = table.shape
     check(lib().rvllm_embedding_gather_launch(ptr(out), ptr(table), ptr(token_ids), token_ids.numel(), hidden, vocab,

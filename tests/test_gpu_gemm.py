@@ -238,3 +238,55 @@ def test_gemm_rejects_bad_arguments():
     assert L.rvllm_fp8_gemm_channelscale(*args(4, 8, 72)) == _lib.E_UNSUPPORTED
     assert L.rvllm_fp8_gemm_channelscale(*args(4, 8, 64, a=p + 1)) == _lib.E_INVALID
     assert L.rvllm_fp8_gemm_channelscale(*args(4, 8, 64, a=None)) == _lib.E_INVALID
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("M,heads,kv_heads,K", [(32, 32, 16, 5376), (7, 8, 4, 1024), (1, 4, 4, 640)])
+def test_fused_qkv_rope_epilogue_equals_gemm_then_rope(orc, dtype, M, heads, kv_heads, K):
+    """The QKV GEMM with RoPE + Q quantisation + paged KV write in its epilogue must leave the same
+    bytes and scale bits as the GEMM into a 16-bit buffer followed by the RoPE / KV-write kernel:
+    Q codes and scales, K / V cache rows and per-slot scales, untouched slots included; one token
+    has no cache slot and one has a position outside the tables."""
+    from rvllm_b200 import gemm, launchers
+    HD = 128
+    N = (heads + 2 * kv_heads) * HD
+    dt = getattr(torch, dtype)
+    g = np.random.default_rng(M + heads + K)
+    a, a_s = datagen.quant_rows(orc, g.standard_normal((M, K), dtype=np.float32))
+    w, w_s = datagen.quant_rows(orc, g.standard_normal((N, K), dtype=np.float32) * 0.05)
+    d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    da, das, dw, dws = d(a), d(a_s), d(w), d(w_s)
+    max_pos, slots = 96, 3 * M + 5
+    ang = g.uniform(0, 6.28, (max_pos, HD // 2)).astype(np.float32)
+    cos, sin = torch.from_numpy(np.cos(ang)).to(dt).cuda(), torch.from_numpy(np.sin(ang)).to(dt).cuda()
+    positions = g.integers(0, max_pos, M).astype(np.int32)
+    slot_mapping = g.permutation(slots)[:M].astype(np.int32)
+    if M > 2:
+        positions[1] = max_pos + 3      # nothing may be written for this token
+        slot_mapping[2] = -1            # Q written, no cache write
+    dpos, dslot = d(positions), d(slot_mapping)
+
+    def fresh():
+        gg = np.random.default_rng(5)
+        return dict(q8=torch.full((M, heads, HD), 0xAB, dtype=torch.uint8, device="cuda"),
+                    qs=torch.full((M, heads), -7.0, dtype=torch.float32, device="cuda"),
+                    kc=d(gg.integers(0, 255, (slots, kv_heads, HD), dtype=np.uint8)),
+                    vc=d(gg.integers(0, 255, (slots, kv_heads, HD), dtype=np.uint8)),
+                    ks=d(gg.uniform(0.1, 1, slots * kv_heads).astype(np.float32)),
+                    vs=d(gg.uniform(0.1, 1, slots * kv_heads).astype(np.float32)))
+    ref = fresh()
+    qkv = torch.empty((M, N), dtype=dt, device="cuda")
+    gemm.fp8_gemm_channelscale(qkv, da, dw, das, dws, impl=TC)
+    launchers.rope_fp8kv(qkv, heads, kv_heads, HD, HD, cos, sin, dpos, dslot, ref["q8"], ref["qs"], ref["kc"], ref["vc"],
+                         ref["ks"], ref["vs"])
+    got = fresh()
+    taken = launchers.qkv_rope_fp8kv(da, dw, das, dws, heads, kv_heads, HD, cos, sin, dpos, dslot, got["q8"], got["qs"],
+                                     got["kc"], got["vc"], got["ks"], got["vs"])
+    torch.cuda.synchronize()
+    assert gemm.tc_status() == 0
+    if not taken:
+        pytest.skip("shape not taken by the fused epilogue (no split-K launch)")
+    for key in ("q8", "kc", "vc"):
+        assert torch.equal(got[key], ref[key]), key
+    for key in ("qs", "ks", "vs"):
+        assert torch.equal(got[key].view(torch.int32), ref[key].view(torch.int32)), key
