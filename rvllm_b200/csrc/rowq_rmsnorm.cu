@@ -69,7 +69,23 @@ __device__ __forceinline__ void rmsnorm_quant_row(uint8_t* __restrict__ out, flo
     const T* src = staged ? srow : (residual != nullptr ? residual_out + base : x);
 
     float amax = 0.0f;
-    if (vec_ok) {
+    // Rows of at most 8 * blockDim values (every decode shape): a thread's one vector of the row and
+    // of gamma stays in registers across the absmax and the encode pass.
+    const bool one_vec = vec_ok && (hidden >> 3) <= nt && ((reinterpret_cast<uintptr_t>(out + base) & 7) == 0);
+    uint4 keep_x = make_uint4(0, 0, 0, 0), keep_g = make_uint4(0, 0, 0, 0);
+    if (one_vec) {
+        if (tid < (hidden >> 3)) {
+            keep_x = reinterpret_cast<const uint4*>(src)[tid];
+            keep_g = rv::ldg128(reinterpret_cast<const uint4*>(gamma) + tid);
+            const uint32_t* xp = &keep_x.x;
+            const uint32_t* gp = &keep_g.x;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float2 a = rv::T16<T>::to_f32x2(xp[j]), g = rv::T16<T>::to_f32x2(gp[j]);
+                amax = fmaxf(amax, fmaxf(fabsf(a.x * rms * g.x), fabsf(a.y * rms * g.y)));
+            }
+        }
+    } else if (vec_ok) {
         const int nvec = hidden >> 3;
         for (int v = tid; v < nvec; v += nt) {
             uint4 xv = reinterpret_cast<const uint4*>(src)[v];
@@ -91,7 +107,23 @@ __device__ __forceinline__ void rmsnorm_quant_row(uint8_t* __restrict__ out, flo
     if (tid == 0) scales[row] = scale;
     const float inv = 1.0f / scale;
 
-    if (vec_ok && ((reinterpret_cast<uintptr_t>(out + base) & 7) == 0)) {
+    if (one_vec) {
+        if (tid < (hidden >> 3)) {
+            const uint32_t* xp = &keep_x.x;
+            const uint32_t* gp = &keep_g.x;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float2 a = rv::T16<T>::to_f32x2(xp[j]), g = rv::T16<T>::to_f32x2(gp[j]);
+                f[2 * j] = a.x * rms * g.x * inv;
+                f[2 * j + 1] = a.y * rms * g.y * inv;
+            }
+            uint2 o;
+            o.x = rv::f32x4_to_e4m3x4(f[0], f[1], f[2], f[3]);
+            o.y = rv::f32x4_to_e4m3x4(f[4], f[5], f[6], f[7]);
+            reinterpret_cast<uint2*>(out + base)[tid] = o;
+        }
+    } else if (vec_ok && ((reinterpret_cast<uintptr_t>(out + base) & 7) == 0)) {
         const int nvec = hidden >> 3;
         for (int v = tid; v < nvec; v += nt) {
             uint4 xv = reinterpret_cast<const uint4*>(src)[v];
