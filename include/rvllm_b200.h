@@ -142,8 +142,10 @@ int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const fl
                                   const void* cos_table, const void* sin_table, const int32_t* positions,
                                   const int32_t* slot_mapping, int max_positions, int num_cache_slots, void* stream);
 /* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
- * CTA's receive buffer when the batch tile has at most 32 rows, else pulled out of the peers' rings),
- * 1 always pull.  Both sum in cluster-rank order, so their results are bitwise equal. */
+ * CTA's receive buffer when the batch tile has at most 32 rows and the cluster meets once, else they
+ * are pulled out of the peers' rings), 1 always pull, 2 push with point-to-point mbarrier arrivals
+ * instead of the cluster barrier (measured within 1 % of form 0; kept as a cross-check).  All forms
+ * sum in cluster-rank order, so their results are bitwise equal (tested). */
 void rvllm_fp8_gemm_tc_reduce(int mode);
 
 /* gate|up projection + act(gate)*up + per-token FP8 re-quantisation in one call

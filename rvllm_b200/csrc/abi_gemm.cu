@@ -254,7 +254,7 @@ int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const fl
     return rc;
 }
 
-void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 ? 1 : 0; }
+void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 || mode == 2 ? mode : 0; }
 
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {
     if (M <= 0 || I <= 0 || K <= 0) return 0;

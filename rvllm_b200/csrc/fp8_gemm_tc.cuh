@@ -124,6 +124,30 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 // Cluster barrier halves and a 4-byte store into a cluster peer's shared memory.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Arrive (release, cluster scope) on the mbarrier at the same shared-memory offset in cluster rank `rank`.
+__device__ __forceinline__ void mbar_arrive_peer(uint64_t* local_bar, uint32_t rank) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(local_bar)), "r"(rank)
+        : "memory");
+}
+// Bounded wait with cluster-scope acquire (the data was written by other CTAs of the cluster).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int site) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    atomicCAS(&g_status, 0, (site << 16) | (int)(blockIdx.x & 0xffff));
+    return false;
+}
 __device__ __forceinline__ void st_peer_f32(uint32_t local_saddr, uint32_t rank, float v) {
     asm volatile(
         "{\n\t.reg .b32 ra;\n\t"
@@ -204,6 +228,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     uint64_t* empty = full + MAX_STAGES;
     uint64_t* acc_ready = empty + MAX_STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* recv_bar = reinterpret_cast<uint64_t*>(header + 512);  // push reduction: all partials for this CTA have landed
     const int STAGES = p.stages;
 
     cg::cluster_group cluster = cg::this_cluster();
@@ -221,6 +246,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             mbar_init(empty + s, 1);
         }
         mbar_init(acc_ready, 1);
+        mbar_init(recv_bar, (uint32_t)gridDim.y * 4u);  // one arrival per epilogue warp of every CTA of the cluster
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
@@ -333,9 +359,19 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
             }
             tc_fence_before();
+            if (p.push == 2) {
+                // point-to-point completion: tell every owner that this warp's partials for it are in place
+                asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                __syncwarp();
+                if (lane < S) mbar_arrive_peer(recv_bar, (uint32_t)lane);
+            }
         }
-        cluster_arrive();
-        cluster_wait();
+        if (p.push == 2) {
+            mbar_wait_cluster(recv_bar, 0, 4);
+        } else {
+            cluster_arrive();
+            cluster_wait();
+        }
         if constexpr (EPI == EPI_QKV_ROPE) {
             // Fused QKV epilogue.  The weight tile is one head (128 output channels): this CTA holds, for
             // each batch column it finishes, the whole head of one token.  Round to the activation type (the
@@ -641,7 +677,7 @@ inline bool cached_map(CUtensorMap* out, const void* base, int rows, int K, int 
 struct Tune {
     int stages = 0;
     int splits = 0;
-    int reduce = 0;  // 1: force the pull form of the split-K reduction
+    int reduce = 0;  // 1: force the pull form of the split-K reduction; 2: push form with point-to-point mbarriers
 };
 inline Tune& tune() {
     static Tune t;
@@ -681,7 +717,7 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     p.K = g.K;
     p.kblocks = (g.K + BK - 1) / BK;
     p.stages = stages;
-    p.push = push ? 1 : 0;
+    p.push = push ? (tune().reduce == 2 ? 2 : 1) : 0;
     p.rope = rope ? *rope : RopeKv{};
     if (EPI == EPI_QKV_ROPE && (!push || !rope))
         return rvhost::fail_msg(-3, "the fused QKV epilogue needs a split-K launch with a batch tile of at most 32 rows");

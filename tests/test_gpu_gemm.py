@@ -143,14 +143,14 @@ def test_split_k_push_and_pull_reductions_are_bitwise_equal(orc, M, splits, mode
         res = torch.from_numpy(np.random.default_rng(8).standard_normal((M, N)).astype(np.float32)).to(dt).cuda()
     outs = []
     try:
-        for reduce_mode in (0, 1):
+        for reduce_mode in (0, 1, 2):  # push + cluster barrier, pull, push + point-to-point mbarriers
             _lib.lib().rvllm_fp8_gemm_tc_tune(0, splits)
             _lib.lib().rvllm_fp8_gemm_tc_reduce(reduce_mode)
             outs.append(run(TC, a, a_s, w, w_s, dt, residual=res))
     finally:
         _lib.lib().rvllm_fp8_gemm_tc_tune(0, 0)
         _lib.lib().rvllm_fp8_gemm_tc_reduce(0)
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     ref = want + (res.float().cpu().numpy() if res is not None else 0.0)
     close(outs[0].float().cpu().numpy(), ref)
 
