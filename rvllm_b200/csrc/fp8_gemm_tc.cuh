@@ -248,6 +248,14 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         mbar_init(acc_ready, 1);
         mbar_init(recv_bar, (uint32_t)gridDim.y * 4u);  // one arrival per epilogue warp of every CTA of the cluster
         fence_barrier_init();
+        // This thread is also the TMA producer.  Weights never depend on the previous kernel: fill the ring
+        // with weight tiles right away (before the block even meets; the barriers are this thread's own),
+        // the activation tiles of those stages follow once the predecessor is done.
+        const int pre = nkb < STAGES ? nkb : STAGES;
+        for (int i = 0; i < pre; i++) {
+            mbar_expect_tx(full + i, C::STAGE_BYTES);
+            tma_load_2d(ring + (size_t)i * C::STAGE_BYTES, &map_w, (kb_lo + i) * BK, n0, full + i);
+        }
     }
     if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
     tc_fence_before();
@@ -259,13 +267,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == 0) {
         if (lane == 0) {
-            // Weights never depend on the previous kernel: fill the ring with weight tiles first,
-            // then wait for the predecessor and add the activation tiles of those stages.
-            const int pre = nkb < STAGES ? nkb : STAGES;
-            for (int i = 0; i < pre; i++) {
-                mbar_expect_tx(full + i, C::STAGE_BYTES);
-                tma_load_2d(ring + (size_t)i * C::STAGE_BYTES, &map_w, (kb_lo + i) * BK, n0, full + i);
-            }
+            const int pre = nkb < STAGES ? nkb : STAGES;  // (their weight tiles are already on the way)
             rv::pdl_wait();
             for (int i = 0; i < pre; i++)
                 tma_load_2d(ring + (size_t)i * C::STAGE_BYTES + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + i);
