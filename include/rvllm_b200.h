@@ -141,6 +141,15 @@ int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const fl
                                   void* k_cache, void* v_cache, float* k_scale_cache, float* v_scale_cache,
                                   const void* cos_table, const void* sin_table, const int32_t* positions,
                                   const int32_t* slot_mapping, int max_positions, int num_cache_slots, void* stream);
+/* out = residual + (quantise_per_token(a16) @ W^T) with the per-token quantiser folded into the GEMM:
+ * a16 [M, K] 16-bit activations (the attention output), amax_partials [M, amax_parts] partial maxima
+ * of |a16| per row (their maximum is the row's absmax; rvllm_paged_decode_fp8_amax leaves one per KV
+ * head).  Same bytes as rvllm_quantize_fp8_per_token_launch followed by rvllm_fp8_gemm_channelscale
+ * with a residual, without the FP8 copy of the activations and without the quantiser launch.  M <= 32;
+ * RVLLM_E_UNSUPPORTED otherwise (use the two calls).  out may alias residual. */
+int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const float* amax_partials, int amax_parts,
+                                   const void* w_fp8, const float* w_scale, const void* residual, int M, int N, int K,
+                                   void* stream);
 /* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
  * CTA's receive buffer when the batch tile has at most 32 rows and the cluster meets once, else they
  * are pulled out of the peers' rings), 1 always pull, 2 push with point-to-point mbarrier arrivals
@@ -223,6 +232,16 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
  * round trip less.  out_fp8 [batch, heads*head_dim] u8, out_scale [batch] f32.  The workspace is
  * always needed: rvllm_paged_decode_quant_workspace_size bytes. */
 uint64_t rvllm_paged_decode_quant_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim);
+/* rvllm_paged_decode_fp8 that also leaves, per (sequence, kv_head), the maximum of |output as stored|
+ * in amax_out [batch, num_kv_heads] (input of rvllm_fp8_gemm_residual_from16).  Only where the tcgen05
+ * kernel runs with a single chunk per sequence; RVLLM_E_UNSUPPORTED otherwise. */
+int rvllm_paged_decode_fp8_amax(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
+                                int out_dtype, float* amax_out, const int32_t* block_tables, const int32_t* context_lens,
+                                void* workspace, size_t workspace_bytes, const float* k_scale_cache,
+                                const float* v_scale_cache, const float* q_scale_cache, const float* q_descale,
+                                const float* k_descale, const float* v_descale, float scale, int batch_size,
+                                int num_heads, int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                                int num_blocks_total, int window_size_left, void* stream);
 int rvllm_paged_decode_fp8_quant(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* out_fp8,
                                  float* out_scale, int round_dtype, const int32_t* block_tables,
                                  const int32_t* context_lens, void* workspace, size_t workspace_bytes,

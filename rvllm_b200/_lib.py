@@ -63,6 +63,7 @@ SIGNATURES = {
     "rvllm_fp8_gemm_tc_status": (_i32, [C.POINTER(_i32), _i32]),
     "rvllm_fp8_gemm_tc_tune": (None, [_i32, _i32]),
     "rvllm_fp8_gemm_tc_reduce": (None, [_i32]),
+    "rvllm_fp8_gemm_residual_from16": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "rvllm_fp8_gemm_qkv_rope_fp8kv": (_i32, [_vp] * 4 + [_i32] * 6 + [_vp] * 10 + [_i32] * 2 + [_vp]),
     "rvllm_fa_sm89_abi_version": (_i32, []),
     "fa_sm89_fp8_output_dtype": (_i32, []),
@@ -81,6 +82,7 @@ SIGNATURES = {
     "rvllm_paged_decode_quant_workspace_size": (_u64, [_i32, _i32, _i32, _i32]),
     "rvllm_paged_decode_fp8_quant": (_i32, [_vp] * 5 + [_i32] + [_vp] * 3 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_paged_decode_fp8": (_i32, [_vp] * 4 + [_i32] + [_vp] * 3 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
+    "rvllm_paged_decode_fp8_amax": (_i32, [_vp] * 4 + [_i32] + [_vp] * 4 + [_sz] + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_paged_decode_static_scratch_bytes": (_sz, []),
     "rvllm_paged_decode_fp8_static_scratch": (_i32, [_vp] * 4 + [_i32] + [_vp] * 2 + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_rope_fp8kv_launch": (_i32, [_vp, _vp, _vp, _i32] + [_vp] * 10 + [_i32] * 8 + [_vp]),

@@ -98,6 +98,7 @@ namespace {
 struct QuantOut {
     uint8_t* fp8 = nullptr;  // when set: fused combine + per-token quantisation instead of a 16-bit output
     float* scale = nullptr;
+    float* amax = nullptr;   // when set (tcgen05 kernel, one chunk): max |stored output| per (sequence, kv_head)
 };
 
 // tcgen05 / TMA main kernel (head_dim 128 or 256, up to 8 query heads per KV head)
@@ -281,6 +282,9 @@ static int decode_core(const QuantOut& qo, const void* q_fp8, const void* k_cach
     p.max_chunks = chunks;
     p.min_chunk_tokens = g_min_chunk_tokens;
     p.force_partial = qo.fp8 ? 1 : 0;
+    p.amax_out = qo.amax;
+    if (qo.amax && (chunks != 1 || g_variant == 1 || g_variant == 2 || g_variant == 3 || !rvua::supports(p, head_dim)))
+        return rv_fail(RVLLM_E_UNSUPPORTED, "the per-token absmax output needs the tcgen05 kernel and a single chunk");
     cudaStream_t s = (cudaStream_t)stream;
     return out_dtype == RVLLM_F16 ? launch_attn_hd<__half>(p, qo, head_dim, s)
                                   : launch_attn_hd<__nv_bfloat16>(p, qo, head_dim, s);
@@ -296,6 +300,22 @@ int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const voi
     return decode_core(QuantOut(), q_fp8, k_cache_fp8, v_cache_fp8, output, out_dtype, block_tables, context_lens,
                        workspace, workspace_bytes, k_scale_cache, v_scale_cache, q_scale_cache, q_descale, k_descale,
                        v_descale, scale, batch_size, num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
+                       num_blocks_total, window_size_left, stream);
+}
+
+int rvllm_paged_decode_fp8_amax(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
+                                int out_dtype, float* amax_out, const int32_t* block_tables, const int32_t* context_lens,
+                                void* workspace, size_t workspace_bytes, const float* k_scale_cache,
+                                const float* v_scale_cache, const float* q_scale_cache, const float* q_descale,
+                                const float* k_descale, const float* v_descale, float scale, int batch_size,
+                                int num_heads, int num_kv_heads, int head_dim, int block_size, int max_blocks_per_seq,
+                                int num_blocks_total, int window_size_left, void* stream) {
+    if (!amax_out) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    QuantOut qo;
+    qo.amax = amax_out;
+    return decode_core(qo, q_fp8, k_cache_fp8, v_cache_fp8, output, out_dtype, block_tables, context_lens, workspace,
+                       workspace_bytes, k_scale_cache, v_scale_cache, q_scale_cache, q_descale, k_descale, v_descale,
+                       scale, batch_size, num_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq,
                        num_blocks_total, window_size_left, stream);
 }
 

@@ -254,6 +254,32 @@ int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const fl
     return rc;
 }
 
+int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const float* amax_partials, int amax_parts,
+                                   const void* w_fp8, const float* w_scale, const void* residual, int M, int N, int K,
+                                   void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || amax_parts <= 0) return rv_fail(RVLLM_E_INVALID, "M, N, K, amax_parts must be > 0");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    if (!out || !a16 || !amax_partials || !w_fp8 || !w_scale || !residual) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (!rv_aligned(a16, 16) || !rv_aligned(w_fp8, 16)) return rv_fail(RVLLM_E_INVALID, "a16 / w must be 16-byte aligned");
+    rvtc::TcArgs t = {};
+    t.out = out;
+    t.out_kind = dtype;
+    t.a = nullptr;
+    t.w = w_fp8;
+    t.a_scale = nullptr;
+    t.w_scale = w_scale;
+    t.residual = residual;
+    t.M = M;
+    t.N = N;
+    t.K = K;
+    t.a16 = a16;
+    t.amax_part = amax_partials;
+    t.amax_parts = amax_parts;
+    const int rc = rvtc::launch_residual_a16(t, dtype == RVLLM_F16 ? 0 : 1, (cudaStream_t)stream);
+    if (rc == -3) return RVLLM_E_UNSUPPORTED;
+    return rc;
+}
+
 void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 || mode == 2 ? mode : 0; }
 
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {

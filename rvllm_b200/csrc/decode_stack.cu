@@ -126,6 +126,7 @@ struct rvllm_stack {
     uint8_t* q_fp8;      // [B, max q_dim]
     float* q_scale;      // [B, heads]
     void* attn_out;      // [B, max q_dim] 16-bit
+    float* attn_amax;    // [B, kv_heads] max |attention output| per (sequence, kv_head)
     void* gateup;        // [B, 2*ffn] 16-bit
     float* logits;       // [B, vocab]
     void* attn_ws;
@@ -212,6 +213,7 @@ size_t layout(rvllm_stack* s, uint8_t* base) {
     s->q_fp8 = take((size_t)B * max_q);
     s->q_scale = (float*)take((size_t)B * c.heads * sizeof(float));
     s->attn_out = take((size_t)B * max_q * 2);
+    s->attn_amax = (float*)take((size_t)B * c.kv_heads * sizeof(float));
     s->gateup = take((size_t)B * 2 * c.ffn * 2);
     s->logits = (float*)take((size_t)B * c.vocab * sizeof(float));
     uint64_t aw = 0;
@@ -298,6 +300,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         }
         const float sm_scale = 1.0f / sqrtf((float)L.head_dim);
         const int* tables = L.global ? s->tables_global : s->tables_sliding;
+        bool o_done = false;
         if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
             // split-KV: the combine pass also does the per-token quantisation (same bytes as the
             // plain attention call followed by the quantiser)
@@ -307,14 +310,35 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                                 c.kv_heads, L.head_dim, c.block_size, L.max_blocks, L.num_blocks,
                                                 L.window_left, st));
         } else {
-            RV_TRY(rvllm_paged_decode_fp8(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, tables, s->ctx_lens,
-                                          s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale, s->q_scale, nullptr,
-                                          nullptr, nullptr, sm_scale, B, c.heads, c.kv_heads, L.head_dim, c.block_size,
-                                          L.max_blocks, L.num_blocks, L.window_left, st));
-            RV_TRY(rvllm_quantize_fp8_per_token_launch(B, L.q_dim, s->x_fp8, s->x_scale, s->attn_out, c.dtype, st));
+            // One chunk per sequence.  Where the tcgen05 attention kernel runs and the batch fits one GEMM
+            // batch tile, it also leaves each row's partial absmax and the O projection quantises its own
+            // activation tiles from the 16-bit output: no quantiser launch, no FP8 copy (same bytes).
+            int a16 = RVLLM_E_UNSUPPORTED;
+            if (B <= 32 && c.gemm_impl != 1 &&
+                rvllm_paged_decode_kernel_for(c.heads, c.kv_heads, L.head_dim, c.block_size, L.num_blocks) == 4)
+                a16 = rvllm_paged_decode_fp8_amax(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, s->attn_amax,
+                                                  tables, s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale,
+                                                  L.v_scale, s->q_scale, nullptr, nullptr, nullptr, sm_scale, B,
+                                                  c.heads, c.kv_heads, L.head_dim, c.block_size, L.max_blocks,
+                                                  L.num_blocks, L.window_left, st);
+            if (a16 == RVLLM_OK) {
+                RV_TRY(rvllm_fp8_gemm_residual_from16(s->residual, c.dtype, s->attn_out, s->attn_amax, c.kv_heads, W.o_w,
+                                                      W.o_scale, s->residual, B, H, L.q_dim, st));
+                o_done = true;
+                n--;
+            } else if (a16 != RVLLM_E_UNSUPPORTED) {
+                RV_TRY(a16);
+            } else {
+                RV_TRY(rvllm_paged_decode_fp8(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, tables,
+                                              s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
+                                              s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads, c.kv_heads,
+                                              L.head_dim, c.block_size, L.max_blocks, L.num_blocks, L.window_left, st));
+                RV_TRY(rvllm_quantize_fp8_per_token_launch(B, L.q_dim, s->x_fp8, s->x_scale, s->attn_out, c.dtype, st));
+            }
         }
-        RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.o_w, s->x_scale, W.o_scale, s->residual,
-                                           B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
+        if (!o_done)
+            RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.o_w, s->x_scale, W.o_scale, s->residual,
+                                               B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
         RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
                                                     W.mlp_norm_gamma, c.dtype, st));
         RV_TRY(rvllm_fp8_gemm_channelscale(s->gateup, c.dtype, s->x_fp8, W.gateup_w, s->x_scale, W.gateup_scale,

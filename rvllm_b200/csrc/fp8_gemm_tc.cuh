@@ -80,6 +80,11 @@ struct TcParams {
     int stages;   // depth of the TMA ring (2..MAX_STAGES); sets the shared-memory footprint
     int push;     // split-K partials are pushed into the finishing CTA's receive buffer (behind the ring)
     RopeKv rope;  // EPI_QKV_ROPE only
+    // EPI_RESIDUAL_A16 only: the activation operand arrives as 16-bit values [M, K] plus `amax_parts` partial
+    // maxima of |value| per row; the kernel derives the per-row scale and quantises its own A tiles
+    const void* a16;
+    const float* amax_part;
+    int amax_parts;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -91,6 +96,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -199,7 +207,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
     return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
 }
 
-constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2, EPI_QKV_ROPE = 3;
+constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2, EPI_QKV_ROPE = 3, EPI_RESIDUAL_A16 = 4;
 
 constexpr int MAX_STAGES = 8;
 constexpr int HEADER_BYTES = 1024;  // barriers + TMEM address holder, in front of the ring
@@ -239,10 +247,14 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int kb_hi = (int)((long long)(split + 1) * p.kblocks / S);
     const int nkb = kb_hi - kb_lo;
 
+    constexpr bool A16 = EPI == EPI_RESIDUAL_A16;           // A tiles are quantised here from 16-bit activations
+    constexpr bool RES = EPI == EPI_RESIDUAL || A16;        // residual epilogue
+    __shared__ float s_ascale[A16 ? BN : 1], s_ainv[A16 ? BN : 1];
+    auto a_scale_of = [&](int m) -> float { return A16 ? s_ascale[m - m0] : p.a_scale[m]; };
     rv::pdl_launch();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(full + s, 1);
+            mbar_init(full + s, A16 ? 5 : 1);  // the producer's arrival (+ one per converting warp)
             mbar_init(empty + s, 1);
         }
         mbar_init(acc_ready, 1);
@@ -253,7 +265,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // the activation tiles of those stages follow once the predecessor is done.
         const int pre = nkb < STAGES ? nkb : STAGES;
         for (int i = 0; i < pre; i++) {
-            mbar_expect_tx(full + i, C::STAGE_BYTES);
+            mbar_expect_tx(full + i, A16 ? TILE_W * BK : C::STAGE_BYTES);
             tma_load_2d(ring + (size_t)i * C::STAGE_BYTES, &map_w, (kb_lo + i) * BK, n0, full + i);
         }
     }
@@ -262,15 +274,31 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    if (A16) {
+        // per-row activation scale from the partial maxima the producer of the activations left behind
+        rv::pdl_wait();
+        if ((int)threadIdx.x < BN) {
+            const int m = m0 + (int)threadIdx.x;
+            float amax = 0.0f;
+            if (m < p.M)
+                for (int q = 0; q < p.amax_parts; q++) amax = fmaxf(amax, p.amax_part[(size_t)m * p.amax_parts + q]);
+            const float sc = rv::row_scale(amax);
+            s_ascale[threadIdx.x] = sc;
+            s_ainv[threadIdx.x] = 1.0f / sc;
+        }
+        __syncthreads();
+    }
     const bool push = S > 1 && p.push != 0;
     if (push) cluster_arrive();  // "this CTA runs": peers wait for it (long since complete) before their first remote store
 
     if (warp == 0) {
         if (lane == 0) {
             const int pre = nkb < STAGES ? nkb : STAGES;  // (their weight tiles are already on the way)
-            rv::pdl_wait();
-            for (int i = 0; i < pre; i++)
-                tma_load_2d(ring + (size_t)i * C::STAGE_BYTES + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + i);
+            if (!A16) {
+                rv::pdl_wait();
+                for (int i = 0; i < pre; i++)
+                    tma_load_2d(ring + (size_t)i * C::STAGE_BYTES + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + i);
+            }
             bool alive = true;
             for (int i = pre; i < nkb; i++) {
                 const int s = i % STAGES;
@@ -278,9 +306,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 alive = mbar_wait(empty + s, ph ^ 1u, 1);
                 if (!alive) break;
                 uint8_t* w_dst = ring + (size_t)s * C::STAGE_BYTES;
-                mbar_expect_tx(full + s, C::STAGE_BYTES);
+                mbar_expect_tx(full + s, A16 ? TILE_W * BK : C::STAGE_BYTES);
                 tma_load_2d(w_dst, &map_w, (kb_lo + i) * BK, n0, full + s);
-                tma_load_2d(w_dst + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + s);
+                if (!A16) tma_load_2d(w_dst + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + s);
             }
         }
     } else if (warp == 1) {
@@ -305,6 +333,42 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             umma_commit(acc_ready);  // arrives when every MMA issued above has completed
         }
     }
+    if (A16 && warp >= EPI_WARP0) {
+        // The four epilogue warps are idle during the main loop: they turn the 16-bit activations into the
+        // swizzled FP8 A tiles themselves (the per-token quantiser's arithmetic: scale = max(absmax / 448,
+        // 1e-12), code = e4m3(x * (1 / scale))), so no separate quantiser launch and no FP8 copy in HBM.
+        const int t = (int)threadIdx.x - EPI_WARP0 * 32;
+        const OutT* a16 = reinterpret_cast<const OutT*>(p.a16);
+        bool alive = true;
+        for (int i = 0; i < nkb && alive; i++) {
+            const int s = i % STAGES;
+            if (i >= STAGES) alive = mbar_wait(empty + s, ((uint32_t)(i / STAGES) & 1u) ^ 1u, 5);
+            if (!alive) break;
+            uint8_t* a_tile = ring + (size_t)s * C::STAGE_BYTES + TILE_W * BK;
+            for (int c = t; c < BN * 8; c += 128) {      // 16-byte chunks of the [BN rows x 128 B] tile
+                const int r = c >> 3, cc = c & 7;
+                const int m = m0 + r, k0 = (kb_lo + i) * BK + cc * 16;
+                uint4 o = make_uint4(0, 0, 0, 0);
+                if (m < p.M && k0 < p.K) {
+                    const uint4* src = reinterpret_cast<const uint4*>(a16 + (size_t)m * p.K + k0);
+                    const uint4 x0 = rv::ldg128(src), x1 = rv::ldg128(src + 1);
+                    const float inv = s_ainv[r];
+                    const uint32_t xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float2 a = rv::T16<OutT>::to_f32x2(xs[2 * j]), b = rv::T16<OutT>::to_f32x2(xs[2 * j + 1]);
+                        w4[j] = rv::f32x4_to_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+                    }
+                    o = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+                *reinterpret_cast<uint4*>(a_tile + r * BK + ((cc ^ (r & 7)) << 4)) = o;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full + s);
+        }
+    }
     __syncwarp();
     rv::pdl_wait();  // scales and the residual come from predecessors; also keeps completion ordered
 
@@ -326,9 +390,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int m = m0 + col, n = n0 + e % TILE_W;
             pre_a[j] = pre_w[j] = pre_res[j] = 0.0f;
             if (e < LC * TILE_W && col < BN && m < p.M && n < p.N) {
-                pre_a[j] = p.a_scale[m];
+                pre_a[j] = a_scale_of(m);
                 pre_w[j] = p.w_scale[n];
-                if (EPI == EPI_RESIDUAL)
+                if (RES)
                     pre_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
             }
         }
@@ -402,7 +466,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             sum_lo += recv[(size_t)(sp * LC + lc) * TILE_W + d];
                             sum_hi += recv[(size_t)(sp * LC + lc) * TILE_W + d + 64];
                         }
-                    const float as = p.a_scale[m];
+                    const float as = a_scale_of(m);
                     const float a = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32_sat(as * (ws_lo * sum_lo)));
                     const float b = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32_sat(as * (ws_hi * sum_hi)));
                     pos = rk.positions[m];
@@ -452,14 +516,14 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
             for (int sp = 0; sp < 8; sp++)
                 if (sp < S) sum += recv[(size_t)(sp * LC + lc) * TILE_W + r];
-            const float as = pre ? as_p : p.a_scale[m];
+            const float as = pre ? as_p : a_scale_of(m);
             const float ws = pre ? ws_p : p.w_scale[n];
             float val = as * (ws * sum);  // same association as the unsplit epilogue
             const size_t o = (size_t)m * p.N + n;
             if (EPI == EPI_F32) {
                 reinterpret_cast<float*>(p.out)[o] = val;
             } else {
-                if (EPI == EPI_RESIDUAL)
+                if (RES)
                     val += pre ? res_p : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
                 reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
             }
@@ -497,12 +561,12 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int j = 0; j < 16; j++) {
                     const int m = m0 + c0 + j;
                     if (m < p.M && n < p.N) {
-                        float val = p.a_scale[m] * (ws * __uint_as_float(v[j]));
+                        float val = a_scale_of(m) * (ws * __uint_as_float(v[j]));
                         const size_t o = (size_t)m * p.N + n;
                         if (EPI == EPI_F32) {
                             reinterpret_cast<float*>(p.out)[o] = val;
                         } else {
-                            if (EPI == EPI_RESIDUAL)
+                            if (RES)
                                 val += rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
                             reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
                         }
@@ -528,9 +592,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (e < BN * TILE_W) {
                 const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
                 if (m < p.M && n < p.N) {
-                    pre_a[j] = p.a_scale[m];
+                    pre_a[j] = a_scale_of(m);
                     pre_w[j] = p.w_scale[n];
-                    if (EPI == EPI_RESIDUAL)
+                    if (RES)
                         pre_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
                 }
             }
@@ -548,7 +612,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (EPI == EPI_F32) {
                     reinterpret_cast<float*>(p.out)[o] = val;
                 } else {
-                    if (EPI == EPI_RESIDUAL)
+                    if (RES)
                         val += have_res ? res : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
                     reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
                 }
@@ -584,7 +648,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (s < S) sum += peer[s][e];
             const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
             const bool in = m < p.M && n < p.N;
-            finish(e, sum, in ? p.a_scale[m] : 0.0f, in ? p.w_scale[n] : 0.0f, false, 0.0f);
+            finish(e, sum, in ? a_scale_of(m) : 0.0f, in ? p.w_scale[n] : 0.0f, false, 0.0f);
         }
         if (!e_rest_done) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
@@ -607,6 +671,9 @@ struct TcArgs {
     const float* w_scale;
     const void* residual;
     int M, N, K;
+    const void* a16 = nullptr;          // EPI_RESIDUAL_A16: 16-bit activations instead of `a` / `a_scale`
+    const float* amax_part = nullptr;
+    int amax_parts = 0;
 };
 
 inline size_t workspace_bytes(int, int, int) { return 0; }
@@ -690,7 +757,7 @@ template <int BN, int EPI, typename OutT>
 int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const RopeKv* rope = nullptr) {
     using C = Cfg<BN>;
     CUtensorMap mw, ma;
-    if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || !cached_map(&ma, g.a, g.M, g.K, BN))
+    if (!cached_map(&mw, g.w, g.N, g.K, TILE_W) || (EPI == EPI_RESIDUAL_A16 ? (ma = mw, false) : !cached_map(&ma, g.a, g.M, g.K, BN)))
         return rvhost::fail_msg(-2, "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)");
     auto kern = fp8_gemm_tc_kernel<BN, EPI, OutT>;
     // Split-K with a small batch tile: push reduction (needs its receive buffer behind the ring);
@@ -721,6 +788,11 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     p.stages = stages;
     p.push = push ? (tune().reduce == 2 ? 2 : 1) : 0;
     p.rope = rope ? *rope : RopeKv{};
+    p.a16 = g.a16;
+    p.amax_part = g.amax_part;
+    p.amax_parts = g.amax_parts;
+    if (EPI == EPI_RESIDUAL_A16 && (!g.a16 || !g.amax_part || g.amax_parts <= 0 || BN > 32))
+        return rvhost::fail_msg(-3, "the 16-bit activation form needs a16, partial maxima and a batch tile of at most 32 rows");
     if (EPI == EPI_QKV_ROPE && (!push || !rope))
         return rvhost::fail_msg(-3, "the fused QKV epilogue needs a split-K launch with a batch tile of at most 32 rows");
     cudaLaunchConfig_t cfg = {};
@@ -820,6 +892,18 @@ inline int launch_qkv_rope(const TcArgs& g, const RopeKv& rk, int dtype, cudaStr
                           : launch_one<16, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
     return dtype == 0 ? launch_one<32, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
                       : launch_one<32, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+}
+
+// Residual GEMM whose activation operand is given as 16-bit values plus per-row partial maxima: the per-token
+// quantiser is folded into the kernel (its idle epilogue warps build the FP8 A tiles).  M <= 32.
+inline int launch_residual_a16(const TcArgs& g, int dtype, cudaStream_t s) {
+    if (g.K % 16 != 0 || g.M > 32) return rvhost::fail_msg(-3, "16-bit activation form: shape not taken");
+    const Plan pl = plan_for(g.M, g.N, g.K);
+    if (pl.bn == 16)
+        return dtype == 0 ? launch_one<16, EPI_RESIDUAL_A16, __half>(g, pl.splits, pl.stages, s)
+                          : launch_one<16, EPI_RESIDUAL_A16, __nv_bfloat16>(g, pl.splits, pl.stages, s);
+    return dtype == 0 ? launch_one<32, EPI_RESIDUAL_A16, __half>(g, pl.splits, pl.stages, s)
+                      : launch_one<32, EPI_RESIDUAL_A16, __nv_bfloat16>(g, pl.splits, pl.stages, s);
 }
 
 inline int read_status(int* out, bool reset) {

@@ -75,6 +75,7 @@ struct Params {
     int max_chunks;
     int min_chunk_tokens;  // a sequence is cut into ceil(attended / this) chunks, at most max_chunks
     int force_partial;     // always leave partials in the workspace (the fused combine+quant pass reads them)
+    float* amax_out;       // tcgen05 kernel, single chunk: max |rounded output| per (sequence, kv_head), or null
 };
 
 // Upper bound on chunks per sequence for a launch shape; the workspace-size query and the

@@ -257,6 +257,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
             } else {
                 for (int i = tid; i < group * HD; i += THREADS)
                     out[((size_t)b * p.heads + (size_t)kvh * group) * HD + i] = rv::T16<OutT>::from_f32(fill);
+                if (p.amax_out && tid == 0) p.amax_out[(size_t)b * p.kv_heads + kvh] = 0.0f;  // zeros, or NaN (ignored by a max)
             }
         }
     } else {
@@ -590,6 +591,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         if (bad) atomicOr(s_bad, bad);
         bar_softmax();
         const unsigned bad_mask = alive ? *s_bad : 0xffffffffu;
+        float amax = 0.0f;  // max |output as stored| over this thread's values (what the per-token quantiser would scan)
 #pragma unroll
         for (int h = 0; h < HALVES; h++) {
             float acc[GT];
@@ -613,7 +615,9 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                     if (nchunks == 1 && !p.force_partial) {
                         float v = L > 0.0f ? acc[k] / L : acc[k];
                         if (any_bad) v = CUDART_NAN_F;
-                        out[((size_t)b * p.heads + head) * HD + d] = rv::T16<OutT>::from_f32(v);
+                        const OutT stored = rv::T16<OutT>::from_f32(v);
+                        out[((size_t)b * p.heads + head) * HD + d] = stored;
+                        amax = fmaxf(amax, fabsf(rv::T16<OutT>::to_f32(stored)));  // fmaxf drops a NaN, as the quantiser does
                     } else {
                         float* ws = p.workspace + (((size_t)b * p.heads + head) * p.max_chunks + chunk) * PSTRIDE;
                         ws[d] = any_bad ? CUDART_NAN_F : acc[k];
@@ -623,6 +627,14 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                         }
                     }
                 }
+        }
+        if (p.amax_out && nchunks == 1 && !p.force_partial) {
+            amax = rv::warp_max(amax);
+            bar_softmax();  // everyone has read the sums: the scratch can be reused
+            if (lane == 0) red[64 + (warp - 2)] = amax;
+            bar_softmax();
+            if (warp == 2 && lane == 0)
+                p.amax_out[(size_t)b * p.kv_heads + kvh] = fmaxf(fmaxf(red[64], red[65]), fmaxf(red[66], red[67]));
         }
         tc_fence_before();
     }

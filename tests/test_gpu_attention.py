@@ -406,3 +406,41 @@ def test_fa2_ptx_entry_against_reference_kernel(orc, kernel_variant):
         _fa2_launch(mod, c, out, 1023)
         outs.append(out.float().cpu().numpy())
     assert_close(outs[1], outs[0].astype(np.float64), abs_tol=1e-3, rel_tol=5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("HD,window,ctxs", [(128, 1023, [0, 1, 600, 1500]), (256, -1, [300, 17, 900, 128])])
+def test_attention_absmax_output(orc, kernel_variant, dtype, HD, window, ctxs):
+    """rvllm_paged_decode_fp8_amax: same output bytes as the plain entry point, plus the maximum of
+    |output as stored| per (sequence, kv_head) — what the per-token quantiser would find."""
+    from rvllm_b200 import _lib
+    from rvllm_b200.attention import PagedDecodeParams
+    if kernel_variant != 4:
+        pytest.skip("only the tcgen05 kernel leaves the partial maxima")
+    L = _lib.lib()
+    c = datagen.attention_case(orc, len(ctxs), 32, 16, HD, 16, ctxs, seed=21 + HD, window=window)
+    B = len(ctxs)
+    L.rvllm_paged_decode_tune(0, 0, 4)
+    p = PagedDecodeParams(B, 32, 16, HD, 16, c["max_blocks"], c["num_blocks"], HD ** -0.5, window)
+    if p.max_chunks() != 1:
+        L.rvllm_paged_decode_tune(1, 0, 4)     # a CTA target of 1: never split
+    try:
+        want = run_ours(c, out_dtype=dtype)
+        t = {k: dev(c[k]) for k in ("q", "k", "v", "ks", "vs", "qs", "tables", "ctx")}
+        out = torch.full((B, 32, HD), 123.0, dtype=dtype, device="cuda")
+        amax = torch.full((B, 16), -1.0, dtype=torch.float32, device="cuda")
+        ws = torch.empty(16, dtype=torch.uint8, device="cuda")
+        rc = L.rvllm_paged_decode_fp8_amax(t["q"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), out.data_ptr(),
+                                           0 if dtype == torch.float16 else 1, amax.data_ptr(), t["tables"].data_ptr(),
+                                           t["ctx"].data_ptr(), ws.data_ptr(), 16, t["ks"].data_ptr(), t["vs"].data_ptr(),
+                                           t["qs"].data_ptr(), None, None, None, HD ** -0.5, B, 32, 16, HD, 16,
+                                           c["max_blocks"], c["num_blocks"], window,
+                                           torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+    finally:
+        L.rvllm_paged_decode_tune(0, 0, 4)
+    assert rc == 0
+    got = out.float().cpu().numpy()
+    assert np.array_equal(got, want)
+    ref = np.abs(got.reshape(B, 16, 2 * HD)).max(axis=2)
+    assert np.array_equal(amax.cpu().numpy(), ref)

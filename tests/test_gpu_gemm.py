@@ -290,3 +290,38 @@ def test_fused_qkv_rope_epilogue_equals_gemm_then_rope(orc, dtype, M, heads, kv_
         assert torch.equal(got[key], ref[key]), key
     for key in ("qs", "ks", "vs"):
         assert torch.equal(got[key].view(torch.int32), ref[key].view(torch.int32)), key
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("M,N,K,parts", [(32, 5376, 4096, 16), (7, 640, 1024, 4), (1, 1336, 2176, 1), (32, 5376, 8192, 16)])
+def test_residual_gemm_from_16bit_activations_equals_quantiser_then_gemm(orc, dtype, M, N, K, parts):
+    """The residual GEMM that quantises its own A tiles from 16-bit activations (given per-row
+    partial maxima) must produce the bytes of: per-token quantiser, then the residual GEMM."""
+    import ctypes
+    from rvllm_b200 import gemm, _lib
+    from rvllm_b200.launchers import QuantizeFp8PerTokenLaunch
+    dt = getattr(torch, dtype)
+    g = np.random.default_rng(N + K + M)
+    x = torch.from_numpy((g.standard_normal((M, K)) * 0.7).astype(np.float32)).to(dt).cuda()
+    if M > 2:
+        x[1].zero_()                                # an all-zero row: scale 1e-12
+    w, w_s = datagen.quant_rows(orc, g.standard_normal((N, K), dtype=np.float32) * 0.05)
+    d = lambda t: torch.from_numpy(np.ascontiguousarray(t)).cuda()
+    dw, dws = d(w), d(w_s)
+    res0 = torch.from_numpy(g.standard_normal((M, N)).astype(np.float32)).to(dt).cuda()
+    # reference chain
+    a8 = torch.empty((M, K), dtype=torch.uint8, device="cuda")
+    a_s = torch.empty(M, dtype=torch.float32, device="cuda")
+    QuantizeFp8PerTokenLaunch(M, K).launch(a8, a_s, x)
+    ref = res0.clone()
+    gemm.fp8_gemm_channelscale(ref, a8, dw, a_s, dws, residual=ref, impl=TC)
+    # fused form: partial maxima over `parts` column groups of each row
+    amax = x.float().abs().reshape(M, parts, K // parts).amax(dim=2).contiguous()
+    got = res0.clone()
+    code = 0 if dt == torch.float16 else 1
+    rc = _lib.lib().rvllm_fp8_gemm_residual_from16(got.data_ptr(), code, x.data_ptr(), amax.data_ptr(), parts,
+                                                   dw.data_ptr(), dws.data_ptr(), got.data_ptr(), M, N, K,
+                                                   torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and gemm.tc_status() == 0
+    assert torch.equal(got, ref)
