@@ -339,30 +339,52 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // 1e-12), code = e4m3(x * (1 / scale))), so no separate quantiser launch and no FP8 copy in HBM.
         const int t = (int)threadIdx.x - EPI_WARP0 * 32;
         const OutT* a16 = reinterpret_cast<const OutT*>(p.a16);
+        constexpr int CPT = (BN * 8 + 127) / 128;  // 16-byte output chunks per thread and K block (1 or 2)
+        // this thread's chunks: row r, 16-column group cc — the same for every K block
+        uint4 nx[CPT][2];                          // the next K block's 16-bit values, fetched one block ahead
+        auto fetch = [&](int i) {
+#pragma unroll
+            for (int q = 0; q < CPT; q++) {
+                const int c = t + q * 128, r = c >> 3, cc = c & 7;
+                const int m = m0 + r, k0 = (kb_lo + i) * BK + cc * 16;
+                nx[q][0] = nx[q][1] = make_uint4(0, 0, 0, 0);
+                if (c < BN * 8 && i < nkb && m < p.M && k0 < p.K) {
+                    const uint4* src = reinterpret_cast<const uint4*>(a16 + (size_t)m * p.K + k0);
+                    nx[q][0] = rv::ldg128(src);
+                    nx[q][1] = rv::ldg128(src + 1);
+                }
+            }
+        };
+        fetch(0);
         bool alive = true;
         for (int i = 0; i < nkb && alive; i++) {
+            uint4 cur[CPT][2];
+#pragma unroll
+            for (int q = 0; q < CPT; q++) {
+                cur[q][0] = nx[q][0];
+                cur[q][1] = nx[q][1];
+            }
+            fetch(i + 1);
             const int s = i % STAGES;
             if (i >= STAGES) alive = mbar_wait(empty + s, ((uint32_t)(i / STAGES) & 1u) ^ 1u, 5);
             if (!alive) break;
             uint8_t* a_tile = ring + (size_t)s * C::STAGE_BYTES + TILE_W * BK;
-            for (int c = t; c < BN * 8; c += 128) {      // 16-byte chunks of the [BN rows x 128 B] tile
-                const int r = c >> 3, cc = c & 7;
-                const int m = m0 + r, k0 = (kb_lo + i) * BK + cc * 16;
-                uint4 o = make_uint4(0, 0, 0, 0);
-                if (m < p.M && k0 < p.K) {
-                    const uint4* src = reinterpret_cast<const uint4*>(a16 + (size_t)m * p.K + k0);
-                    const uint4 x0 = rv::ldg128(src), x1 = rv::ldg128(src + 1);
+#pragma unroll
+            for (int q = 0; q < CPT; q++) {
+                const int c = t + q * 128, r = c >> 3, cc = c & 7;
+                if (c < BN * 8) {
                     const float inv = s_ainv[r];
-                    const uint32_t xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    const uint32_t xs[8] = {cur[q][0].x, cur[q][0].y, cur[q][0].z, cur[q][0].w,
+                                            cur[q][1].x, cur[q][1].y, cur[q][1].z, cur[q][1].w};
                     uint32_t w4[4];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const float2 a = rv::T16<OutT>::to_f32x2(xs[2 * j]), b = rv::T16<OutT>::to_f32x2(xs[2 * j + 1]);
                         w4[j] = rv::f32x4_to_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
                     }
-                    o = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                    // (rows past M and columns past K were fetched as zeros: code 0)
+                    *reinterpret_cast<uint4*>(a_tile + r * BK + ((cc ^ (r & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
-                *reinterpret_cast<uint4*>(a_tile + r * BK + ((cc ^ (r & 7)) << 4)) = o;
             }
             fence_proxy_async();
             __syncwarp();
