@@ -83,7 +83,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.first = index, [], None, 0
 
     def start(self):
         try:
@@ -93,6 +93,11 @@ class ClockSampler:
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
+
+    def mark(self):
+        """Samples from here on count: nvidia-smi was started earlier only so that its start-up
+        time does not eat the timed region."""
+        self.first = len(self.rows)
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -105,6 +110,7 @@ class ClockSampler:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        self.rows = self.rows[self.first:]
         sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
         out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": None, "reasons": [], "samples": len(sm)}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -362,6 +368,8 @@ def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, ba
     from rvllm_b200.stack import DecodeStack
 
     c = dict(cfg, batch=B)
+    if sampler:
+        sampler.start()   # started early (it needs a few hundred ms to produce its first line); counted from mark()
     stack = DecodeStack(c, weights)
     g = np.random.default_rng(3)
     prompt = g.integers(0, c["vocab"], (B, c["prompt_len"]), dtype=np.int32)
@@ -375,7 +383,7 @@ def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, ba
     if barrier:
         barrier()
     if sampler:
-        sampler.start()
+        sampler.mark()
     if profiler_range:
         torch.cuda.profiler.start()
     sec = time_steps(torch, stack, steps)
