@@ -153,17 +153,27 @@ int rvllm_fused_act_mul_fp8_quant_launch(uint32_t num_tokens, uint32_t intermedi
     uint8_t* o = (uint8_t*)out_fp8;
     int I = (int)intermediate;
     // Few long rows (a decode batch): spread each row over a cluster of CTAs.  Same bytes and scales.
-    const uint32_t cl = num_tokens <= 128 ? 8u : (num_tokens <= 256 ? 4u : (num_tokens <= 512 ? 2u : 1u));
-    if (cl > 1 && intermediate >= 4096 && num_tokens <= 65535) {
+    // The kernel is one latency chain per CTA (load, meet the cluster, store), so what matters is that all
+    // CTAs are resident at once: about 512 CTAs at 4 per SM, however many rows share them.  From about
+    // 100 rows on, one CTA of 1024 threads per row (one wave up to 148 rows) is as fast or faster.
+    const uint32_t cl = num_tokens <= 64 ? 8u : (num_tokens <= 96 ? 4u : 1u);
+    if (cl > 1 && intermediate >= 4096) {
         dim3 cgrid(cl, num_tokens), cblock(rvact::CLUSTER_THREADS), cdim(cl, 1, 1);
-        if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16)
-            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_SILU, __half>, cgrid, cblock, 0, s, cdim, o, scale, (const __half*)gate_up, I);
-        else if (act == RVLLM_ACT_SILU)
-            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_SILU, __nv_bfloat16>, cgrid, cblock, 0, s, cdim, o, scale, (const __nv_bfloat16*)gate_up, I);
-        else if (dtype == RVLLM_F16)
-            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_GELU, __half>, cgrid, cblock, 0, s, cdim, o, scale, (const __half*)gate_up, I);
-        else
-            rv_launch(rvact::act_mul_quant_cluster_kernel<rvact::ACT_GELU, __nv_bfloat16>, cgrid, cblock, 0, s, cdim, o, scale, (const __nv_bfloat16*)gate_up, I);
+        const bool roomy = cl * num_tokens <= 3u * 128u;  // resident at 3 CTAs per SM: keep the wider register cache
+#define RV_ACT_CLUSTER(ACT, T)                                                                                         \
+    do {                                                                                                               \
+        if (roomy)                                                                                                     \
+            rv_launch(rvact::act_mul_quant_cluster_kernel<ACT, T, 4, 3>, cgrid, cblock, 0, s, cdim, o, scale,          \
+                      (const T*)gate_up, I);                                                                           \
+        else                                                                                                           \
+            rv_launch(rvact::act_mul_quant_cluster_kernel<ACT, T, 3, 4>, cgrid, cblock, 0, s, cdim, o, scale,          \
+                      (const T*)gate_up, I);                                                                           \
+    } while (0)
+        if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16) RV_ACT_CLUSTER(rvact::ACT_SILU, __half);
+        else if (act == RVLLM_ACT_SILU) RV_ACT_CLUSTER(rvact::ACT_SILU, __nv_bfloat16);
+        else if (dtype == RVLLM_F16) RV_ACT_CLUSTER(rvact::ACT_GELU, __half);
+        else RV_ACT_CLUSTER(rvact::ACT_GELU, __nv_bfloat16);
+#undef RV_ACT_CLUSTER
         return rv_launched("fused_act_mul_fp8_quant (cluster)");
     }
     if (act == RVLLM_ACT_SILU && dtype == RVLLM_F16)

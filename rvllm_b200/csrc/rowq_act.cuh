@@ -113,10 +113,12 @@ __device__ __forceinline__ void act_mul_quant_row(uint8_t* __restrict__ out, flo
 // one above, so bytes and scales are identical to the one-CTA-per-row kernel.
 // Geometry: grid = (CL, num_tokens), cluster = (CL, 1, 1), block = CLUSTER_THREADS.
 constexpr int CLUSTER_THREADS = 256;
-constexpr int CLUSTER_CACHE_VECS = 4;  // slices up to 4 * 256 * 8 = 8192 elements stay in registers
-
-template <int ACT, typename T>
-__global__ void __launch_bounds__(CLUSTER_THREADS)
+// CLUSTER_CACHE_VECS 16-byte pieces of the slice stay in registers between the two passes (the rest is
+// read again); MINB CTAs per SM are asked of the compiler.  Two forms are launched: (4, 3) when the
+// whole grid is resident anyway (at most 3 CTAs per SM), (3, 4) when a fourth CTA per SM lets a larger
+// grid run as one wave -- the kernel is one latency chain per CTA, so a second wave doubles its time.
+template <int ACT, typename T, int CLUSTER_CACHE_VECS, int MINB>
+__global__ void __launch_bounds__(CLUSTER_THREADS, MINB)
 act_mul_quant_cluster_kernel(uint8_t* __restrict__ out, float* __restrict__ scales, const T* __restrict__ gate_up, int inter) {
     namespace cg = cooperative_groups;
     __shared__ float red[33];

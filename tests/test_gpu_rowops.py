@@ -232,7 +232,8 @@ def test_quantize_and_add_variant_bit_exact_vs_reference_kernel(orc):
 @pytest.mark.parametrize("dtype,suffix", [(0, "_kernel"), (1, "_bf16_kernel")])
 @pytest.mark.parametrize("act,stem,sym", [(0, "fused_silu_fp8_quant", "fused_silu_mul_fp8_quant"),
                                           (1, "fused_gelu_mul_fp8_quant", "fused_gelu_mul_fp8_quant")])
-@pytest.mark.parametrize("tokens,inter", [(32, 21504), (3, 73728), (130, 4096), (300, 8200)])
+@pytest.mark.parametrize("tokens,inter", [(32, 21504), (3, 73728), (64, 21504), (96, 21504), (80, 40960),
+                                          (130, 4096), (300, 8200)])
 def test_act_mul_quant_cluster_launch_equals_one_cta_per_row(orc, dtype, suffix, act, stem, sym, tokens, inter):
     """The C launcher spreads each row of a small batch over a cluster of CTAs; the PTX entry point
     keeps the reference geometry of one CTA per row.  Bytes and scale bits must be identical,
