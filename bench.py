@@ -235,6 +235,7 @@ def run_reference_arm(args, cfg):
     if rank != 0:
         return
     orc.build()
+    orc.use_all_host_threads()  # a torchrun worker inherits OMP_NUM_THREADS=1
     B = args.batch
     times = []
     per_step = max(0.3, min(4.0, 150.0 / (args.warmup + args.steps)))  # the whole run stays within a few minutes
@@ -479,6 +480,7 @@ def run_gpu_arm(args, cfg):
         if world == 1 and not args.no_cpu_baseline:
             import oracle as orc
             orc.build()
+            orc.use_all_host_threads()
             est, spent, desc = cpu_step_sample(cfg, B, ctx=cfg["prompt_len"], min_seconds=12.0)
             line["cpu_baseline"] = {"value": B / est, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
                                     "sample": desc, "sample_seconds": spent}

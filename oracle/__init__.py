@@ -265,3 +265,12 @@ def embedding_gather(table16, token_ids):
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def use_all_host_threads() -> int:
+    """Run the parallel loops on every CPU this process may use, whatever OMP_NUM_THREADS says
+    (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers).  Returns the thread count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_threads(int(n))
+    return num_threads()

@@ -836,3 +836,12 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Worker threads of the parallel loops from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -94,3 +94,19 @@ def test_rope_kv_write_matches_numpy(orc):
     assert ksc.reshape(slots, kvh)[7].all() and not ksc.reshape(slots, kvh)[8].any()  # slot -1 skipped
     v = x[:, (heads + kvh) * hd:].reshape(T, kvh, hd)
     assert np.abs(orc.e4m3_decode(vc[30]) * vsc.reshape(slots, kvh)[30][:, None] - v[2]).max() <= 0.07 * np.abs(v[2]).max()
+
+
+def test_thread_count_override_survives_launcher_env():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the timed CPU arm asks for
+    every CPU the process may use instead."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = "import oracle as o; a = o.num_threads(); b = o.use_all_host_threads(); print(a, b)"
+    env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    before, after = map(int, out.stdout.split())
+    assert before == 1
+    assert after == len(os.sched_getaffinity(0))
