@@ -11,6 +11,7 @@
 #include "host_util.h"
 // the PTX-module translation units double as this library's kernels
 #include "greedy_argmax.cu"
+#include "greedy_argmax_cluster.cuh"
 #include "rope_kv_write.cu"
 #include "rowq_gelu.cu"
 #include "rowq_rmsnorm.cu"
@@ -206,6 +207,10 @@ int rvllm_argmax_launch(uint32_t num_tokens, uint32_t vocab, const float* logits
             return rv_fail(RVLLM_E_LAUNCH, "cudaMemsetAsync(out) failed");
         dim3 grid((vocab + 1023) / 1024, num_tokens), block(256);
         rv_launch(argmax_grid_f32_kernel, dim3(grid), dim3(block), 0, s, dim3(1, 1, 1), logits, out, (int)vocab);
+    } else if (vocab >= 32768 && num_tokens <= 64) {
+        // few long rows: eight CTAs per row (same winner, see greedy_argmax_cluster.cuh)
+        dim3 cgrid(8, num_tokens), cblock(rvargmax::ARGMAX_CLUSTER_THREADS), cdim(8, 1, 1);
+        rv_launch(rvargmax::argmax_cluster_f32_kernel, cgrid, cblock, 0, s, cdim, logits, out, (int)vocab);
     } else {
         uint32_t b = 1;
         while (b * 2 <= rv_umin(vocab, 1024)) b *= 2;  // min(vocab, 1024) rounded down to a power of two

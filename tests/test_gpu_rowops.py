@@ -151,7 +151,7 @@ def test_act_mul_quant_nonfinite_row_gives_nan_scale(orc):
 
 # --------------------------------------------------------------------------- stage 4
 @pytest.mark.parametrize("grid", [False, True])
-@pytest.mark.parametrize("tokens,vocab", [(4, 2048), (32, 262144), (1, 262144), (3, 1000), (2, 5)])
+@pytest.mark.parametrize("tokens,vocab", [(4, 2048), (32, 262144), (1, 262144), (3, 1000), (2, 5), (5, 32770), (3, 40001)])
 def test_argmax_exact(orc, grid, tokens, vocab):
     from rvllm_b200.launchers import ArgmaxLaunch
     g = np.random.default_rng(vocab + tokens)
@@ -182,6 +182,21 @@ def test_argmax_all_nan_row(orc):
     out = torch.zeros(2, dtype=torch.int32, device="cuda")
     ArgmaxLaunch(2, 4096).launch(x, out)
     assert out.cpu().numpy().tolist() == [-1, 77]
+
+
+def test_argmax_long_rows_edge_candidates(orc):
+    """Rows long enough for the launcher to spread each over a cluster: no candidate at all, a single
+    candidate in the last element, and a tie between the first and the last slice."""
+    from rvllm_b200.launchers import ArgmaxLaunch
+    vocab = 65538
+    x = np.full((4, vocab), np.nan, np.float32)
+    x[1, vocab - 1] = -np.inf
+    x[2, :] = -1.0
+    x[2, 3] = x[2, vocab - 2] = 9.0
+    x[3, :] = 0.0
+    out = torch.full((4,), -7, dtype=torch.int32, device="cuda")
+    ArgmaxLaunch(4, vocab).launch(torch.from_numpy(x).cuda(), out)
+    assert out.cpu().numpy().tolist() == [-1, vocab - 1, 3, 0] == orc.argmax_f32(x, orc.MODE_CUDA).tolist()
 
 
 # --------------------------------------------------------------------------- reference kernels, same GPU
