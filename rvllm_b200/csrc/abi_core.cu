@@ -207,9 +207,10 @@ int rvllm_argmax_launch(uint32_t num_tokens, uint32_t vocab, const float* logits
             return rv_fail(RVLLM_E_LAUNCH, "cudaMemsetAsync(out) failed");
         dim3 grid((vocab + 1023) / 1024, num_tokens), block(256);
         rv_launch(argmax_grid_f32_kernel, dim3(grid), dim3(block), 0, s, dim3(1, 1, 1), logits, out, (int)vocab);
-    } else if (vocab >= 32768 && num_tokens <= 64) {
-        // few long rows: eight CTAs per row (same winner, see greedy_argmax_cluster.cuh)
-        dim3 cgrid(8, num_tokens), cblock(rvargmax::ARGMAX_CLUSTER_THREADS), cdim(8, 1, 1);
+    } else if (vocab >= 32768 && num_tokens <= 192) {
+        // few long rows: eight CTAs per row (same winner, see greedy_argmax_cluster.cuh); 1024 threads while
+        // two such CTAs per SM hold the whole grid, 512 beyond (four per SM)
+        dim3 cgrid(8, num_tokens), cblock(num_tokens <= 32 ? rvargmax::ARGMAX_CLUSTER_THREADS : 512), cdim(8, 1, 1);
         rv_launch(rvargmax::argmax_cluster_f32_kernel, cgrid, cblock, 0, s, cdim, logits, out, (int)vocab);
     } else {
         uint32_t b = 1;

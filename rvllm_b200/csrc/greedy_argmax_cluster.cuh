@@ -4,7 +4,7 @@
 // lowest index on ties, NaN never a candidate, -1 for a row without candidates.  A decode batch has a
 // few dozen rows of about 1 MB each; one CTA per row leaves most SMs idle and streams at a fraction
 // of the HBM rate, eight CTAs per row read the same bytes as one short burst.
-// Geometry: grid = (CL, num_tokens), cluster = (CL, 1, 1), block = ARGMAX_CLUSTER_THREADS.
+// Geometry: grid = (CL, num_tokens), cluster = (CL, 1, 1), block = a multiple of 32 up to ARGMAX_CLUSTER_THREADS.
 #pragma once
 #include <cooperative_groups.h>
 
