@@ -48,12 +48,6 @@ extern "C" {
 int rvllm_b200_abi_version(void);          /* = 1 */
 const char* rvllm_b200_last_error(void);   /* thread-local; "" when no error */
 const char* rvllm_b200_build_arch(void);   /* "sm_100a" */
-/* Programmatic dependent launch: when enabled (the default) every kernel is launched with the
- * programmatic-stream-serialization attribute, so the next kernel on the stream may start its
- * prologue and weight prefetch while the current one drains; every kernel waits for its
- * predecessor before touching dependent data.  Process-wide; set it before recording graphs. */
-void rvllm_b200_set_pdl(int enabled);
-int rvllm_b200_get_pdl(void);
 
 /* ---- 1. fused RMSNorm + per-token FP8 quantisation ----------------------------------
  * Replaces FusedRmsnormFp8QuantLaunch / FusedAddRmsnormFp8QuantLaunch /
@@ -127,9 +121,6 @@ size_t rvllm_fp8_gemm_workspace(int M, int N, int K);
  * (site << 16 | CTA) of the first wait that ran out.  Synchronous (copies from the device);
  * for tests and diagnosis, not for the decode loop.  reset != 0 clears it. */
 int rvllm_fp8_gemm_tc_status(int* status, int reset);
-/* Overrides of the tcgen05 kernel's automatic choices, for tuning runs: TMA ring depth
- * (2..8) and split-K factor (1..8); 0 restores the automatic choice.  Process-wide. */
-void rvllm_fp8_gemm_tc_tune(int stages, int splits);
 /* QKV projection with RoPE, per-(token, head) Q quantisation and the paged FP8 K/V write (per-(slot,
  * kv_head) scales) done in the GEMM's epilogue: the result of rvllm_fp8_gemm_channelscale into a
  * [M, (heads + 2*kv_heads)*128] 16-bit buffer followed by rvllm_rope_fp8kv_launch with rotary_dim =
@@ -150,12 +141,6 @@ int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const fl
 int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const float* amax_partials, int amax_parts,
                                    const void* w_fp8, const float* w_scale, const void* residual, int M, int N, int K,
                                    void* stream);
-/* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
- * CTA's receive buffer when the batch tile has at most 32 rows and the cluster meets once, else they
- * are pulled out of the peers' rings), 1 always pull, 2 push with point-to-point mbarrier arrivals
- * instead of the cluster barrier (measured within 1 % of form 0; kept as a cross-check).  All forms
- * sum in cluster-rank order, so their results are bitwise equal (tested). */
-void rvllm_fp8_gemm_tc_reduce(int mode);
 
 /* gate|up projection + act(gate)*up + per-token FP8 re-quantisation in one call
  * (reference: GEMM at layer_exec.rs:484-494 followed by FusedSiluMulFp8QuantLaunch :509).
@@ -200,22 +185,14 @@ int rvllm_paged_decode_fp8_validate(int batch_size, int num_heads, int num_kv_he
                                     int window_size_left, float scale);
 uint64_t rvllm_paged_decode_workspace_size(int batch_size, int num_heads, int num_kv_heads, int head_dim);
 int rvllm_paged_decode_max_chunks(int batch_size, int num_kv_heads);
-/* Overrides for tuning runs (0 restores the default): CTAs the grid aims for, the fewest tokens
- * worth a chunk of their own, and the main-kernel variant (1 = both products on the FP32 pipes,
- * 2 = scores on mma.sync FP8 tensor cores and P.V on the FP32 pipes, 3 = both products on mma.sync,
- * 4 = tcgen05 / TMEM / TMA; 0 picks 4 where the shape allows it, else 3, else 2).
- * Process-wide; the workspace query and the launch always use the same values. */
-void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant);
 /* Variant 4 is the tcgen05 / TMA main kernel (head_dim 128 or 256, at most 8 query heads per KV
  * head, pages of 8..128 tokens that divide 128).  Its waits on mbarriers are bounded; this reads
  * (and optionally clears) the word that records the first wait that gave up: 0 = none. */
 int rvllm_paged_decode_tc_status(int* status, int reset);
-/* Which main kernel (1-4, as in rvllm_paged_decode_tune) a launch of this shape runs under the
- * current settings; negative on bad arguments. */
+/* Which main kernel a launch of this shape runs (1 = both products on the FP32 pipes, 2 = scores on
+ * mma.sync FP8 tensor cores and P.V on the FP32 pipes, 3 = both products on mma.sync, 4 = tcgen05 /
+ * TMEM / TMA: 4 where the shape allows it, else 3, else 2); negative on bad arguments. */
 int rvllm_paged_decode_kernel_for(int num_heads, int num_kv_heads, int head_dim, int block_size, int num_blocks_total);
-/* Depth of the tcgen05 kernel's K/V ring in 16 KB units (2..8 for head_dim 128, 3..8 for 256);
- * 0 restores the automatic choice.  Tuning aid, process-wide. */
-void rvllm_paged_decode_ring(int units);
 int rvllm_paged_decode_fp8(const void* q_fp8, const void* k_cache_fp8, const void* v_cache_fp8, void* output,
                            int out_dtype, const int32_t* block_tables, const int32_t* context_lens,
                            void* workspace, size_t workspace_bytes, const float* k_scale_cache,
@@ -286,6 +263,43 @@ int rvllm_rope_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in
                             int num_cache_slots, int dtype, void* stream);
 int rvllm_embedding_gather_launch(void* out, const void* table, const int32_t* token_ids, int num_tokens,
                                   int hidden, int vocab, void* stream);
+
+/* Llama-form RoPE (interleaved pairs 2t, 2t+1 over the whole head) + FP8 Q + paged FP8 K/V write with the
+ * static per-tensor scales *q_scale_ptr / *kv_scale_ptr: FusedRopeCacheFp8KvLaunch
+ * (v3/crates/rvllm-fused/src/launcher.rs:577-712; kernel v3/kernels/fused_rope_cache_fp8kv.cu:20-101; call
+ * site v3/crates/rvllm-runtime/src/layer_exec.rs:297).  Same validation (head_dim 128/256/512, heads a
+ * multiple of kv_heads) and geometry (grid tokens x max(heads, kv_heads), block max(head_dim/2, 32)); the
+ * inputs carry a row stride in elements so the packed QKV output is consumed in place.  A position outside
+ * [0, max_positions) or a non-positive scale writes nothing; a slot outside [0, num_cache_slots) skips the
+ * cache write, as in the reference kernel. */
+int rvllm_rope_cache_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in, int in_stride, void* q_fp8,
+                                  void* k_cache, void* v_cache, const void* cos_table, const void* sin_table,
+                                  const int32_t* positions, const int32_t* slot_mapping, const float* q_scale_ptr,
+                                  const float* kv_scale_ptr, int num_tokens, int num_heads, int num_kv_heads, int head_dim,
+                                  int max_positions, int num_cache_slots, int dtype, void* stream);
+
+/* ---- 6b. Gemma-4 layer decorations and the greedy tail's soft cap --------------------------------
+ * Per-head RMSNorm of the packed QKV projection output into compact Q / K / V buffers (learned gain on Q
+ * and K, none on V): FusedQkvRmsnormLaunch (v3/crates/rvllm-fused/src/gemma4_launcher.rs:178-246; kernel
+ * v3/kernels/fused_qkv_rmsnorm.cu:28-130; call site v3/crates/rvllm-runtime/src/gemma4_layer_exec.rs:754-789).
+ * grid (tokens, heads + 2*kv_heads), block min(head_dim, 1024). */
+int rvllm_fused_qkv_rmsnorm_launch(const void* q_in, const void* k_in, const void* v_in, void* q_out, void* k_out,
+                                   void* v_out, const void* q_gamma, const void* k_gamma, int num_tokens, int num_heads,
+                                   int num_kv_heads, int head_dim, float eps, int src_row_stride, int dtype,
+                                   void* stream);
+/* Post-norm folded into the residual update: residual = (residual + rmsnorm(x) * gamma) * layer_scalar, x
+ * being the GEMM's f32 output times its per-channel scales (gemm_out_is_f32 != 0: FusedNormAddResidualF16Launch,
+ * gemma4_launcher.rs:784-822, kernel v3/kernels/fused_norm_add_residual_f16.cu:8-58) or its 16-bit output
+ * (gemm_out_is_f32 == 0, channelscale ignored: FusedNormAddResidualF16InLaunch :888-923, kernel :67-116).
+ * layer_scalar may be NULL (= 1).  Call sites gemma4_layer_exec.rs:1200-1235.  grid tokens, block min(hidden, 1024). */
+int rvllm_fused_norm_add_residual_launch(const void* gemm_out, int gemm_out_is_f32, const float* channelscale,
+                                         const void* gamma, void* residual, const void* layer_scalar, int num_tokens,
+                                         int hidden, float eps, int dtype, void* stream);
+/* residual *= *scalar (ResidualScaleF16Launch, gemma4_launcher.rs:572-616; v3/kernels/residual_scale_f16.cu:13-27). */
+int rvllm_residual_scale_launch(void* residual, const void* scalar, int num_tokens, int hidden, int dtype, void* stream);
+/* logits = cap * tanh(logits / cap) in place on 16-bit logits (LogitSoftcapLaunch, gemma4_launcher.rs:953-996;
+ * v3/kernels/logit_softcap.cu:12-31; call site v3/crates/rvllm-runtime/src/gemma4_bring_up.rs:2144-2151). */
+int rvllm_logit_softcap_launch(void* logits, int num_tokens, int vocab, float cap, int dtype, void* stream);
 
 /* FP8 encode / decode of a flat array with the kernels' own convert instructions
  * (used by the bit-exactness tests; not on the decode path). */

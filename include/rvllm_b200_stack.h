@@ -44,6 +44,10 @@ typedef struct {
     float rms_eps;
     float rope_theta;
     uint64_t seed;       /* shuffles the physical block order of the block tables */
+    int kv_pool_blocks;  /* 0: every sequence owns max_context tokens of every global layer's cache.  > 0: the
+                            global layers share a pool of this many blocks per layer, dealt out per sequence by
+                            need (a ragged batch: rvllm_stack_seed_contexts); sliding layers always keep their
+                            fixed ring of sliding_window tokens per sequence */
 } rvllm_stack_config;
 
 typedef struct {
@@ -83,9 +87,15 @@ int rvllm_stack_reset(rvllm_stack* s, const int32_t* prompt_tokens);
  * with constant bytes and scales instead of being produced by `context` decode steps.  The
  * kernels then do the work of a step at that context length without the prefill run. */
 int rvllm_stack_seed_context(rvllm_stack* s, int context);
+/* The same with one context length per sequence (host [batch] int32, each in [0, max_context)): a ragged
+ * batch.  With kv_pool_blocks > 0 the pool is dealt out so that sequence b can reach position
+ * contexts[b] + max_steps; RVLLM_E_INVALID if the pool is too small. */
+int rvllm_stack_seed_contexts(rvllm_stack* s, const int32_t* contexts);
 
 /* Enqueue `n` decode steps (graph replays) on the stack's stream; returns without waiting.
- * rvllm_stack_sync waits for them. */
+ * rvllm_stack_sync waits for them.  A run that would take any sequence past max_context is refused
+ * with RVLLM_E_INVALID before anything is launched (so are the eager and the host-buffer forms); the
+ * emitted-token history keeps the first max_steps steps after a reset and drops later ones. */
 int rvllm_stack_run(rvllm_stack* s, int n);
 int rvllm_stack_sync(rvllm_stack* s);
 /* Same steps launched kernel by kernel without the graph (for debugging and as a check that

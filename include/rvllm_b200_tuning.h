@@ -1,0 +1,53 @@
+/*
+ * rvllm_b200 — tuning and diagnostic hooks.  NOT part of the drop-in ABI.
+ *
+ * The reference boundary allows no mutable process state behind the kernel entry points
+ * (v3/crates/rvllm-cutlass/src/lib_so.rs:139-191 binds plain functions).  Everything in
+ * rvllm_b200.h honours that: with the hooks below left alone, a launch depends on its arguments
+ * only.  The hooks exist for sweeps and for tests that force one kernel form against another.
+ * They set process-wide atomics: a launch running on another thread sees the old or the new value.
+ * A workspace query and the launch it sizes must not straddle a change, and graphs record the
+ * choice in force at capture time.  A production host never calls them.
+ */
+#ifndef RVLLM_B200_TUNING_H
+#define RVLLM_B200_TUNING_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Programmatic dependent launch: when enabled (the default) every kernel is launched with the
+ * programmatic-stream-serialization attribute, so the next kernel on the stream may start its
+ * prologue and weight prefetch while the current one drains; every kernel waits for its
+ * predecessor before touching dependent data.  Process-wide; set it before recording graphs. */
+void rvllm_b200_set_pdl(int enabled);
+int rvllm_b200_get_pdl(void);
+
+/* Overrides of the tcgen05 kernel's automatic choices, for tuning runs: TMA ring depth
+ * (2..8) and split-K factor (1..8); 0 restores the automatic choice.  Process-wide. */
+void rvllm_fp8_gemm_tc_tune(int stages, int splits);
+/* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
+ * CTA's receive buffer when the batch tile has at most 32 rows and the cluster meets once, else they
+ * are pulled out of the peers' rings), 1 always pull, 2 push with point-to-point mbarrier arrivals
+ * instead of the cluster barrier (measured within 1 % of form 0; kept as a cross-check).  All forms
+ * sum in cluster-rank order, so their results are bitwise equal (tested). */
+void rvllm_fp8_gemm_tc_reduce(int mode);
+
+/* Overrides for tuning runs (0 restores the default): CTAs the grid aims for, the fewest tokens
+ * worth a chunk of their own, and the main-kernel variant (1 = both products on the FP32 pipes,
+ * 2 = scores on mma.sync FP8 tensor cores and P.V on the FP32 pipes, 3 = both products on mma.sync,
+ * 4 = tcgen05 / TMEM / TMA; 0 picks 4 where the shape allows it, else 3, else 2).
+ * Process-wide; the workspace query and the launch always use the same values. */
+void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant);
+/* Depth of the tcgen05 kernel's K/V ring in 16 KB units (2..8 for head_dim 128, 3..8 for 256);
+ * 0 restores the automatic choice.  Tuning aid, process-wide. */
+void rvllm_paged_decode_ring(int units);
+
+/* Host-only self-test of the per-device "set up once" bookkeeping that guards cudaFuncSetAttribute
+ * (the attribute belongs to a device, not to the process).  Touches no CUDA API; 0 = pass. */
+int rvllm_b200_selftest_device_once(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RVLLM_B200_TUNING_H */

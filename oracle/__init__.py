@@ -263,6 +263,65 @@ def embedding_gather(table16, token_ids):
     return out
 
 
+
+# --------------------------------------------------------------------------- Gemma-4 decorations
+def qkv_rmsnorm(qkv16, q_gamma16, k_gamma16, heads, kv_heads, head_dim, eps, dtype=F16, block_dim=None):
+    """Packed rows [T, stride >= (heads + 2*kv_heads)*head_dim] -> compact (q, k, v) 16-bit bit patterns."""
+    T, stride = qkv16.shape
+    if block_dim is None:
+        block_dim = max(32, min(head_dim, 1024) // 32 * 32)
+    q = np.empty((T, heads, head_dim), np.uint16)
+    k = np.empty((T, kv_heads, head_dim), np.uint16)
+    v = np.empty((T, kv_heads, head_dim), np.uint16)
+    _chk(lib().orc_qkv_rmsnorm(_p(q), _p(k), _p(v), _p(qkv16), _p(q_gamma16), _p(k_gamma16), T, heads, kv_heads,
+                               head_dim, C.c_float(eps), stride, dtype, block_dim), "qkv_rmsnorm")
+    return q, k, v
+
+
+def norm_add_residual(residual16, gemm_out, gamma16, eps, channelscale=None, layer_scalar16=None, dtype=F16,
+                      block_dim=None):
+    """residual = (residual + rmsnorm(x) * gamma) * layer_scalar; gemm_out f32 (with channelscale) or 16-bit bits.
+    Returns the new residual (the input is not modified)."""
+    T, H = residual16.shape
+    if block_dim is None:
+        block_dim = max(32, min(H, 1024) // 32 * 32)
+    out = residual16.copy()
+    f32 = gemm_out if gemm_out.dtype == np.float32 else None
+    b16 = gemm_out if gemm_out.dtype == np.uint16 else None
+    _chk(lib().orc_norm_add_residual(_p(out), _p(f32), _p(b16), _p(channelscale), _p(gamma16), _p(layer_scalar16),
+                                     T, H, C.c_float(eps), dtype, block_dim), "norm_add_residual")
+    return out
+
+
+def residual_scale(residual16, scalar16, dtype=F16):
+    out = residual16.copy()
+    _chk(lib().orc_residual_scale(_p(out), _p(scalar16), C.c_size_t(out.size), dtype), "residual_scale")
+    return out
+
+
+def logit_softcap(logits16, cap, dtype=F16):
+    out = logits16.copy()
+    _chk(lib().orc_logit_softcap(_p(out), C.c_size_t(out.size), C.c_float(cap), dtype), "logit_softcap")
+    return out
+
+
+def rope_cache_fp8kv(qkv16, heads, kv_heads, head_dim, cos16, sin16, positions, slot_mapping, k_cache, v_cache,
+                     q_scale, kv_scale, dtype=F16, q_fp8=None):
+    """Llama-form RoPE on packed rows [T, (heads + 2*kv_heads)*head_dim]; caches updated in place; returns q_fp8."""
+    T, stride = qkv16.shape
+    q_dim, kv_dim = heads * head_dim, kv_heads * head_dim
+    flat = qkv16.reshape(-1)
+    if q_fp8 is None:
+        q_fp8 = np.zeros((T, heads, head_dim), np.uint8)
+    base = flat.ctypes.data
+    slots = k_cache.size // (kv_heads * head_dim) if kv_heads else 0
+    _chk(lib().orc_rope_cache_fp8kv(C.c_void_p(base), C.c_void_p(base + 2 * q_dim), C.c_void_p(base + 2 * (q_dim + kv_dim)),
+                                    C.c_longlong(stride), C.c_longlong(stride), _p(q_fp8), _p(k_cache), _p(v_cache),
+                                    _p(cos16), _p(sin16), _p(positions), _p(slot_mapping), C.c_float(q_scale),
+                                    C.c_float(kv_scale), T, heads, kv_heads, head_dim, cos16.shape[0], slots, dtype),
+         "rope_cache_fp8kv")
+    return q_fp8
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

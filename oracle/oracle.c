@@ -829,6 +829,173 @@ int orc_embedding_gather(uint16_t *out, const uint16_t *table, const int *token_
     return 0;
 }
 
+/* ------------------------------------------------------------------------- */
+/* Gemma-4 decorations, soft cap, Llama-form RoPE                             */
+/* ------------------------------------------------------------------------- */
+
+/* fused_qkv_rmsnorm_kernel, v3/kernels/fused_qkv_rmsnorm.cu:28-130, for a launch of
+ * block_dim threads: thread-strided sum of squares (:99-103, contracted to fma by the
+ * device compiler), shuffle-down tree per warp (lane 0 holds the total; the pairing is
+ * the xor butterfly's), the same tree over the warp totals, rsqrt(ss/head_dim + eps),
+ * out = f16(x * rms [* gamma]) (:124-128).  qkv: packed rows [tokens][src_row_stride];
+ * outputs compact [tokens][heads][head_dim].  1/sqrtf stands in for the device rsqrtf. */
+int orc_qkv_rmsnorm(uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, const uint16_t *qkv,
+                    const uint16_t *q_gamma, const uint16_t *k_gamma, int num_tokens,
+                    int num_heads, int num_kv_heads, int head_dim, float eps,
+                    int src_row_stride, int dtype, int block_dim) {
+    if (num_tokens <= 0 || num_heads <= 0 || num_kv_heads < 0 || head_dim <= 0 || !qkv || !q_out) return -1;
+    if (block_dim < 32 || block_dim > 1024 || block_dim % 32) return -1;
+    if (!(eps > 0.0f) || !isfinite(eps)) return -1;
+    int total = num_heads + 2 * num_kv_heads;
+    if ((long long)src_row_stride < (long long)total * head_dim) return -1;
+    float partial[1024];
+    for (int t = 0; t < num_tokens; t++)
+        for (int hg = 0; hg < total; hg++) {
+            const uint16_t *gamma = NULL;
+            uint16_t *dst;
+            long long src_off;
+            if (hg < num_heads) {
+                gamma = q_gamma;
+                src_off = (long long)hg * head_dim;
+                dst = q_out + ((size_t)t * num_heads + hg) * head_dim;
+            } else if (hg < num_heads + num_kv_heads) {
+                int hl = hg - num_heads;
+                gamma = k_gamma;
+                src_off = (long long)(num_heads + hl) * head_dim;
+                dst = k_out + ((size_t)t * num_kv_heads + hl) * head_dim;
+            } else {
+                int hl = hg - num_heads - num_kv_heads;
+                src_off = (long long)(num_heads + num_kv_heads + hl) * head_dim;
+                dst = v_out + ((size_t)t * num_kv_heads + hl) * head_dim;
+            }
+            const uint16_t *src = qkv + (size_t)t * src_row_stride + src_off;
+            for (int i = 0; i < block_dim; i++) partial[i] = 0.0f;
+            for (int i = 0; i < head_dim; i++) {
+                float a = orc_h2f(src[i], dtype);
+                partial[i % block_dim] = fmaf(a, a, partial[i % block_dim]);
+            }
+            float ss = block_sum_ref_order(partial, block_dim);
+            float rms = 1.0f / sqrtf(ss / (float)head_dim + eps);
+            for (int i = 0; i < head_dim; i++) {
+                float v = orc_h2f(src[i], dtype) * rms;
+                if (gamma) v *= orc_h2f(gamma[i], dtype);
+                dst[i] = orc_f2h(v, dtype);
+            }
+        }
+    return 0;
+}
+
+/* fused_norm_add_residual_f16_kernel / _f16in_kernel,
+ * v3/kernels/fused_norm_add_residual_f16.cu:8-58,67-116: x = gemm_out * channelscale
+ * (f32 input) or the 16-bit GEMM output; thread-strided sum of squares, xor butterfly
+ * per warp, warp totals added in warp order by thread 0 (:45-50); residual =
+ * f16((residual + x * rms * gamma) * layer_scalar).  The device compiler contracts
+ * residual + (x*rms)*gamma into one fma. */
+int orc_norm_add_residual(uint16_t *residual, const float *gemm_f32, const uint16_t *gemm_16,
+                          const float *channelscale, const uint16_t *gamma,
+                          const uint16_t *layer_scalar, int num_tokens, int hidden, float eps,
+                          int dtype, int block_dim) {
+    if (num_tokens <= 0 || hidden <= 0 || !residual || !gamma || (!gemm_f32 && !gemm_16)) return -1;
+    if (gemm_f32 && !channelscale) return -1;
+    if (block_dim < 32 || block_dim > 1024 || block_dim % 32) return -1;
+    if (!(eps > 0.0f) || !isfinite(eps)) return -1;
+    float partial[1024];
+    float *x = (float *)malloc(sizeof(float) * (size_t)hidden);
+    float ls = layer_scalar ? orc_h2f(layer_scalar[0], dtype) : 1.0f;
+    for (int t = 0; t < num_tokens; t++) {
+        for (int i = 0; i < block_dim; i++) partial[i] = 0.0f;
+        for (int i = 0; i < hidden; i++) {
+            float a = gemm_f32 ? gemm_f32[(size_t)t * hidden + i] * channelscale[i]
+                               : orc_h2f(gemm_16[(size_t)t * hidden + i], dtype);
+            x[i] = a;
+            partial[i % block_dim] = fmaf(a, a, partial[i % block_dim]);
+        }
+        int nw = (block_dim + 31) / 32;
+        float total = 0.0f;
+        for (int w = 0; w < nw; w++) {
+            float v[32];
+            for (int l = 0; l < 32; l++) v[l] = partial[w * 32 + l];
+            for (int off = 16; off > 0; off >>= 1) {
+                float nv[32];
+                for (int l = 0; l < 32; l++) nv[l] = v[l] + v[l ^ off];
+                memcpy(v, nv, sizeof v);
+            }
+            total += v[0];
+        }
+        float rms = 1.0f / sqrtf(total / (float)hidden + eps);
+        uint16_t *res = residual + (size_t)t * hidden;
+        for (int i = 0; i < hidden; i++) {
+            float r = fmaf(x[i] * rms, orc_h2f(gamma[i], dtype), orc_h2f(res[i], dtype));
+            res[i] = orc_f2h(r * ls, dtype);
+        }
+    }
+    free(x);
+    return 0;
+}
+
+/* residual_scale_f16_kernel, v3/kernels/residual_scale_f16.cu:13-27. */
+int orc_residual_scale(uint16_t *residual, const uint16_t *scalar, size_t n, int dtype) {
+    if (!residual || !scalar) return -1;
+    float s = orc_h2f(scalar[0], dtype);
+    for (size_t i = 0; i < n; i++) residual[i] = orc_f2h(orc_h2f(residual[i], dtype) * s, dtype);
+    return 0;
+}
+
+/* logit_softcap_kernel, v3/kernels/logit_softcap.cu:12-31: cap * tanhf(x * (1/cap)). */
+int orc_logit_softcap(uint16_t *logits, size_t n, float cap, int dtype) {
+    if (!logits || !(cap > 0.0f) || !isfinite(cap)) return -1;
+    float inv = 1.0f / cap;
+    for (size_t i = 0; i < n; i++) logits[i] = orc_f2h(cap * tanhf(orc_h2f(logits[i], dtype) * inv), dtype);
+    return 0;
+}
+
+/* fused_rope_cache_fp8kv_kernel, v3/kernels/fused_rope_cache_fp8kv.cu:20-101:
+ * interleaved pairs (2t, 2t+1) over the whole head, cos/sin [max_positions][head_dim/2],
+ * static scales; q' = (q0*c - q1*s, q0*s + q1*c) * (1/q_scale) (the device compiler
+ * contracts a*b - c*d into fma(a, b, -(c*d)) and a*b + c*d into fma(a, b, c*d)); K
+ * rotated and V unrotated into the paged cache times 1/kv_scale.  A bad position or
+ * scale writes nothing; a slot outside the cache skips the cache write. */
+int orc_rope_cache_fp8kv(const uint16_t *q_in, const uint16_t *k_in, const uint16_t *v_in,
+                         long long q_stride, long long kv_stride, uint8_t *q_fp8, uint8_t *k_cache,
+                         uint8_t *v_cache, const uint16_t *cos_t, const uint16_t *sin_t,
+                         const int *positions, const int *slot_mapping, float q_scale,
+                         float kv_scale, int num_tokens, int heads, int kv_heads, int head_dim,
+                         int max_positions, int num_cache_slots, int dtype) {
+    if (!q_in || !q_fp8 || !positions || num_tokens <= 0 || heads <= 0 || kv_heads < 0 ||
+        head_dim <= 0 || head_dim % 2 || max_positions <= 0 || !cos_t || !sin_t) return -1;
+    if (!isfinite(q_scale) || q_scale <= 0.0f) return 0;
+    if (kv_heads > 0 && (!isfinite(kv_scale) || kv_scale <= 0.0f)) return 0;
+    float q_inv = 1.0f / q_scale, kv_inv = kv_heads > 0 ? 1.0f / kv_scale : 0.0f;
+    int half = head_dim / 2;
+    for (int t = 0; t < num_tokens; t++) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_positions) continue;
+        for (int p = 0; p < half; p++) {
+            float c = orc_h2f(cos_t[(size_t)pos * half + p], dtype);
+            float s = orc_h2f(sin_t[(size_t)pos * half + p], dtype);
+            for (int h = 0; h < heads; h++) {
+                const uint16_t *src = q_in + (size_t)t * q_stride + (size_t)h * head_dim + 2 * p;
+                float a = orc_h2f(src[0], dtype), b = orc_h2f(src[1], dtype);
+                uint8_t *o = q_fp8 + ((size_t)t * heads + h) * head_dim + 2 * p;
+                o[0] = orc_e4m3_encode(fmaf(a, c, -(b * s)) * q_inv, 1);
+                o[1] = orc_e4m3_encode(fmaf(a, s, b * c) * q_inv, 1);
+            }
+            int slot = kv_heads > 0 ? slot_mapping[t] : -1;
+            if (slot < 0 || slot >= num_cache_slots) continue;
+            for (int h = 0; h < kv_heads; h++) {
+                size_t in_off = (size_t)t * kv_stride + (size_t)h * head_dim + 2 * p;
+                float a = orc_h2f(k_in[in_off], dtype), b = orc_h2f(k_in[in_off + 1], dtype);
+                size_t off = ((size_t)slot * kv_heads + h) * head_dim + 2 * p;
+                k_cache[off] = orc_e4m3_encode(fmaf(a, c, -(b * s)) * kv_inv, 1);
+                k_cache[off + 1] = orc_e4m3_encode(fmaf(a, s, b * c) * kv_inv, 1);
+                v_cache[off] = orc_e4m3_encode(orc_h2f(v_in[in_off], dtype) * kv_inv, 1);
+                v_cache[off + 1] = orc_e4m3_encode(orc_h2f(v_in[in_off + 1], dtype) * kv_inv, 1);
+            }
+        }
+    }
+    return 0;
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

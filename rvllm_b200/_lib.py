@@ -41,6 +41,7 @@ SIGNATURES = {
     "rvllm_b200_build_arch": (C.c_char_p, []),
     "rvllm_b200_set_pdl": (None, [_i32]),
     "rvllm_b200_get_pdl": (_i32, []),
+    "rvllm_b200_selftest_device_once": (_i32, []),
     "rvllm_fused_rmsnorm_fp8_quant_validate": (_i32, [_u32, _u32, _f32]),
     "rvllm_fused_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _i32, _vp]),
     "rvllm_fused_add_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),
@@ -86,6 +87,11 @@ SIGNATURES = {
     "rvllm_paged_decode_static_scratch_bytes": (_sz, []),
     "rvllm_paged_decode_fp8_static_scratch": (_i32, [_vp] * 4 + [_i32] + [_vp] * 2 + [_vp] * 6 + [_f32] + [_i32] * 8 + [_vp]),
     "rvllm_rope_fp8kv_launch": (_i32, [_vp, _vp, _vp, _i32] + [_vp] * 10 + [_i32] * 8 + [_vp]),
+    "rvllm_rope_cache_fp8kv_launch": (_i32, [_vp, _vp, _vp, _i32] + [_vp] * 9 + [_i32] * 7 + [_vp]),
+    "rvllm_fused_qkv_rmsnorm_launch": (_i32, [_vp] * 8 + [_i32] * 4 + [_f32, _i32, _i32, _vp]),
+    "rvllm_fused_norm_add_residual_launch": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _i32, _vp]),
+    "rvllm_residual_scale_launch": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
+    "rvllm_logit_softcap_launch": (_i32, [_vp, _i32, _i32, _f32, _i32, _vp]),
     "rvllm_embedding_gather_launch": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "rvllm_e4m3_encode_f32": (_i32, [_vp, _vp, _sz, _vp]),
     "rvllm_e4m3_decode_f32": (_i32, [_vp, _vp, _sz, _vp]),

@@ -36,7 +36,14 @@ PTX_MODULES = {
     "fused_gelu_mul_fp8_quant": "rowq_gelu.cu",
     "argmax": "greedy_argmax.cu",
     "embedding_gather_f16": "rope_kv_write.cu",
+    "fused_rope_partial_fp8kv": "rope_kv_write.cu",
     "flash_attention": "fa2_decode_fp8kv.cu",
+    # Gemma-4 decorations, soft cap and the Llama-form RoPE: one source, the reference's five module names
+    "fused_qkv_rmsnorm": "rowq_gemma.cu",
+    "fused_norm_add_residual_f16": "rowq_gemma.cu",
+    "residual_scale_f16": "rowq_gemma.cu",
+    "logit_softcap": "rowq_gemma.cu",
+    "fused_rope_cache_fp8kv": "rowq_gemma.cu",
 }
 REVISION = "b200f8e4d0c1"
 

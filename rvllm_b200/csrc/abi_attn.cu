@@ -3,16 +3,21 @@
 #include <math.h>
 
 #include "../../include/rvllm_b200.h"
+#include "../../include/rvllm_b200_tuning.h"
+#include <atomic>
 #include <mutex>
 
 #include "host_util.h"
 #include "paged_decode_fp8_tc.cuh"
 #include "paged_decode_fp8_umma.cuh"
 
-static int g_target_ctas = rvattn::TARGET_CTAS;
-static int g_min_chunk_tokens = rvattn::MIN_CHUNK_TOKENS;
-static int g_ring_units = 0;  // tcgen05 kernel: K/V ring depth in 16 KB units, 0 = automatic
-static int g_variant = 0;  // 0 automatic (tcgen05 kernel where the shape allows, else 3, else 2), 1 FP32-pipe kernel,
+// Tuning overrides (declared in rvllm_b200_tuning.h).  Atomics: a setter racing a launch on another thread
+// yields the old or the new value, never a torn one; a workspace query and its launch must still not
+// straddle a change.
+static std::atomic<int> g_target_ctas{rvattn::TARGET_CTAS};
+static std::atomic<int> g_min_chunk_tokens{rvattn::MIN_CHUNK_TOKENS};
+static std::atomic<int> g_ring_units{0};  // tcgen05 kernel: K/V ring depth in 16 KB units, 0 = automatic
+static std::atomic<int> g_variant{0};  // 0 automatic (tcgen05 kernel where the shape allows, else 3, else 2), 1 FP32-pipe kernel,
                            // 2 mma.sync scores + FP32-pipe P.V, 3 both products on mma.sync, 4 tcgen05 / TMA
 
 extern "C" {
@@ -112,13 +117,11 @@ int launch_umma(const rvattn::Params& p, cudaStream_t s) {
             return rv_fail(RVLLM_E_LAUNCH, "cuTensorMapEncodeTiled failed for the KV cache");
         auto kern = rvua::paged_decode_fp8_umma_kernel<HD, GT, OutT>;
         using C = rvua::Cfg<HD>;
-        static bool attr_set = false;  // per kernel instantiation
-        if (!attr_set) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(rvua::MAX_UNITS)) != cudaSuccess)
-                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
-            attr_set = true;
-        }
-        int units = g_ring_units > 0 ? g_ring_units : rvua::pick_units<HD>((long long)p.kv_heads * p.max_chunks * p.batch);
+        static RvDeviceOnce smem_once;  // per kernel instantiation and device
+        if (rv_allow_smem(smem_once, kern, C::smem_bytes(rvua::MAX_UNITS)))
+            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
+        const int ring = g_ring_units.load();
+        int units = ring > 0 ? ring : rvua::pick_units<HD>((long long)p.kv_heads * p.max_chunks * p.batch);
         if (units < C::MIN_UNITS) units = C::MIN_UNITS;
         if (units > rvua::MAX_UNITS) units = rvua::MAX_UNITS;
         rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)C::smem_bytes(units), s,
@@ -152,35 +155,26 @@ int launch_attn(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
     } else if (g_variant == 1) {
         auto kern = rvattn::paged_decode_fp8_kernel<HD, GT, OutT>;
         const size_t smem = rvattn::smem_bytes(HD, GT);
-        static bool attr_set = false;  // per kernel instantiation
-        if (smem > 48 * 1024 && !attr_set) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
-            attr_set = true;
-        }
+        static RvDeviceOnce smem_once;  // per kernel instantiation and device
+        if (smem > 48 * 1024 && rv_allow_smem(smem_once, kern, (int)smem))
+            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
         rv_launch(kern, grid, dim3(rvattn::THREADS), smem, s, dim3(1, 1, 1), p);
     } else if (g_variant != 2 && HD <= 256 &&
                (long long)p.num_blocks_total * p.block_size * p.kv_heads < (1ll << 31)) {
         if constexpr (HD <= 256) {
             auto kern = rvattn::paged_decode_fp8_tc_kernel<HD, GT, OutT>;
             const size_t smem = rvattn::tc_smem_bytes(HD, GT);
-            static bool attr_set = false;  // per kernel instantiation
-            if (smem > 48 * 1024 && !attr_set) {
-                if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                    return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
-                attr_set = true;
-            }
+            static RvDeviceOnce smem_once;  // per kernel instantiation and device
+            if (smem > 48 * 1024 && rv_allow_smem(smem_once, kern, (int)smem))
+                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
             rv_launch(kern, grid, dim3(rvattn::MMA_THREADS), smem, s, dim3(1, 1, 1), p);
         }
     } else {
         auto kern = rvattn::paged_decode_fp8_mma_kernel<HD, GT, OutT>;
         const size_t smem = rvattn::mma_smem_bytes(HD, GT);
-        static bool attr_set = false;  // per kernel instantiation
-        if (smem > 48 * 1024 && !attr_set) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
-            attr_set = true;
-        }
+        static RvDeviceOnce smem_once;  // per kernel instantiation and device
+        if (smem > 48 * 1024 && rv_allow_smem(smem_once, kern, (int)smem))
+            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
         rv_launch(kern, grid, dim3(rvattn::MMA_THREADS), smem, s, dim3(1, 1, 1), p);
     }
     int rc = rv_launched("paged_decode_fp8");
@@ -188,12 +182,9 @@ int launch_attn(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
     if (qo.fp8) {
         auto qk = rvattn::paged_decode_fp8_combine_quant_kernel<HD, OutT>;
         const size_t qsmem = (size_t)p.heads * HD * sizeof(float);
-        static bool qattr = false;
-        if (qsmem > 48 * 1024 && !qattr) {
-            if (cudaFuncSetAttribute(qk, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
-                return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the attention quant pass");
-            qattr = true;
-        }
+        static RvDeviceOnce q_once;
+        if (qsmem > 48 * 1024 && rv_allow_smem(q_once, qk, 160 * 1024))
+            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the attention quant pass");
         if (qsmem > 160 * 1024) return rv_fail(RVLLM_E_UNSUPPORTED, "heads * head_dim too large for the fused quant pass");
         rv_launch(qk, dim3(p.batch), dim3(512), qsmem, s, dim3(1, 1, 1), (const float*)p.workspace, qo.fp8, qo.scale,
                   (const int*)p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq, p.window_size_left,

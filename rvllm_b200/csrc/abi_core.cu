@@ -7,13 +7,17 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "../../include/rvllm_b200.h"
+#include "../../include/rvllm_b200_tuning.h"
 #include "host_util.h"
 // the PTX-module translation units double as this library's kernels
 #include "greedy_argmax.cu"
 #include "greedy_argmax_cluster.cuh"
 #include "rope_kv_write.cu"
 #include "rowq_gelu.cu"
+#include "rowq_gemma.cu"
 #include "rowq_rmsnorm.cu"
 #include "rowq_silu.cu"
 
@@ -43,9 +47,9 @@ int rv_launched(const char* what) {
     }
     return RVLLM_OK;
 }
-static bool g_pdl = true;
-bool rv_pdl_enabled() { return g_pdl; }
-void rv_set_pdl(bool on) { g_pdl = on; }
+static std::atomic<bool> g_pdl{true};
+bool rv_pdl_enabled() { return g_pdl.load(std::memory_order_relaxed); }
+void rv_set_pdl(bool on) { g_pdl.store(on, std::memory_order_relaxed); }
 
 namespace rvhost {
 int fail_msg(int code, const char* msg) { return rv_fail(code, "%s", msg); }
@@ -58,6 +62,22 @@ const char* rvllm_b200_last_error(void) { return g_err; }
 const char* rvllm_b200_build_arch(void) { return "sm_100a"; }
 void rvllm_b200_set_pdl(int enabled) { rv_set_pdl(enabled != 0); }
 int rvllm_b200_get_pdl(void) { return rv_pdl_enabled() ? 1 : 0; }
+
+int rvllm_b200_selftest_device_once(void) {
+    RvDeviceOnce once;
+    int calls = 0;
+    auto ok = [&]() { calls++; return 0; };
+    auto bad = [&]() { calls++; return -1; };
+    if (once.seen(0) || once.seen(1)) return 1;
+    if (once.run(0, ok) != 0 || calls != 1 || !once.seen(0) || once.seen(1)) return 2;   // first use of device 0
+    if (once.run(0, ok) != 0 || calls != 1) return 3;                                    // remembered
+    if (once.run(1, bad) != -1 || calls != 2 || once.seen(1)) return 4;                  // a failure is not remembered
+    if (once.run(1, ok) != 0 || calls != 3 || !once.seen(1)) return 5;                   // device 1 has its own flag
+    if (once.run(70, ok) != 0 || calls != 4 || !once.seen(70) || once.seen(6)) return 6; // second word of the table
+    if (once.run(-1, ok) != 0 || once.run(-1, ok) != 0 || calls != 6) return 7;          // unknown device: every time
+    if (once.run(RvDeviceOnce::MAX_DEVICES, ok) != 0 || calls != 7) return 8;
+    return 0;
+}
 
 // ---------------------------------------------------------------- stage 1
 int rvllm_fused_rmsnorm_fp8_quant_validate(uint32_t num_tokens, uint32_t hidden, float eps) {
@@ -250,6 +270,128 @@ int rvllm_rope_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in
             (const __nv_bfloat16*)cos_table, (const __nv_bfloat16*)sin_table, positions, slot_mapping, num_tokens,
             num_heads, num_kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
     return rv_launched("rope_fp8kv");
+}
+
+// ---------------------------------------------------------------- Gemma-4 decorations, greedy tail
+static inline uint32_t block_for(uint32_t width) { return round_block(rv_umin(width, 1024)); }
+
+int rvllm_fused_qkv_rmsnorm_launch(const void* q_in, const void* k_in, const void* v_in, void* q_out, void* k_out,
+                                   void* v_out, const void* q_gamma, const void* k_gamma, int num_tokens, int num_heads,
+                                   int num_kv_heads, int head_dim, float eps, int src_row_stride, int dtype,
+                                   void* stream) {
+    if (num_tokens <= 0 || num_heads <= 0 || num_kv_heads < 0 || head_dim <= 0)
+        return rv_fail(RVLLM_E_INVALID, "bad token / head counts");
+    if (!isfinite(eps) || eps <= 0.0f) return rv_fail(RVLLM_E_INVALID, "eps must be finite and > 0");
+    if ((long long)src_row_stride < ((long long)num_heads + 2LL * num_kv_heads) * head_dim)
+        return rv_fail(RVLLM_E_INVALID, "src_row_stride is shorter than one packed QKV row");
+    if (!q_in || !q_out || !q_gamma || (num_kv_heads > 0 && (!k_in || !v_in || !k_out || !v_out || !k_gamma)))
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (q_in == q_out || (num_kv_heads > 0 && (k_in == k_out || v_in == v_out)))
+        return rv_fail(RVLLM_E_INVALID, "in-place QKV norm is not supported (outputs are compact, inputs packed)");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens, num_heads + 2 * num_kv_heads), block(block_for((uint32_t)head_dim));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        rv_launch(fused_qkv_rmsnorm_kernel, grid, block, 0, s, dim3(1, 1, 1), (const __half*)q_in, (const __half*)k_in,
+                  (const __half*)v_in, (__half*)q_out, (__half*)k_out, (__half*)v_out, (const __half*)q_gamma,
+                  (const __half*)k_gamma, num_tokens, num_heads, num_kv_heads, head_dim, eps, src_row_stride);
+    else
+        rv_launch(fused_qkv_rmsnorm_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)q_in,
+                  (const __nv_bfloat16*)k_in, (const __nv_bfloat16*)v_in, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out,
+                  (__nv_bfloat16*)v_out, (const __nv_bfloat16*)q_gamma, (const __nv_bfloat16*)k_gamma, num_tokens,
+                  num_heads, num_kv_heads, head_dim, eps, src_row_stride);
+    return rv_launched("fused_qkv_rmsnorm");
+}
+
+int rvllm_fused_norm_add_residual_launch(const void* gemm_out, int gemm_out_is_f32, const float* channelscale,
+                                         const void* gamma, void* residual, const void* layer_scalar, int num_tokens,
+                                         int hidden, float eps, int dtype, void* stream) {
+    if (num_tokens <= 0 || hidden <= 0) return rv_fail(RVLLM_E_INVALID, "num_tokens and hidden must be > 0");
+    if (!isfinite(eps) || eps <= 0.0f) return rv_fail(RVLLM_E_INVALID, "eps must be finite and > 0");
+    if (!gemm_out || !gamma || !residual || (gemm_out_is_f32 && !channelscale))
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens), block(block_for((uint32_t)hidden));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gemm_out_is_f32) {
+        if (dtype == RVLLM_F16)
+            rv_launch(fused_norm_add_residual_f16_kernel, grid, block, 0, s, dim3(1, 1, 1), (const float*)gemm_out,
+                      channelscale, (const __half*)gamma, (__half*)residual, (const __half*)layer_scalar, hidden, eps);
+        else
+            rv_launch(fused_norm_add_residual_f16_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1), (const float*)gemm_out,
+                      channelscale, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)residual,
+                      (const __nv_bfloat16*)layer_scalar, hidden, eps);
+    } else {
+        if (dtype == RVLLM_F16)
+            rv_launch(fused_norm_add_residual_f16in_kernel, grid, block, 0, s, dim3(1, 1, 1), (const __half*)gemm_out,
+                      (const __half*)gamma, (__half*)residual, (const __half*)layer_scalar, hidden, eps);
+        else
+            rv_launch(fused_norm_add_residual_f16in_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1),
+                      (const __nv_bfloat16*)gemm_out, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)residual,
+                      (const __nv_bfloat16*)layer_scalar, hidden, eps);
+    }
+    return rv_launched("fused_norm_add_residual");
+}
+
+int rvllm_residual_scale_launch(void* residual, const void* scalar, int num_tokens, int hidden, int dtype, void* stream) {
+    if (num_tokens <= 0 || hidden <= 0) return rv_fail(RVLLM_E_INVALID, "num_tokens and hidden must be > 0");
+    if (!residual || !scalar) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens), block(block_for((uint32_t)hidden));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        rv_launch(residual_scale_f16_kernel, grid, block, 0, s, dim3(1, 1, 1), (__half*)residual, (const __half*)scalar, hidden);
+    else
+        rv_launch(residual_scale_f16_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1), (__nv_bfloat16*)residual,
+                  (const __nv_bfloat16*)scalar, hidden);
+    return rv_launched("residual_scale");
+}
+
+int rvllm_logit_softcap_launch(void* logits, int num_tokens, int vocab, float cap, int dtype, void* stream) {
+    if (num_tokens <= 0 || vocab <= 0) return rv_fail(RVLLM_E_INVALID, "zero dim");          // gemma4_launcher.rs:960-963
+    if (!isfinite(cap) || cap <= 0.0f) return rv_fail(RVLLM_E_INVALID, "cap must be > 0");   // :964-966
+    if (!logits) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens), block(block_for((uint32_t)vocab));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        rv_launch(logit_softcap_kernel, grid, block, 0, s, dim3(1, 1, 1), (__half*)logits, vocab, cap);
+    else
+        rv_launch(logit_softcap_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1), (__nv_bfloat16*)logits, vocab, cap);
+    return rv_launched("logit_softcap");
+}
+
+int rvllm_rope_cache_fp8kv_launch(const void* q_in, const void* k_in, const void* v_in, int in_stride, void* q_fp8,
+                                  void* k_cache, void* v_cache, const void* cos_table, const void* sin_table,
+                                  const int32_t* positions, const int32_t* slot_mapping, const float* q_scale_ptr,
+                                  const float* kv_scale_ptr, int num_tokens, int num_heads, int num_kv_heads, int head_dim,
+                                  int max_positions, int num_cache_slots, int dtype, void* stream) {
+    if (num_tokens <= 0 || num_heads <= 0 || num_kv_heads < 0) return rv_fail(RVLLM_E_INVALID, "bad token / head counts");
+    if (head_dim != 128 && head_dim != 256 && head_dim != 512)                                  // launcher.rs:598-603
+        return rv_fail(RVLLM_E_INVALID, "head_dim must be 128, 256 or 512");
+    if (num_kv_heads > 0 && num_heads % num_kv_heads != 0)
+        return rv_fail(RVLLM_E_INVALID, "num_heads must be a multiple of num_kv_heads");
+    if (max_positions <= 0 || (num_kv_heads > 0 && num_cache_slots <= 0) || in_stride <= 0) return rv_fail(RVLLM_E_INVALID, "bad sizes");
+    if (!q_in || !q_fp8 || !cos_table || !sin_table || !positions || !q_scale_ptr ||
+        (num_kv_heads > 0 && (!k_in || !v_in || !k_cache || !v_cache || !slot_mapping || !kv_scale_ptr)))
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (!rv_aligned(q_in, 4) || (num_kv_heads > 0 && (!rv_aligned(k_in, 4) || !rv_aligned(v_in, 4))) || (in_stride & 1))
+        return rv_fail(RVLLM_E_INVALID, "q / k / v rows must be 4-byte aligned");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid(num_tokens, num_heads > num_kv_heads ? num_heads : num_kv_heads), block(rv_umax(head_dim / 2, 32));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        rv_launch(rvllm_rope_cache_fp8kv_strided_kernel, grid, block, 0, s, dim3(1, 1, 1), (const __half*)q_in,
+                  (const __half*)k_in, (const __half*)v_in, in_stride, (uint8_t*)q_fp8, (uint8_t*)k_cache,
+                  (uint8_t*)v_cache, (const __half*)cos_table, (const __half*)sin_table, positions, slot_mapping,
+                  q_scale_ptr, kv_scale_ptr, num_tokens, num_heads, num_kv_heads, head_dim, max_positions, num_cache_slots);
+    else
+        rv_launch(rvllm_rope_cache_fp8kv_strided_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)q_in,
+                  (const __nv_bfloat16*)k_in, (const __nv_bfloat16*)v_in, in_stride, (uint8_t*)q_fp8, (uint8_t*)k_cache,
+                  (uint8_t*)v_cache, (const __nv_bfloat16*)cos_table, (const __nv_bfloat16*)sin_table, positions,
+                  slot_mapping, q_scale_ptr, kv_scale_ptr, num_tokens, num_heads, num_kv_heads, head_dim, max_positions,
+                  num_cache_slots);
+    return rv_launched("rope_cache_fp8kv");
 }
 
 int rvllm_embedding_gather_launch(void* out, const void* table, const int32_t* token_ids, int num_tokens,

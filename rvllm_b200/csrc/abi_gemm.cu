@@ -3,6 +3,7 @@
 #include <math.h>
 
 #include "../../include/rvllm_b200.h"
+#include "../../include/rvllm_b200_tuning.h"
 #include "host_util.h"
 #include "fp8_gemm_stream.cuh"
 #include "fp8_gemm_tc.cuh"
@@ -40,12 +41,9 @@ template <int NT8, int EPI, typename OutT>
 int launch_stream_one(const rvgemm::StreamParams& p, int splits, int mblocks, cudaStream_t s) {
     auto kern = rvgemm::fp8_gemm_stream_kernel<NT8, EPI, OutT>;
     const size_t smem = (size_t)rvgemm::K_WARPS * NT8 * 8 * rvgemm::TILE_N * sizeof(float);
-    static bool attr_set = false;  // per kernel instantiation; set once so graph capture sees launches only
-    if (smem > 48 * 1024 && !attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the streaming GEMM");
-        attr_set = true;
-    }
+    static RvDeviceOnce smem_once;  // per kernel instantiation and device; set once so graph capture sees launches only
+    if (smem > 48 * 1024 && rv_allow_smem(smem_once, kern, (int)smem))
+        return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for the streaming GEMM");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.N + rvgemm::TILE_N - 1) / rvgemm::TILE_N, splits, mblocks);
     cfg.blockDim = dim3(rvgemm::THREADS);

@@ -48,7 +48,8 @@ __global__ void prepare_step_kernel(const int* __restrict__ positions, const int
     if (b >= batch) return;
     const int pos = positions[b];
     const int page = pos / block_size, off = pos % block_size;
-    slots_global[b] = page < mb_global ? tables_global[b * mb_global + page] * block_size + off : -1;
+    const int blk = page < mb_global ? tables_global[b * mb_global + page] : -1;  // -1: no block dealt to this page
+    slots_global[b] = blk >= 0 ? blk * block_size + off : -1;
     slots_sliding[b] = mb_sliding > 0 ? tables_sliding[b * mb_sliding + page % mb_sliding] * block_size + off : -1;
     ctx_lens[b] = pos + 1;
 }
@@ -115,6 +116,7 @@ struct rvllm_stack {
     cudaGraphExec_t exec = nullptr;
     int launches = 0;
     int steps_done = 0;
+    int start_pos = 0;  // largest position any sequence had after the last reset / seeding (host-side copy)
     // one arena; everything below points into it
     uint8_t* arena = nullptr;
     size_t arena_bytes = 0;
@@ -161,6 +163,7 @@ int validate_cfg(const rvllm_stack_config* c) {
     if (!isfinite(c->rms_eps) || c->rms_eps < 0 || !isfinite(c->rope_theta) || c->rope_theta <= 1.0f)
         return rv_fail(RVLLM_E_INVALID, "bad eps / rope theta");
     if (c->gemm_impl < 0 || c->gemm_impl > 2) return rv_fail(RVLLM_E_INVALID, "gemm_impl must be 0, 1 or 2");
+    if (c->kv_pool_blocks < 0) return rv_fail(RVLLM_E_INVALID, "kv_pool_blocks must be >= 0");
     return RVLLM_OK;
 }
 
@@ -193,7 +196,8 @@ size_t layout(rvllm_stack* s, uint8_t* base) {
         L.kv_dim = c.kv_heads * L.head_dim;
         L.qkv_n = L.q_dim + 2 * L.kv_dim;
         L.max_blocks = L.global ? s->mb_global : s->mb_sliding;
-        L.num_blocks = B * L.max_blocks;
+        // a global layer's physical blocks: one full table per sequence, or the shared pool of a ragged batch
+        L.num_blocks = (L.global && c.kv_pool_blocks > 0) ? c.kv_pool_blocks : B * L.max_blocks;
         L.window_left = L.global ? -1 : c.sliding_window - 1;
         max_q = L.q_dim > max_q ? L.q_dim : max_q;
         max_qkv = L.qkv_n > max_qkv ? L.qkv_n : max_qkv;
@@ -384,6 +388,40 @@ unsigned long long coprime_multiplier(unsigned long long seed, unsigned long lon
     return m;
 }
 
+
+// Deals the global layers' block pool out to the sequences.  need[b] = blocks sequence b may touch (NULL: an
+// equal share each).  Physical ids come from a seeded shuffle of the pool; table entries past a sequence's
+// share are -1 (no slot: the KV write of such a position is skipped, as for any negative slot).
+int assign_pool_blocks(rvllm_stack* s, const int* need) {
+    const rvllm_stack_config& c = s->cfg;
+    const int B = c.batch, mb = s->mb_global, pool = c.kv_pool_blocks;
+    std::vector<int> table((size_t)B * mb, -1), perm((size_t)pool);
+    for (int i = 0; i < pool; i++) perm[i] = i;
+    unsigned long long x = c.seed * 0x9E3779B97F4A7C15ull + 0xD1B54A32D192ED03ull;
+    for (int i = pool - 1; i > 0; i--) {  // Fisher-Yates with a splitmix-style stream
+        x += 0x9E3779B97F4A7C15ull;
+        unsigned long long z = x;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const int j = (int)(z % (unsigned long long)(i + 1));
+        const int t = perm[i];
+        perm[i] = perm[j];
+        perm[j] = t;
+    }
+    long long used = 0;
+    for (int b = 0; b < B; b++) {
+        int n = need ? need[b] : pool / B;
+        if (n > mb) n = mb;
+        if (used + n > pool) return rv_fail(RVLLM_E_INVALID, "the KV block pool (%d blocks) is too small for this batch", pool);
+        for (int p = 0; p < n; p++) table[(size_t)b * mb + p] = perm[(size_t)used + p];
+        used += n;
+    }
+    RV_TRY(cuda_ok(cudaMemcpyAsync(s->tables_global, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice,
+                                   s->stream), "upload block tables"));
+    return cuda_ok(cudaStreamSynchronize(s->stream), "upload block tables");  // `table` must outlive the copy
+}
+
 }  // namespace
 
 extern "C" {
@@ -430,8 +468,15 @@ int rvllm_stack_create(rvllm_stack** out, const rvllm_stack_config* cfg, const r
     cudaMemsetAsync(s->arena, 0, s->arena_bytes, s->stream);
     // block tables: shuffled physical order, one table per cache layout
     const unsigned long long ng = (unsigned long long)cfg->batch * s->mb_global;
-    fill_tables_kernel<<<64, 256, 0, s->stream>>>(s->tables_global, (int)ng, coprime_multiplier(cfg->seed, ng),
-                                                  cfg->seed % ng);
+    int pool_rc = RVLLM_OK;
+    if (cfg->kv_pool_blocks > 0) {
+        // ragged batch: every sequence gets an equal share of the pool until rvllm_stack_seed_contexts deals
+        // the blocks out by need
+        pool_rc = assign_pool_blocks(s, nullptr);
+    } else {
+        fill_tables_kernel<<<64, 256, 0, s->stream>>>(s->tables_global, (int)ng, coprime_multiplier(cfg->seed, ng),
+                                                      cfg->seed % ng);
+    }
     if (s->mb_sliding > 0) {
         const unsigned long long nsl = (unsigned long long)cfg->batch * s->mb_sliding;
         fill_tables_kernel<<<64, 256, 0, s->stream>>>(s->tables_sliding, (int)nsl,
@@ -445,7 +490,7 @@ int rvllm_stack_create(rvllm_stack** out, const rvllm_stack_config* cfg, const r
         rope_table_kernel<__nv_bfloat16><<<(mp * hs + 255) / 256, 256, 0, s->stream>>>((__nv_bfloat16*)s->cos_s, (__nv_bfloat16*)s->sin_s, mp, hs, cfg->rope_theta);
         rope_table_kernel<__nv_bfloat16><<<(mp * hg + 255) / 256, 256, 0, s->stream>>>((__nv_bfloat16*)s->cos_g, (__nv_bfloat16*)s->sin_g, mp, hg, cfg->rope_theta);
     }
-    rc = rv_launched("stack set-up kernels");
+    rc = pool_rc != RVLLM_OK ? pool_rc : rv_launched("stack set-up kernels");
     if (rc == RVLLM_OK) rc = cuda_ok(cudaStreamSynchronize(s->stream), "stack set-up");
     // One eager step sets every function attribute and tensor map before capture; its effects
     // are wiped by the reset below.
@@ -497,13 +542,31 @@ int rvllm_stack_reset(rvllm_stack* s, const int32_t* prompt_tokens) {
         cudaMemsetAsync(s->prompt, 0, sizeof(int) * (size_t)c.batch * c.prompt_len, s->stream);
     }
     s->steps_done = 0;
+    s->start_pos = 0;
     return cuda_ok(cudaStreamSynchronize(s->stream), "reset");
 }
 
-int rvllm_stack_seed_context(rvllm_stack* s, int context) {
-    if (!s || context < 0 || context >= s->cfg.max_context) return rv_fail(RVLLM_E_INVALID, "bad seeded context");
+static int seed_common(rvllm_stack* s, const int32_t* contexts, int uniform) {
     const rvllm_stack_config& c = s->cfg;
     RV_TRY(rvllm_stack_reset(s, nullptr));
+    std::vector<int> pos((size_t)c.batch, uniform), need;
+    int most = uniform;
+    if (contexts)
+        for (int b = 0; b < c.batch; b++) {
+            if (contexts[b] < 0 || contexts[b] >= c.max_context) return rv_fail(RVLLM_E_INVALID, "bad seeded context");
+            pos[b] = contexts[b];
+            most = contexts[b] > most ? contexts[b] : most;
+        }
+    if (c.kv_pool_blocks > 0) {
+        // a sequence may touch positions [0, context + steps still to come): max_steps bounds those
+        need.resize(c.batch);
+        for (int b = 0; b < c.batch; b++) {
+            long long last = (long long)pos[b] + c.max_steps;
+            if (last > c.max_context) last = c.max_context;
+            need[b] = (int)((last + c.block_size - 1) / c.block_size);
+        }
+        RV_TRY(assign_pool_blocks(s, need.data()));
+    }
     for (const LayerState& L : s->ls) {
         const size_t slots = (size_t)L.num_blocks * c.block_size;
         cudaMemsetAsync(L.k_cache, 0x34, slots * L.kv_dim, s->stream);  // 0.75 in E4M3
@@ -511,13 +574,36 @@ int rvllm_stack_seed_context(rvllm_stack* s, int context) {
         fill_f32_kernel<<<256, 256, 0, s->stream>>>(L.k_scale, slots * c.kv_heads, 0.02f);
         fill_f32_kernel<<<256, 256, 0, s->stream>>>(L.v_scale, slots * c.kv_heads, 0.03f);
     }
-    fill_i32_kernel<<<1, 256, 0, s->stream>>>(s->positions, c.batch, context);
     RV_TRY(rv_launched("seed context"));
-    return cuda_ok(cudaStreamSynchronize(s->stream), "seed context");
+    RV_TRY(cuda_ok(cudaMemcpyAsync(s->positions, pos.data(), sizeof(int) * c.batch, cudaMemcpyHostToDevice, s->stream),
+                   "upload positions"));
+    RV_TRY(cuda_ok(cudaStreamSynchronize(s->stream), "seed context"));
+    s->start_pos = most;
+    return RVLLM_OK;
+}
+
+int rvllm_stack_seed_context(rvllm_stack* s, int context) {
+    if (!s || context < 0 || context >= s->cfg.max_context) return rv_fail(RVLLM_E_INVALID, "bad seeded context");
+    return seed_common(s, nullptr, context);
+}
+
+int rvllm_stack_seed_contexts(rvllm_stack* s, const int32_t* contexts) {
+    if (!s || !contexts) return rv_fail(RVLLM_E_INVALID, "bad seeded contexts");
+    return seed_common(s, contexts, 0);
+}
+
+// A step at position p writes slot p of a global layer's cache: positions must stay below max_context, or the
+// write is skipped and attention reads rows that were never written.  Refused before anything is launched.
+static int room_for(rvllm_stack* s, int n) {
+    if ((long long)s->start_pos + s->steps_done + n > s->cfg.max_context)
+        return rv_fail(RVLLM_E_INVALID, "%d more step(s) would pass max_context = %d (position %d now)", n,
+                       s->cfg.max_context, s->start_pos + s->steps_done);
+    return RVLLM_OK;
 }
 
 int rvllm_stack_run(rvllm_stack* s, int n) {
     if (!s || n < 0) return rv_fail(RVLLM_E_INVALID, "bad run arguments");
+    RV_TRY(room_for(s, n));
     for (int i = 0; i < n; i++) RV_TRY(cuda_ok(cudaGraphLaunch(s->exec, s->stream), "graph launch"));
     s->steps_done += n;
     return RVLLM_OK;
@@ -525,6 +611,7 @@ int rvllm_stack_run(rvllm_stack* s, int n) {
 
 int rvllm_stack_run_eager(rvllm_stack* s, int n) {
     if (!s || n < 0) return rv_fail(RVLLM_E_INVALID, "bad run arguments");
+    RV_TRY(room_for(s, n));
     for (int i = 0; i < n; i++) RV_TRY(enqueue_step(s, nullptr));
     s->steps_done += n;
     return RVLLM_OK;
@@ -537,6 +624,7 @@ int rvllm_stack_sync(rvllm_stack* s) {
 
 int rvllm_stack_step_host(rvllm_stack* s, const int32_t* tokens_in, int32_t* tokens_out) {
     if (!s || !tokens_out) return rv_fail(RVLLM_E_INVALID, "bad step arguments");
+    RV_TRY(room_for(s, 1));
     const int B = s->cfg.batch;
     if (tokens_in) {
         memcpy(s->pinned, tokens_in, sizeof(int32_t) * B);

@@ -32,8 +32,11 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
+
+#include "host_util.h"
 
 #include "common.cuh"
 
@@ -766,9 +769,9 @@ inline bool cached_map(CUtensorMap* out, const void* base, int rows, int K, int 
 
 // Experiment hooks (0 = automatic): ring depth and split-K factor.
 struct Tune {
-    int stages = 0;
-    int splits = 0;
-    int reduce = 0;  // 1: force the pull form of the split-K reduction; 2: push form with point-to-point mbarriers
+    std::atomic<int> stages{0};
+    std::atomic<int> splits{0};
+    std::atomic<int> reduce{0};  // 1: force the pull form of the split-K reduction; 2: push form with point-to-point mbarriers
 };
 inline Tune& tune() {
     static Tune t;
@@ -789,14 +792,13 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     if (stages < min_stages) stages = min_stages;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     while (stages > min_stages && C::smem_bytes(stages, push) > 227 * 1024) stages--;
-    static bool attr_set = false;  // per kernel instantiation: allow the largest ring once
-    if (!attr_set) {
+    static RvDeviceOnce smem_once;  // per kernel instantiation and device: allow the largest ring once
+    {
         int most = MAX_STAGES;
         const bool may_push = BN <= 32;  // the largest footprint this instantiation can be launched with
         while (most > C::MIN_STAGES && C::smem_bytes(most, may_push) > 227 * 1024) most--;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(most, may_push)) != cudaSuccess)
+        if (rv_allow_smem(smem_once, kern, C::smem_bytes(most, may_push)))
             return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
-        attr_set = true;
     }
     TcParams p;
     p.a_scale = g.a_scale;
@@ -880,11 +882,12 @@ struct Plan {
 inline Plan plan_for(int M, int N, int K) {
     Plan pl;
     pl.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    pl.splits = tune().splits > 0 ? tune().splits : pick_splits(M, N, K, pl.bn);
+    const int t_splits = tune().splits.load(), t_stages = tune().stages.load();
+    pl.splits = t_splits > 0 ? t_splits : pick_splits(M, N, K, pl.bn);
     pl.kblocks = (K + BK - 1) / BK;
     if (pl.splits > pl.kblocks) pl.splits = pl.kblocks;
     if (pl.splits > 8) pl.splits = 8;
-    pl.stages = tune().stages > 0 ? tune().stages : pick_stages(pl.bn, pl.splits);
+    pl.stages = t_stages > 0 ? t_stages : pick_stages(pl.bn, pl.splits);
     return pl;
 }
 

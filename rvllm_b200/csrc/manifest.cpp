@@ -327,9 +327,18 @@ int rvllm_manifest_load_and_verify(rvllm_manifest** out, const char* manifest_pa
     bool arch_ok = false;
     for (const char* a : archs) arch_ok = arch_ok || m->arch == a;
     if (!arch_ok) return bail("unsupported kernel architecture " + m->arch);
+    // 1..=MAX_ARTIFACTS entries (v3/crates/rvllm-kernels/src/manifest.rs:190-195)
+    if (m->entries.empty() || m->entries.size() > MAX_ARTIFACTS) return bail("artifact count must be in 1..=4096");
     std::string dir = manifest_path;
     size_t slash = dir.rfind('/');
-    m->dir = slash == std::string::npos ? "." : dir.substr(0, slash);
+    dir = slash == std::string::npos ? "." : dir.substr(0, slash);
+    // The manifest directory and every artifact are resolved (symlinks included) and the artifact must
+    // still lie under the resolved directory, as manifest.rs:197-238 does with canonicalize/starts_with.
+    char* root_c = realpath(dir.c_str(), nullptr);
+    if (!root_c) return bail("cannot resolve the manifest directory");
+    m->dir = root_c;
+    free(root_c);
+    uint64_t total_bytes = 0;
     for (auto& kv : m->entries) {
         Entry& e = kv.second;
         const std::string& name = kv.first;
@@ -341,7 +350,15 @@ int rvllm_manifest_load_and_verify(rvllm_manifest** out, const char* manifest_pa
         if (!agree) return bail(name + ": artifact kind, extension, and ABI do not agree");
         if (!path_ok(e.path)) return bail(name + ": path must be relative and stay inside the manifest directory");
         if (e.bytes == 0 || e.bytes > MAX_ARTIFACT_BYTES) return bail(name + ": artifact size out of range");
-        if (!read_bounded(m->dir + "/" + e.path, MAX_ARTIFACT_BYTES, e.data, why)) return bail(name + ": " + why);
+        total_bytes += e.bytes;  // each term <= 512 MiB and at most 4096 terms: cannot overflow
+        if (total_bytes > MAX_ARTIFACT_BYTES * 4) return bail("total artifact bytes exceed release limit");
+        char* real_c = realpath((m->dir + "/" + e.path).c_str(), nullptr);
+        if (!real_c) return bail(name + ": cannot resolve " + e.path);
+        const std::string real = real_c;
+        free(real_c);
+        const std::string prefix = m->dir == "/" ? m->dir : m->dir + "/";
+        if (real.compare(0, prefix.size(), prefix) != 0) return bail(name + ": artifact escapes manifest root");
+        if (!read_bounded(real, MAX_ARTIFACT_BYTES, e.data, why)) return bail(name + ": " + why);
         if (e.data.size() != e.bytes) return bail(name + ": size differs from the manifest");
         if (sha256_hex(e.data.data(), e.data.size()) != e.sha256) return bail(name + ": sha256 differs from the manifest");
     }

@@ -27,13 +27,13 @@ __device__ __forceinline__ float scale_of(float amax) { return isinf(amax) ? CUD
 // and one barrier, so a CTA pays two dependent memory round trips (position -> cos/sin) instead of
 // one per operand.
 template <typename T>
-__device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, const T* v_in, int in_stride,
-                                                uint8_t* q_fp8, uint8_t* k_cache, uint8_t* v_cache,
+__device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, const T* v_in, long long q_stride,
+                                                long long kv_stride, uint8_t* q_fp8, uint8_t* k_cache, uint8_t* v_cache,
                                                 float* k_scale_cache, float* v_scale_cache, float* q_scale_cache,
-                                                const T* cos_t, const T* sin_t, const int* positions,
-                                                const int* slot_mapping, int num_tokens, int heads, int kv_heads,
-                                                int head_dim, int rotary_dim, int max_positions,
-                                                int num_cache_slots) {
+                                                const float* q_scale_ptr, const T* cos_t, const T* sin_t,
+                                                const int* positions, const int* slot_mapping, int num_tokens,
+                                                int heads, int kv_heads, int head_dim, int rotary_dim,
+                                                int max_positions, int num_cache_slots) {
     __shared__ float red[8][3];
     rv::pdl_launch();
     rv::pdl_wait();
@@ -46,13 +46,13 @@ __device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, co
     const bool do_kv = head < kv_heads && slot >= 0 && slot < num_cache_slots;
     float qa = 0.0f, qb = 0.0f, ka = 0.0f, kb = 0.0f, va = 0.0f, vb = 0.0f;
     if (do_q) {
-        const T* row = q_in + (size_t)tok * in_stride + (size_t)head * head_dim;
+        const T* row = q_in + (size_t)tok * q_stride + (size_t)head * head_dim;
         qa = rv::T16<T>::to_f32(row[tid]);
         qb = rv::T16<T>::to_f32(row[tid + half_head]);
     }
     if (do_kv) {
-        const T* krow = k_in + (size_t)tok * in_stride + (size_t)head * head_dim;
-        const T* vrow = v_in + (size_t)tok * in_stride + (size_t)head * head_dim;
+        const T* krow = k_in + (size_t)tok * kv_stride + (size_t)head * head_dim;
+        const T* vrow = v_in + (size_t)tok * kv_stride + (size_t)head * head_dim;
         ka = rv::T16<T>::to_f32(krow[tid]);
         kb = rv::T16<T>::to_f32(krow[tid + half_head]);
         va = rv::T16<T>::to_f32(vrow[tid]);
@@ -84,8 +84,15 @@ __device__ __forceinline__ void rope_fp8kv_body(const T* q_in, const T* k_in, co
         mv = fmaxf(mv, red[w][2]);
     }
     if (do_q) {
-        const float sc = scale_of(mq);
-        if (tid == 0) q_scale_cache[(size_t)tok * heads + head] = sc;
+        // dynamic per-(token, head) scale, or — when the caller keeps no scale cache — the static *q_scale_ptr
+        float sc;
+        if (q_scale_cache) {
+            sc = scale_of(mq);
+            if (tid == 0) q_scale_cache[(size_t)tok * heads + head] = sc;
+        } else {
+            sc = *q_scale_ptr;
+            if (!isfinite(sc) || sc <= 0.0f) sc = CUDART_NAN_F;
+        }
         const float inv = 1.0f / sc;
         uint8_t* o = q_fp8 + ((size_t)tok * heads + head) * head_dim;
         o[tid] = rv::f32_to_e4m3(qlo * inv);
@@ -116,9 +123,9 @@ rvllm_rope_fp8kv_kernel(const __half* q_in, const __half* k_in, const __half* v_
                         float* q_scale_cache, const __half* cos_t, const __half* sin_t, const int* positions,
                         const int* slot_mapping, int num_tokens, int heads, int kv_heads, int head_dim,
                         int rotary_dim, int max_positions, int num_cache_slots) {
-    rope_fp8kv_body<__half>(q_in, k_in, v_in, in_stride, q_fp8, k_cache, v_cache, k_scale_cache, v_scale_cache,
-                            q_scale_cache, cos_t, sin_t, positions, slot_mapping, num_tokens, heads, kv_heads,
-                            head_dim, rotary_dim, max_positions, num_cache_slots);
+    rope_fp8kv_body<__half>(q_in, k_in, v_in, in_stride, in_stride, q_fp8, k_cache, v_cache, k_scale_cache,
+                            v_scale_cache, q_scale_cache, nullptr, cos_t, sin_t, positions, slot_mapping, num_tokens,
+                            heads, kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
 }
 extern "C" __global__ void __launch_bounds__(256)
 rvllm_rope_fp8kv_bf16_kernel(const __nv_bfloat16* q_in, const __nv_bfloat16* k_in, const __nv_bfloat16* v_in,
@@ -127,9 +134,35 @@ rvllm_rope_fp8kv_bf16_kernel(const __nv_bfloat16* q_in, const __nv_bfloat16* k_i
                              const __nv_bfloat16* cos_t, const __nv_bfloat16* sin_t, const int* positions,
                              const int* slot_mapping, int num_tokens, int heads, int kv_heads, int head_dim,
                              int rotary_dim, int max_positions, int num_cache_slots) {
-    rope_fp8kv_body<__nv_bfloat16>(q_in, k_in, v_in, in_stride, q_fp8, k_cache, v_cache, k_scale_cache,
-                                   v_scale_cache, q_scale_cache, cos_t, sin_t, positions, slot_mapping, num_tokens,
-                                   heads, kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
+    rope_fp8kv_body<__nv_bfloat16>(q_in, k_in, v_in, in_stride, in_stride, q_fp8, k_cache, v_cache, k_scale_cache,
+                                   v_scale_cache, q_scale_cache, nullptr, cos_t, sin_t, positions, slot_mapping,
+                                   num_tokens, heads, kv_heads, head_dim, rotary_dim, max_positions, num_cache_slots);
+}
+
+// The reference's own entry point and argument list (v3/kernels/fused_rope_partial_fp8kv.cu:54-76; launcher
+// FusedRopePartialFp8KvLaunch, v3/crates/rvllm-fused/src/gemma4_launcher.rs:248-400): compact
+// [tokens, heads, head_dim] Q and [tokens, kv_heads, head_dim] K / V inputs, and a static Q scale read from
+// q_scale_ptr when q_scale_cache is null.  grid (tokens, max(heads, kv_heads)), block head_dim / 2.
+extern "C" __global__ void __launch_bounds__(256)
+fused_rope_partial_fp8kv_kernel(const __half* q_in, const __half* k_in, const __half* v_in, uint8_t* q_fp8_out,
+                                uint8_t* key_cache, uint8_t* value_cache, float* k_scale_cache, float* v_scale_cache,
+                                float* q_scale_cache, const __half* cos_table, const __half* sin_table,
+                                const int* positions, const int* slot_mapping, const float* q_scale_ptr, int num_tokens,
+                                int num_heads, int num_kv_heads, int head_dim, int rotary_dim, int max_positions,
+                                int num_cache_slots) {
+    if (!q_in || !q_fp8_out || !positions || num_tokens <= 0 || num_heads <= 0 || num_kv_heads < 0 || head_dim < 64 ||
+        head_dim % 64 != 0 || rotary_dim < 0 || max_positions <= 0 || (rotary_dim > 0 && (!cos_table || !sin_table)) ||
+        (!q_scale_cache && !q_scale_ptr) ||
+        (num_kv_heads > 0 && (!k_in || !v_in || !key_cache || !value_cache || !k_scale_cache || !v_scale_cache ||
+                              !slot_mapping || num_cache_slots <= 0)) ||
+        (int)blockIdx.y >= (num_heads > num_kv_heads ? num_heads : num_kv_heads) || blockDim.y != 1 || blockDim.z != 1 ||
+        gridDim.z != 1)
+        return;
+    rope_fp8kv_body<__half>(q_in, k_in, v_in, (long long)num_heads * head_dim, (long long)num_kv_heads * head_dim,
+                            q_fp8_out, key_cache, value_cache, k_scale_cache, v_scale_cache, q_scale_cache, q_scale_ptr,
+                            cos_table, sin_table, positions, num_kv_heads > 0 ? slot_mapping : positions, num_tokens,
+                            num_heads, num_kv_heads, head_dim, rotary_dim, max_positions,
+                            num_kv_heads > 0 ? num_cache_slots : 0);
 }
 
 // Token embedding gather (reference: kernels/embedding_gather_f16.cu): out[t, :] =

@@ -47,6 +47,12 @@ def test_identity(L):
     assert L.fa_sm89_fp8_output_dtype() == 1 and L.fa_sm89_fp8_output_element_size() == 2
 
 
+def test_per_device_setup_bookkeeping(L):
+    """cudaFuncSetAttribute belongs to a device: the once-flags are kept per device ordinal, a failed
+    set-up is retried, and an unknown ordinal sets up every time (self-test in the library, no CUDA call)."""
+    assert L.rvllm_b200_selftest_device_once() == 0
+
+
 def test_row_launcher_validation_kats():
     from rvllm_b200 import InvalidArgument
     from rvllm_b200.launchers import (ArgmaxLaunch, FusedRmsnormFp8QuantLaunch, FusedSiluMulFp8QuantLaunch,

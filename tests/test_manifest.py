@@ -102,6 +102,50 @@ def test_rejected_manifests(tmp_path, why, kw):
         load(path, digest, rev, arch)
 
 
+def test_symlinked_directory_that_leaves_the_root_is_rejected(tmp_path):
+    """manifest.rs:226-238 canonicalises the artifact path and requires it under the canonical root: a
+    lexically clean `sub/x.ptx` whose `sub` is a symlink out of the bundle must not be read."""
+    from rvllm_b200 import RvllmError
+    outside = tmp_path / "outside"
+    outside.mkdir()
+    body = b"HELLO PTX"
+    (outside / "x.ptx").write_bytes(body)
+    root = tmp_path / "bundle"
+    root.mkdir()
+    (root / "sub").symlink_to(outside, target_is_directory=True)
+    ent = {"x": {"path": "sub/x.ptx", "sha256": hashlib.sha256(body).hexdigest(), "bytes": len(body), "kind": "ptx",
+                 "abi": "cuda-ptx-v1"}}
+    path, digest = write_bundle(root, entries=ent)
+    with pytest.raises(RvllmError) as e:
+        load(path, digest)
+    assert "escapes" in str(e.value)
+    # the same layout with a real directory is fine, and so is a symlink that stays inside the root
+    (root / "sub").unlink()
+    (root / "sub").mkdir()
+    (root / "sub" / "x.ptx").write_bytes(body)
+    (root / "alias").symlink_to(root / "sub", target_is_directory=True)
+    ent["y"] = dict(ent["x"], path="alias/x.ptx")
+    path, digest = write_bundle(root, entries=ent)
+    assert len(load(path, digest)) == 2
+
+
+def test_empty_entries_and_total_size_limit(tmp_path):
+    """manifest.rs:190-195 (1..=4096 artifacts) and :217-224 (sum of declared sizes <= 4 x 512 MiB)."""
+    from rvllm_b200 import RvllmError
+    path, digest = write_bundle(tmp_path, entries={})
+    with pytest.raises(RvllmError) as e:
+        load(path, digest)
+    assert "count" in str(e.value)
+    body = b"HELLO PTX"
+    big = 512 * 1024 * 1024  # each declared size is legal on its own; five of them exceed the release limit
+    ent = {"a%d" % i: {"path": "argmax.ptx", "sha256": hashlib.sha256(body).hexdigest(), "bytes": big, "kind": "ptx",
+                       "abi": "cuda-ptx-v1"} for i in range(5)}
+    path, digest = write_bundle(tmp_path, entries=ent)
+    with pytest.raises(RvllmError) as e:
+        load(path, digest)
+    assert "total" in str(e.value) or "size" in str(e.value)
+
+
 def test_duplicate_fields_and_trailing_data_rejected(tmp_path):
     from rvllm_b200 import RvllmError
     path, _ = write_bundle(tmp_path)
