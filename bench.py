@@ -236,6 +236,7 @@ def run_reference_arm(args, cfg):
         return
     orc.build()
     orc.use_all_host_threads()  # a torchrun worker inherits OMP_NUM_THREADS=1
+    t_run0 = time.perf_counter()
     B = args.batch
     times = []
     per_step = max(0.3, min(4.0, 150.0 / (args.warmup + args.steps)))  # the whole run stays within a few minutes
@@ -253,6 +254,9 @@ def run_reference_arm(args, cfg):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # every "step" is an estimate from a timed sample of the step's work (the description is in
+        # cpu_baseline.sample), not a full step: steps x ms_per_step is not the wall time of this run
+        "sampled": True, "sample_seconds_per_step": per_step, "wall_seconds": time.perf_counter() - t_run0,
     }
     print(json.dumps(line))
 
@@ -278,9 +282,20 @@ def time_steps(torch, stack, n):
     return e0.elapsed_time(e1) / 1e3
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gate|up GEMM, from the ncu capture
-# summarised in profiles/fp8_gemm_tc_gateup_m32.md, keyed by (N, K, M); other shapes were not captured
-NCU_TRAFFIC_BYTES = {(43008, 5376, 32): 236.3e6}
+def ncu_traffic_bytes(kernel, N, K, M):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of a kernel as captured under ncu: read from
+    the table kept beside the capture summaries, so a re-captured kernel updates the figure in one place and a
+    shape that was never captured reports null."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            rows = json.load(f)["captures"]
+    except (OSError, ValueError, KeyError):
+        return None
+    for r in rows:
+        if r.get("kernel") == kernel and (r.get("N"), r.get("K"), r.get("M")) == (N, K, M):
+            return r.get("dram_bytes_per_launch")
+    return None
 
 
 def dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src):
@@ -313,7 +328,7 @@ def dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src):
     return {"bound": "hbm", "kernel": "fp8 GEMM, gate|up shape [%d x %d] x M=%d" % (2 * F, H, B),
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
             "us_per_launch": sec * 1e6, "algorithmic_bytes_per_launch": algo,
-            "traffic": NCU_TRAFFIC_BYTES.get((2 * F, H, B))}
+            "traffic": ncu_traffic_bytes("fp8_gemm_tc_kernel", 2 * F, H, B)}
 
 
 def attention_case(torch, cfg, B, ctx, peak, peak_src):
@@ -369,6 +384,312 @@ def attention_case(torch, cfg, B, ctx, peak, peak_src):
     return out
 
 
+# ----------------------------------------------------------------------------- config 2: the GEMM sweep
+PROJECTIONS = [("qkv", 8192, 5376, False), ("o", 5376, 4096, True), ("gateup", 43008, 5376, False),
+               ("down", 5376, 21504, True)]
+SWEEP_M = [1, 8, 32, 128, 512, 2048]
+
+
+def time_launches(torch, launch, n, warm=3):
+    """Mean device time of n launches (CUDA events on the launching stream, after warm-up)."""
+    for i in range(warm):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / n
+
+
+def fp8_tensor_peak(torch, seconds=2.0):
+    """Dense FP8 throughput of this repository's own tcgen05 kernel on an 8192^3 problem (2 * N^3 flops):
+    best single launch (burst) and a back-to-back loop of about `seconds` (sustained, under the power cap).
+    No FP8 peak is published for this part; 2 x the measured bf16 cuBLAS figure is printed beside it."""
+    from rvllm_b200 import gemm
+    n = 8192
+    a = torch.randint(0, 120, (n, n), dtype=torch.uint8, device="cuda")
+    w = torch.randint(0, 120, (n, n), dtype=torch.uint8, device="cuda")
+    a_s = torch.full((n,), 0.01, dtype=torch.float32, device="cuda")
+    w_s = torch.full((n,), 0.01, dtype=torch.float32, device="cuda")
+    out = torch.empty((n, n), dtype=torch.bfloat16, device="cuda")
+    run = lambda i=0: gemm.fp8_gemm_channelscale(out, a, w, a_s, w_s, impl=gemm.IMPL_TCGEN05)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(10):
+        best = min(best, time_launches(torch, run, 1, warm=0))
+    reps = max(8, int(seconds / best))
+    sustained = time_launches(torch, run, reps, warm=0)
+    flops = 2.0 * n ** 3
+    out_d = {"shape": "8192^3", "burst_tflops": flops / best / 1e12, "sustained_tflops": flops / sustained / 1e12,
+             "sustained_launches": reps}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        out_d["twice_measured_bf16_tflops"] = {"burst": 2 * d["bf16_tflops"], "sustained": 2 * d["bf16_tflops_sustained"]}
+    except (OSError, ValueError, KeyError):
+        pass
+    del a, w, out
+    return out_d
+
+
+def gemm_sweep(torch, cfg):
+    """Four projection shapes x M in {1, 8, 32, 128, 512, 2048} through the C ABI: per-token activation scales,
+    per-channel weight scales, 16-bit output (the O and down shapes with the fused residual).  Each launch of a
+    row cycles to another copy of the weights so that the stream comes from HBM (copies x bytes > L2)."""
+    from rvllm_b200 import gemm
+    peak, peak_src = measured_peaks()
+    fp8 = fp8_tensor_peak(torch)
+    rows = []
+    tdt = torch.float16 if cfg["dtype"] == 0 else torch.bfloat16
+    for name, N, K, residual in PROJECTIONS:
+        copies = max(2, int(300e6 // (N * K)) + 1)
+        ws = [torch.randint(0, 120, (N, K), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+        w_s = torch.full((N,), 0.001, dtype=torch.float32, device="cuda")
+        for M in SWEEP_M:
+            a = torch.randint(0, 120, (M, K), dtype=torch.uint8, device="cuda")
+            a_s = torch.full((M,), 0.01, dtype=torch.float32, device="cuda")
+            out = torch.zeros((M, N), dtype=tdt, device="cuda")
+            res = out if residual else None
+
+            def launch(i, a=a, a_s=a_s, out=out, res=res):
+                gemm.fp8_gemm_channelscale(out, a, ws[i % copies], a_s, w_s, residual=res, impl=gemm.IMPL_TCGEN05)
+            sec = time_launches(torch, launch, max(4 * copies, 12))
+            algo = gemm_bytes(M, N, K, residual)
+            flops = 2.0 * M * N * K
+            rows.append({"shape": name, "N": N, "K": K, "M": M, "us": sec * 1e6, "gbs": algo / sec / 1e9,
+                         "frac_hbm": algo / sec / 1e9 / peak, "tflops": flops / sec / 1e12,
+                         "frac_fp8": flops / sec / 1e12 / fp8["burst_tflops"], "weight_copies": copies})
+            del a, out
+        del ws
+    assert gemm.tc_status() == 0, "a bounded wait in the tcgen05 GEMM ran out"
+    return {"gemm_sweep": rows, "fp8_peak": fp8, "hbm_peak_gbs": peak, "hbm_peak_source": peak_src,
+            "note": "frac_fp8 is against the burst figure of this repository's own kernel at 8192^3"}
+
+
+# ----------------------------------------------------------------------------- config 3: ragged attention
+def ragged_attention(torch, cfg, batch=64, lo=512, hi=32768, seed=2, with_reference=False, reps=6):
+    """The decode-attention launch of the ragged configuration: `batch` sequences with context lengths drawn
+    uniformly from [lo, hi], 32 query / 16 KV heads, both layer kinds (sliding: head_dim 128, window 1024, ring
+    of pages; global: head_dim 256), block_size 16, shuffled physical blocks, random cache bytes with
+    per-(slot, head) scales.  with_reference also times the reference's two kernels on the same buffers."""
+    import numpy as np
+    from rvllm_b200.attention import PagedDecodeFp8Launcher, PagedDecodeParams
+    peak, peak_src = measured_peaks()
+    H_, KVH, bs = cfg["heads"], cfg["kv_heads"], cfg["block_size"]
+    tdt = torch.float16   # the reference entry points write f16
+    ctx_np = np.random.default_rng(seed).integers(lo, hi + 1, batch).astype(np.int32)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    out = []
+    for tag, HD, window in (("sliding", cfg["sliding_head_dim"], cfg["sliding_window"] - 1),
+                            ("global", cfg["global_head_dim"], -1)):
+        att = np.minimum(ctx_np, window + 1) if window >= 0 else ctx_np
+        mb = (window + 1 + bs - 1) // bs + 1 if window >= 0 else int((ctx_np.max() + bs - 1) // bs)
+        need = np.full(batch, mb) if window >= 0 else (ctx_np + bs - 1) // bs
+        nblk = int(need.sum())
+        perm = torch.randperm(nblk, device="cuda", generator=gen).to(torch.int32)
+        tables = torch.full((batch, mb), -1, dtype=torch.int32, device="cuda")
+        o = 0
+        for b in range(batch):
+            tables[b, :int(need[b])] = perm[o:o + int(need[b])]
+            o += int(need[b])
+        k = torch.randint(0, 120, (nblk, bs, KVH, HD), dtype=torch.uint8, device="cuda", generator=gen)
+        v = torch.randint(0, 120, (nblk, bs, KVH, HD), dtype=torch.uint8, device="cuda", generator=gen)
+        sc = torch.full((nblk * bs * KVH,), 0.01, dtype=torch.float32, device="cuda")
+        q = torch.randint(0, 120, (batch, H_, HD), dtype=torch.uint8, device="cuda", generator=gen)
+        qs = torch.full((batch * H_,), 0.01, dtype=torch.float32, device="cuda")
+        ctxs = torch.from_numpy(ctx_np).cuda()
+        res = torch.empty((batch, H_, HD), dtype=tdt, device="cuda")
+        p = PagedDecodeParams(batch, H_, KVH, HD, bs, mb, nblk, HD ** -0.5, window)
+        ws = torch.empty(max(p.workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
+        la = PagedDecodeFp8Launcher(p)
+        sec = time_launches(torch, lambda i: la.launch(q, k, v, res, tables, ctxs, workspace=ws, k_scale_cache=sc,
+                                                       v_scale_cache=sc, q_scale_cache=qs), reps, warm=2)
+        algo = int(att.sum()) * KVH * (2 * HD + 8)
+        row = {"kernel": "paged decode attention, %s layer shape (head_dim %d)" % (tag, HD), "batch": batch,
+               "contexts": "uniform in [%d, %d], seed %d" % (lo, hi, seed), "attended_tokens": int(att.sum()),
+               "us_per_launch": sec * 1e6, "achieved": algo / sec / 1e9, "peak": peak, "unit": "GB/s",
+               "frac": algo / sec / 1e9 / peak, "peak_source": peak_src, "algorithmic_bytes_per_launch": algo,
+               "cache_bytes_touched_exceed_l2": bool(algo > 126e6)}
+        if with_reference:
+            row["reference"] = reference_attention_times(torch, dict(q=q, k=k, v=v, sc=sc, qs=qs, tables=tables, ctx=ctxs,
+                                                                     batch=batch, heads=H_, kv_heads=KVH, hd=HD, bs=bs, mb=mb,
+                                                                     nblk=nblk, window=window), sec)
+        out.append(row)
+        del k, v
+    return out
+
+
+# ----------------------------------------------------------------------------- the reference's kernels, same GPU
+def _ref_dir():
+    return os.path.join(ROOT, "oracle", "_ref")
+
+
+def reference_attention_times(torch, c, ours_sec):
+    """fa_sm89_paged_decode_fp8 (the reference's split-KV kernel, compiled from v3/kernels/fp8_decode_v2.cu with
+    its own flags) and flash_attention_2_decode_fp8kv_kernel (what its Gemma bring-up launches on this
+    architecture; it has no ring paging, so it is given the global-layer case only), on the buffers of `c`."""
+    import ctypes as C
+    from tests import ptx_harness as H
+    out = {}
+    so = os.path.join(_ref_dir(), "libfa_sm89_ref.so")
+    o16 = torch.empty((c["batch"], c["heads"], c["hd"]), dtype=torch.float16, device="cuda")
+    if os.path.exists(so):
+        ref = C.CDLL(so)
+        ref.fa_sm89_decode_workspace_size.restype = C.c_uint64
+        vp, f32, i32 = C.c_void_p, C.c_float, C.c_int
+        ref.fa_sm89_paged_decode_fp8.argtypes = [vp] * 7 + [C.c_size_t] + [vp] * 6 + [f32] + [i32] * 8 + [vp]
+        need = int(ref.fa_sm89_decode_workspace_size(c["batch"], c["heads"], c["kv_heads"], c["hd"]))
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+
+        def run(i):
+            rc = ref.fa_sm89_paged_decode_fp8(c["q"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), o16.data_ptr(),
+                                              c["tables"].data_ptr(), c["ctx"].data_ptr(), ws.data_ptr(), need,
+                                              c["sc"].data_ptr(), c["sc"].data_ptr(), c["qs"].data_ptr(), None, None, None,
+                                              c["hd"] ** -0.5, c["batch"], c["heads"], c["kv_heads"], c["hd"], c["bs"],
+                                              c["mb"], c["nblk"], c["window"], st)
+            assert rc == 0
+        sec = time_launches(torch, run, 2, warm=1)
+        out["fa_sm89_paged_decode_fp8"] = {"us_per_launch": sec * 1e6, "ours_speedup": sec / ours_sec}
+    if c["window"] < 0 and os.path.exists(os.path.join(_ref_dir(), "flash_attention.ptx")):
+        mod = H.reference("flash_attention")
+        hd = c["hd"]
+        smem = (2 * 16 * hd + 16 + 4) * 4          # v3/crates/rvllm-attention/src/decode.rs:572-630
+        if smem > 48 * 1024:
+            mod.set_max_dynamic_smem("flash_attention_2_decode_fp8kv_kernel", smem)
+
+        def run2(i):
+            mod.launch("flash_attention_2_decode_fp8kv_kernel", (c["batch"], c["heads"]), (128,), smem,
+                       [H.P(o16), H.P(c["q"]), H.P(c["k"]), H.P(c["v"]), H.P(c["sc"]), H.P(c["sc"]), H.P(c["qs"]), H.NULL(),
+                        H.NULL(), H.P(c["tables"]), H.P(c["ctx"]), H.NULL(), H.F(hd ** -0.5), H.I(c["heads"]),
+                        H.I(c["kv_heads"]), H.I(hd), H.I(c["bs"]), H.I(c["mb"]), H.I(c["window"]), H.I(c["nblk"])])
+        sec = time_launches(torch, run2, 2, warm=1)
+        out["flash_attention_2_decode_fp8kv_kernel"] = {"us_per_launch": sec * 1e6, "ours_speedup": sec / ours_sec}
+    return out
+
+
+def reference_kernel_table(torch, cfg):
+    """ours / theirs device time per kernel, same GPU, same run: the reference's own CUDA kernels for this path
+    (compiled from its sources with its flags into oracle/_ref) at the Rust launchers' geometry, next to this
+    repository's C-ABI calls on the same buffers.  Test-side tooling: the decode path never loads oracle/_ref."""
+    import numpy as np
+    from tests import ptx_harness as H
+    from rvllm_b200 import gemm, launchers
+    if not H.have_reference():
+        return {"unavailable": "oracle/_ref is not built (the reference checkout was not present at build time)"}
+    rows = []
+    B, Hd, F, V = 32, cfg["hidden"], cfg["ffn"], cfg["vocab"]
+    f16 = torch.float16
+
+    def add(name, ours, theirs, n=20):
+        to = time_launches(torch, ours, n)
+        tt = time_launches(torch, theirs, n)
+        rows.append({"kernel": name, "ours_us": to * 1e6, "reference_us": tt * 1e6, "speedup": tt / to})
+
+    # row kernels at the decode shapes
+    x = torch.randn((B, Hd), device="cuda").to(f16)
+    gamma = torch.ones(Hd, dtype=f16, device="cuda")
+    o8 = torch.empty((B, Hd), dtype=torch.uint8, device="cuda")
+    sc = torch.empty(B, dtype=torch.float32, device="cuda")
+    rn = H.reference("fused_rmsnorm_fp8_quant")
+    add("fused_rmsnorm_fp8_quant [32 x 5376]",
+        lambda i: launchers.FusedRmsnormFp8QuantLaunch(B, Hd, 1e-6).launch(o8, sc, x, gamma),
+        lambda i: rn.launch("fused_rmsnorm_fp8_quant_kernel", (B,), (1024,), 128,
+                            [H.P(o8), H.P(sc), H.P(x), H.P(gamma), H.F(1e-6), H.I(Hd)]))
+    xq = torch.randn((B, 4096), device="cuda").to(f16)
+    oq = torch.empty((B, 4096), dtype=torch.uint8, device="cuda")
+    add("quantize_fp8_per_token [32 x 4096]",
+        lambda i: launchers.QuantizeFp8PerTokenLaunch(B, 4096).launch(oq, sc, xq),
+        lambda i: rn.launch("quantize_fp8_per_token_kernel", (B,), (1024,), 128, [H.P(oq), H.P(sc), H.P(xq), H.I(4096)]))
+    gu = torch.randn((B, 2 * F), device="cuda").to(f16)
+    oa = torch.empty((B, F), dtype=torch.uint8, device="cuda")
+    sl = H.reference("fused_silu_fp8_quant")
+    add("fused_silu_mul_fp8_quant [32 x 21504]",
+        lambda i: launchers.FusedSiluMulFp8QuantLaunch(B, F).launch(oa, sc, gu),
+        lambda i: sl.launch("fused_silu_mul_fp8_quant_kernel", (B,), (1024,), 128, [H.P(oa), H.P(sc), H.P(gu), H.I(F)]))
+    lg = torch.randn((B, V), device="cuda")
+    am = torch.zeros(B, dtype=torch.int32, device="cuda")
+    ar = H.reference("argmax")
+    add("argmax [32 x 262144]", lambda i: launchers.ArgmaxLaunch(B, V).launch(lg, am),
+        lambda i: ar.launch("argmax_kernel", (B,), (1024,), 0, [H.P(lg), H.P(am), H.I(V)]), n=10)
+    # M = 1 GEMV: the reference's two kernels + its f32 -> f16 pass, against one call of ours
+    kt, sk, cv = H.reference("fp8_channelscale_gemv_ktiled"), H.reference("fp8_channelscale_gemv_splitk"), H.reference("f32_to_f16_sat")
+    for name, N, K, _ in PROJECTIONS:
+        copies = max(2, int(300e6 // (N * K)) + 1)
+        ws = [torch.randint(0, 120, (N, K), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+        w_s = torch.full((N,), 0.001, dtype=torch.float32, device="cuda")
+        a = torch.randint(0, 120, (1, K), dtype=torch.uint8, device="cuda")
+        a_s = torch.full((1,), 0.01, dtype=torch.float32, device="cuda")
+        o16 = torch.empty((1, N), dtype=f16, device="cuda")
+        o32 = torch.zeros(N, dtype=torch.float32, device="cuda")
+        gx = (N + 7) // 8
+
+        def theirs(i, N=N, K=K, ws=ws, copies=copies, w_s=w_s, a=a, a_s=a_s, o16=o16, o32=o32, gx=gx):
+            w = ws[i % copies]
+            if N <= 8192 and K >= 8192:   # gemma4_layer_exec.rs:2379: split-K 8 into a zeroed f32 buffer
+                o32.zero_()
+                sk.launch("fp8_channelscale_gemv_splitk_kernel", (gx, 8), (256,), 0,
+                          [H.P(o32), H.P(w), H.P(w_s), H.P(a), H.P(a_s), H.I(N), H.I(K), H.I(8)])
+            else:
+                tile = min(8192, K)
+                kt.launch("fp8_channelscale_gemv_ktiled_kernel", (gx,), (256,), tile * 2,
+                          [H.P(o32), H.P(w), H.P(w_s), H.P(a), H.P(a_s), H.I(N), H.I(K), H.I(tile)])
+            cv.launch("f32_to_f16_sat_kernel", ((N + 255) // 256,), (256,), 0, [H.P(o16), H.P(o32), H.I(N)])
+        add("fp8 GEMM M=1, %s [%d x %d]" % (name, N, K),
+            lambda i, ws=ws, copies=copies, w_s=w_s, a=a, a_s=a_s, o16=o16: gemm.fp8_gemm_channelscale(
+                o16, a, ws[i % copies], a_s, w_s, impl=gemm.IMPL_TCGEN05), theirs, n=max(12, 3 * copies))
+        del ws
+    att = ragged_attention(torch, cfg, batch=64, with_reference=True, reps=4)
+    return {"kernels": rows, "attention_ragged_batch64": att,
+            "note": "reference kernels: the reference's sources compiled for sm_100 with its own flags; M > 1 FP8 GEMMs "
+                    "have no reference-side kernel that compiles here (CUTLASS sm_90a / cuBLASLt are not linked)"}
+
+
+# ----------------------------------------------------------------------------- config 5: ragged replicas
+def ragged_replica_run(torch, cfg, weights, per_gpu_batch, steps, lo=1024, hi=16384, seed=4, barrier=None):
+    """One replica's share of the ragged serving configuration: `per_gpu_batch` sequences whose contexts are
+    drawn uniformly from [lo, hi] (seeded per rank), KV caches seeded synthetically at those lengths, global
+    layers sharing one block pool sized by need, then `steps` decode steps timed on the device."""
+    import numpy as np
+    from rvllm_b200.stack import DecodeStack
+    rank = int(os.environ.get("RANK", "0"))
+    ctx = np.random.default_rng(seed * 1000 + rank).integers(lo, hi + 1, per_gpu_batch).astype(np.int32)
+    reserve = steps + 8
+    bs = cfg["block_size"]
+    pool = int(((ctx + reserve + bs - 1) // bs).sum())
+    c = dict(cfg, batch=per_gpu_batch, prompt_len=0, max_context=(hi + reserve + 255) // 256 * 256, max_steps=reserve,
+             kv_pool_blocks=pool)
+    stack = DecodeStack(c, weights)
+    stack.seed_contexts(ctx)
+    stack.run(4)
+    stack.sync()
+    if barrier:
+        barrier()
+    sec = time_steps(torch, stack, steps)
+    if barrier:
+        barrier()
+    # bytes: the step model with every sequence at its own mid-run context
+    mid = ctx.astype(np.int64) + 4 + steps // 2
+    b_step = step_bytes(c, per_gpu_batch, 0)
+    for l in range(c["num_layers"]):
+        g = c["global_every"] != 0 and (l + 1) % c["global_every"] == 0
+        hd = c["global_head_dim"] if g else c["sliding_head_dim"]
+        eff = mid if g else np.minimum(mid, c["sliding_window"])
+        b_step += int(eff.sum()) * c["kv_heads"] * (2 * hd + 8)
+    res = {"batch_per_gpu": per_gpu_batch, "steps": steps, "seconds": sec, "ms_per_step": sec / steps * 1e3,
+           "tok_s": per_gpu_batch * steps / sec, "contexts": "uniform in [%d, %d], seed %d + rank" % (lo, hi, seed),
+           "mean_context": float(ctx.mean()), "kv_pool_blocks_per_global_layer": pool,
+           "device_bytes": stack.device_bytes(), "step_bytes": b_step}
+    stack.close()
+    return res
+
+
 def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None, profiler_range=False, seeded=False):
     import numpy as np
     from rvllm_b200.stack import DecodeStack
@@ -420,6 +741,29 @@ def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, ba
     return res
 
 
+def greedy_parity_block(steps):
+    """The composition the headline number times (fused QKV+RoPE epilogue, tcgen05 attention leaving per-row
+    maxima, O projection quantising its own A tiles, fused gate|up activation, cluster argmax) decoded greedily at
+    a width the CPU oracle can chain — 3 layers (2 sliding head_dim 128 + 1 global head_dim 256), hidden 1024,
+    32q/16kv heads, batch 32 — and replayed teacher-forced through the oracle.  The oracle is the checker here,
+    nothing measured."""
+    import numpy as np
+    import oracle as orc
+    from oracle.chain import greedy_parity
+    from rvllm_b200.stack import DecodeStack, random_weights, tiny_shape
+    cfg = tiny_shape(hidden=1024, ffn=2048, vocab=2048, num_layers=3, heads=32, kv_heads=16, sliding_head_dim=128,
+                     global_head_dim=256, sliding_window=32, global_every=3, dtype=1, batch=32, prompt_len=8,
+                     max_context=8 + steps, max_steps=8 + steps)
+    w = random_weights(cfg, seed=0)
+    stack = DecodeStack(cfg, w)
+    prompt = np.random.default_rng(32).integers(0, cfg["vocab"], (32, 8), dtype=np.int32)
+    stats = greedy_parity(orc, stack, cfg, w, prompt, steps)
+    stats["launches_per_step"] = stack.launches_per_step()
+    stats["shape"] = "3 layers (2 sliding hd128 + 1 global hd256), hidden 1024, ffn 2048, vocab 2048, 32q/16kv, batch 32"
+    stack.close()
+    return stats
+
+
 def run_gpu_arm(args, cfg):
     import torch
 
@@ -464,6 +808,9 @@ def run_gpu_arm(args, cfg):
         "data": "synthetic", "config": workload_config(cfg, B),
         "gpu_launches": main["launches_per_step"] * args.steps, "clocks": main["clocks"],
         "weights_gb": weights.nbytes() / 1e9, "setup_s": setup_s,
+        "collective": "none on the data path (independent replicas); NCCL only for the barrier around the timed "
+                      "region and the max-over-ranks of the device times" if world > 1 else "none (one GPU)",
+        "greedy_tokens_tail": main["greedy_tokens_tail"],
     }
     if "e2e" in main:
         e = dict(main["e2e"])
@@ -474,6 +821,23 @@ def run_gpu_arm(args, cfg):
     line["step_roofline"] = {"algorithmic_bytes_per_step": main["step_bytes"], "context": main["context_mid"],
                              "achieved_gbs": main["step_bytes"] / (main["seconds"] / args.steps) / 1e9,
                              "frac_of_hbm_peak": step_frac}
+    if args.ragged_batch > 0 and cfg["num_layers"] > 0:
+        # the ragged serving configuration, every rank: aggregate batch = ragged_batch x N (1024 at N = 8),
+        # contexts uniform in [1024, 16384], 128 steps; weak scaling like the headline line
+        rg = ragged_replica_run(torch, cfg, weights, args.ragged_batch, args.ragged_steps, barrier=barrier)
+        rg_sec = replicas.job_seconds(dist, rg["seconds"], device="cuda")
+        line["ragged_replicas"] = {
+            "workload": "aggregate batch %d split evenly over %d GPU(s), contexts uniform in [1024, 16384], %d decode "
+                        "steps, KV caches seeded synthetically at those lengths" % (args.ragged_batch * world, world,
+                                                                                     args.ragged_steps),
+            "value": world * args.ragged_batch * args.ragged_steps / rg_sec, "unit": UNIT, "scaling": "weak",
+            "ms_per_step": rg_sec / args.ragged_steps * 1e3, "batch_per_gpu": args.ragged_batch,
+            "aggregate_batch": args.ragged_batch * world, "mean_context_rank0": rg["mean_context"],
+            "frac_of_hbm_peak_rank0": rg["step_bytes"] / (rg["seconds"] / args.ragged_steps) / 1e9 / peak,
+            "kv_pool_blocks_per_global_layer": rg["kv_pool_blocks_per_global_layer"],
+            "stack_device_gb_rank0": rg["device_bytes"] / 1e9,
+            "note": "per-GPU batch is fixed at the share of the 8-GPU configuration (1024 / 8); a single GPU cannot "
+                    "hold 1024 such sequences (about 0.9 GB of KV each)"}
     if rank == 0:
         if not args.no_roofline:
             line["roofline"] = dominant_kernel_roofline(torch, cfg, weights, B, peak, peak_src)
@@ -484,14 +848,18 @@ def run_gpu_arm(args, cfg):
             est, spent, desc = cpu_step_sample(cfg, B, ctx=cfg["prompt_len"], min_seconds=12.0)
             line["cpu_baseline"] = {"value": B / est, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
                                     "sample": desc, "sample_seconds": spent}
-        if world == 1 and args.all_batches:
-            line["by_batch"] = {}
+        if world == 1 and not args.no_by_batch:
+            # the metric names three batch sizes: the headline one above, the other two here
+            line["by_batch"] = {str(B): {"tok_s": main["tok_s"], "ms_per_step": main["ms_per_step"],
+                                         "frac_of_hbm_peak": step_frac}}
             for b in (1, 128):
+                if b == B:
+                    continue
                 r = run_batch(torch, cfg, weights, b, args.steps, args.warmup, 0)
                 line["by_batch"][str(b)] = {"tok_s": r["tok_s"], "ms_per_step": r["ms_per_step"],
                                             "frac_of_hbm_peak": r["step_bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / peak}
-            line["by_batch"][str(B)] = {"tok_s": main["tok_s"], "ms_per_step": main["ms_per_step"],
-                                        "frac_of_hbm_peak": step_frac}
+        if world == 1 and not args.no_cpu_baseline and not args.no_parity:
+            line["parity"] = greedy_parity_block(args.parity_steps)
         print(json.dumps(line))
     if dist:
         dist.barrier(device_ids=[local])
@@ -507,8 +875,18 @@ def main():
     ap.add_argument("--batch", type=int, default=HEADLINE_BATCH)
     ap.add_argument("--e2e-steps", type=int, default=32)
     ap.add_argument("--layers", type=int, default=62, help="reduce only for quick functional checks")
-    ap.add_argument("--gemm-impl", type=int, default=0)
-    ap.add_argument("--all-batches", action="store_true", help="also time batch 1 and 128")
+    ap.add_argument("--no-by-batch", action="store_true", help="skip the batch 1 and batch 128 runs of the metric")
+    ap.add_argument("--no-parity", action="store_true", help="skip the greedy-token check against the oracle chain")
+    ap.add_argument("--parity-steps", type=int, default=64)
+    ap.add_argument("--ragged-batch", type=int, default=128,
+                    help="per-GPU batch of the ragged serving configuration (0 = skip it)")
+    ap.add_argument("--ragged-steps", type=int, default=128)
+    ap.add_argument("--gemm-sweep", action="store_true",
+                    help="only the GEMM sweep: four projection shapes x M in {1, 8, 32, 128, 512, 2048}, and the FP8 peak")
+    ap.add_argument("--ragged-attention", action="store_true",
+                    help="only the decode attention at batch 64 with contexts uniform in [512, 32768]")
+    ap.add_argument("--vs-ref-kernels", action="store_true",
+                    help="only the ours / reference kernel table (needs oracle/_ref)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--roofline-only", action="store_true",
@@ -516,8 +894,6 @@ def main():
     ap.add_argument("--attention-only", action="store_true",
                     help="small case for ncu: only the decode-attention kernel at the two layer shapes")
     ap.add_argument("--context", type=int, default=576, help="context length of --attention-only")
-    ap.add_argument("--attention-variant", type=int, default=0,
-                    help="decode-attention main kernel: 0 automatic, 1 FP32 pipes, 2/3 mma.sync, 4 tcgen05")
     ap.add_argument("--seeded-context", action="store_true",
                     help="profiling aid: fill the KV caches synthetically instead of running the 512 prefill steps")
     ap.add_argument("--profiler-range", action="store_true",
@@ -525,8 +901,7 @@ def main():
     args = ap.parse_args()
     from rvllm_b200.stack import gemma31b_shape
     need = 512 + max(args.warmup, 3) + args.steps + args.e2e_steps + 8
-    cfg = gemma31b_shape(args.batch, num_layers=args.layers, gemm_impl=args.gemm_impl,
-                         max_context=(need + 255) // 256 * 256, max_steps=need)
+    cfg = gemma31b_shape(args.batch, num_layers=args.layers, max_context=(need + 255) // 256 * 256, max_steps=need)
     if args.roofline_only:
         import torch
         from rvllm_b200.stack import Weights, _quant_weight
@@ -539,9 +914,17 @@ def main():
         peak, src = measured_peaks()
         print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
         return
-    if args.impl != "reference" and args.attention_variant != 0:
-        from rvllm_b200 import _lib
-        _lib.lib().rvllm_paged_decode_tune(0, 0, args.attention_variant)
+    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels:
+        import torch
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
+        if args.gemm_sweep:
+            print(json.dumps(gemm_sweep(torch, cfg)))
+        if args.ragged_attention:
+            print(json.dumps({"attention_ragged": ragged_attention(torch, cfg)}))
+        if args.vs_ref_kernels:
+            print(json.dumps({"ref_kernels": reference_kernel_table(torch, cfg)}))
+        return
     if args.attention_only:
         import torch
         peak, src = measured_peaks()
