@@ -151,6 +151,44 @@ int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void*
                                     int dtype, int impl, void* workspace, size_t workspace_size, void* stream);
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K);
 
+/* Everything between two attention calls of a decoder layer in ONE launch, for decode batches of at most 32
+ * rows: O projection (+residual) -> RMSNorm + FP8 quant -> gate|up projection -> act(gate)*up + FP8 quant ->
+ * down projection (+residual) -> RMSNorm + FP8 quant with the next layer's gain.  Reference: the six launches of
+ * v3/crates/rvllm-runtime/src/layer_exec.rs:425-541 (quantize_fp8_per_token, cuBLASLt O GEMM + residual,
+ * fused_rmsnorm_fp8_quant, gate|up GEMM, fused_silu_mul_fp8_quant, down GEMM + residual) and the
+ * fused_rmsnorm_fp8_quant that opens the next layer (:205-222); there is no single reference entry point.  Every
+ * stage is the arithmetic of this library's stand-alone calls (rvllm_fp8_gemm_residual_from16 or
+ * rvllm_fp8_gemm_channelscale, rvllm_fused_rmsnorm_fp8_quant_launch, rvllm_fp8_gemm_channelscale,
+ * rvllm_fused_act_mul_fp8_quant_launch), bit for bit; the CTAs stay resident across the stages and meet at
+ * grid-wide barriers while their TMA producers already stream the next stage's weights.
+ *
+ * attention output: 16-bit [M, o_k] + attn_amax [M, amax_parts] (as left by rvllm_paged_decode_fp8_amax), or, with
+ * attn_out16 NULL, FP8 rows attn_fp8 [M, o_k] + attn_scale [M].  residual [M, hidden] 16-bit is updated in place.
+ * x_fp8 [M, hidden] / x_scale [M]: the RMSNorm output feeding gate|up; on return they hold the closing norm's
+ * output (RMSNorm of the final residual with next_norm_gamma), the next layer's QKV input.  h_fp8 [M, ffn] /
+ * h_scale [M]: act(gate)*up.  gateup_w [2*ffn, hidden] rows [gate | up]; o_w [hidden, o_k]; down_w [hidden, ffn].
+ * stages: mask of RVLLM_BLOCK_* (all of them in production; a subset runs only those stages on the buffers given,
+ * which is how each stage is tested against the stand-alone kernels).
+ * workspace: rvllm_fp8_layer_block_workspace(ffn) bytes, 256-byte aligned.  Its first 256 bytes are the grid
+ * barrier's counters: they must be zero before the first launch (one cudaMemsetAsync at set-up) and every launch
+ * leaves them zero; calls that share a workspace must not overlap on the GPU.
+ * Returns RVLLM_E_UNSUPPORTED for shapes it does not take (M > 32, hidden not a multiple of 128 or above 6144,
+ * ffn not a multiple of 64 or above 4 * hidden, or a device on which the grid cannot be resident at once):
+ * issue the stand-alone calls then. */
+#define RVLLM_BLOCK_O 1
+#define RVLLM_BLOCK_NORM_MLP 2
+#define RVLLM_BLOCK_GATEUP_ACT 4
+#define RVLLM_BLOCK_DOWN 8
+#define RVLLM_BLOCK_NORM_NEXT 16
+#define RVLLM_BLOCK_ALL 31
+size_t rvllm_fp8_layer_block_workspace(int ffn);
+int rvllm_fp8_layer_block(int M, int hidden, int ffn, int o_k, int act, int dtype, float eps, const void* attn_out16,
+                          const float* attn_amax, int amax_parts, const void* attn_fp8, const float* attn_scale,
+                          const void* o_w, const float* o_scale, void* residual, const void* mlp_norm_gamma,
+                          const void* next_norm_gamma, void* x_fp8, float* x_scale, const void* gateup_w,
+                          const float* gateup_scale, void* h_fp8, float* h_scale, const void* down_w,
+                          const float* down_scale, void* workspace, size_t workspace_bytes, int stages, void* stream);
+
 /* ---- 5. FP8-KV paged GQA decode attention -------------------------------------------
  * The fa_sm89_* family the reference loads from libfa_sm89_kernels.so
  * (v3/kernels/fp8_decode_v2.cu:939-1112; loader v3/crates/rvllm-attention/src/lib.rs:353-493).

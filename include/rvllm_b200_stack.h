@@ -48,6 +48,8 @@ typedef struct {
                             global layers share a pool of this many blocks per layer, dealt out per sequence by
                             need (a ragged batch: rvllm_stack_seed_contexts); sliding layers always keep their
                             fixed ring of sliding_window tokens per sequence */
+    int fused_block;     /* 1: where the shape allows (batch <= 32), everything between two attention calls is one
+                            launch (rvllm_fp8_layer_block); 0: always the stand-alone kernels.  Same bytes either way. */
 } rvllm_stack_config;
 
 typedef struct {

@@ -7,6 +7,7 @@
 #include "host_util.h"
 #include "fp8_gemm_stream.cuh"
 #include "fp8_gemm_tc.cuh"
+#include "fp8_layer_block.cuh"
 
 extern "C" {
 // ---------------------------------------------------------------- stage 2: GEMM
@@ -306,5 +307,71 @@ int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void*
                                                 stream);
 }
 
+size_t rvllm_fp8_layer_block_workspace(int ffn) {
+    if (ffn <= 0 || ffn % 64 != 0) return 0;
+    return rvblk::blk_workspace_bytes(ffn);
+}
+
+int rvllm_fp8_layer_block(int M, int hidden, int ffn, int o_k, int act, int dtype, float eps, const void* attn_out16,
+                          const float* attn_amax, int amax_parts, const void* attn_fp8, const float* attn_scale,
+                          const void* o_w, const float* o_scale, void* residual, const void* mlp_norm_gamma,
+                          const void* next_norm_gamma, void* x_fp8, float* x_scale, const void* gateup_w,
+                          const float* gateup_scale, void* h_fp8, float* h_scale, const void* down_w,
+                          const float* down_scale, void* workspace, size_t workspace_bytes, int stages, void* stream) {
+    if (M <= 0 || hidden <= 0 || ffn <= 0 || o_k <= 0) return rv_fail(RVLLM_E_INVALID, "M, hidden, ffn, o_k must be > 0");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    if (act != RVLLM_ACT_SILU && act != RVLLM_ACT_GELU_TANH) return rv_fail(RVLLM_E_INVALID, "unknown activation");
+    if (!isfinite(eps) || eps < 0.0f) return rv_fail(RVLLM_E_INVALID, "eps must be finite and >= 0");
+    if (stages <= 0 || stages > 31) return rv_fail(RVLLM_E_INVALID, "stages must be a non-empty mask of RVLLM_BLOCK_*");
+    if (!rvblk::blk_shape_ok(M, hidden, ffn, o_k))
+        return rv_fail(RVLLM_E_UNSUPPORTED, "layer block: shape not taken (M <= 32, hidden %% 128 == 0 and <= 6144, "
+                                            "ffn %% 64 == 0 and <= 4 * hidden)");
+    const bool o = stages & rvblk::PH_O, n1 = stages & rvblk::PH_N1, gu = stages & rvblk::PH_GU, d = stages & rvblk::PH_D,
+               n2 = stages & rvblk::PH_N2;
+    if (o && !((attn_out16 && attn_amax && amax_parts > 0) || (attn_fp8 && attn_scale)))
+        return rv_fail(RVLLM_E_INVALID, "O stage: give the attention output as 16-bit values + partial maxima or as FP8 rows + scales");
+    if ((o && (!o_w || !o_scale)) || ((o || d || n1 || n2) && !residual) || (n1 && !mlp_norm_gamma) ||
+        ((n1 || gu || n2) && (!x_fp8 || !x_scale)) || (gu && (!gateup_w || !gateup_scale)) ||
+        ((gu || d) && (!h_fp8 || !h_scale)) || (d && (!down_w || !down_scale)) || !o_w || !gateup_w || !down_w || !x_fp8 || !h_fp8)
+        return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (!rv_aligned(o_w, 16) || !rv_aligned(gateup_w, 16) || !rv_aligned(down_w, 16) || !rv_aligned(x_fp8, 16) ||
+        !rv_aligned(h_fp8, 16) || (attn_out16 && !rv_aligned(attn_out16, 16)) || (attn_fp8 && !rv_aligned(attn_fp8, 16)) ||
+        (residual && !rv_aligned(residual, 16)))
+        return rv_fail(RVLLM_E_INVALID, "operands must be 16-byte aligned");
+    if (!workspace || !rv_aligned(workspace, 256) || workspace_bytes < rvblk::blk_workspace_bytes(ffn))
+        return rv_fail(RVLLM_E_WORKSPACE, "layer-block workspace missing, misaligned or too small");
+    rvblk::BlkArgs g = {};
+    g.M = M;
+    g.H = hidden;
+    g.F = ffn;
+    g.KO = o_k;
+    g.act = act;
+    g.dtype = dtype == RVLLM_F16 ? 0 : 1;
+    g.phases = stages;
+    g.eps = eps;
+    g.attn16 = attn_out16;
+    g.attn_amax = attn_amax;
+    g.amax_parts = amax_parts;
+    g.attn_fp8 = attn_out16 ? nullptr : attn_fp8;
+    g.attn_scale = attn_scale;
+    g.o_w = o_w;
+    g.o_wscale = o_scale;
+    g.residual = residual;
+    g.gamma1 = mlp_norm_gamma;
+    g.gamma2 = next_norm_gamma;
+    g.x8 = x_fp8;
+    g.xs = x_scale;
+    g.gu_w = gateup_w;
+    g.gu_wscale = gateup_scale;
+    g.h8 = h_fp8;
+    g.hs = h_scale;
+    g.d_w = down_w;
+    g.d_wscale = down_scale;
+    g.workspace = workspace;
+    g.workspace_bytes = workspace_bytes;
+    const int rc = rvblk::launch_block(g, (cudaStream_t)stream);
+    if (rc == -3) return RVLLM_E_UNSUPPORTED;
+    return rc;
+}
 
 }  // extern "C"

@@ -76,10 +76,6 @@ __global__ void advance_kernel(int* __restrict__ tokens, const int* __restrict__
 __global__ void fill_f32_kernel(float* dst, size_t n, float v) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = v;
 }
-__global__ void fill_i32_kernel(int* dst, int n, int v) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = v;
-}
-
 template <typename T>
 __global__ void rope_table_kernel(T* cos_t, T* sin_t, int max_pos, int half, float theta);
 template <>
@@ -130,6 +126,12 @@ struct rvllm_stack {
     void* attn_out;      // [B, max q_dim] 16-bit
     float* attn_amax;    // [B, kv_heads] max |attention output| per (sequence, kv_head)
     void* gateup;        // [B, 2*ffn] 16-bit
+    uint8_t* attn_fp8;   // [B, max q_dim] attention output quantised per token (split-KV form)
+    float* attn_scale;   // [B]
+    uint8_t* h_fp8;      // [B, ffn] act(gate)*up of the layer-block kernel
+    float* h_scale;      // [B]
+    void* blk_ws;        // layer-block kernel: grid-barrier words + partial row maxima
+    size_t blk_ws_bytes;
     float* logits;       // [B, vocab]
     void* attn_ws;
     size_t attn_ws_bytes;
@@ -164,6 +166,7 @@ int validate_cfg(const rvllm_stack_config* c) {
         return rv_fail(RVLLM_E_INVALID, "bad eps / rope theta");
     if (c->gemm_impl < 0 || c->gemm_impl > 2) return rv_fail(RVLLM_E_INVALID, "gemm_impl must be 0, 1 or 2");
     if (c->kv_pool_blocks < 0) return rv_fail(RVLLM_E_INVALID, "kv_pool_blocks must be >= 0");
+    if (c->fused_block != 0 && c->fused_block != 1) return rv_fail(RVLLM_E_INVALID, "fused_block must be 0 or 1");
     return RVLLM_OK;
 }
 
@@ -219,6 +222,12 @@ size_t layout(rvllm_stack* s, uint8_t* base) {
     s->attn_out = take((size_t)B * max_q * 2);
     s->attn_amax = (float*)take((size_t)B * c.kv_heads * sizeof(float));
     s->gateup = take((size_t)B * 2 * c.ffn * 2);
+    s->attn_fp8 = take((size_t)B * max_q);
+    s->attn_scale = (float*)take((size_t)B * sizeof(float));
+    s->h_fp8 = take((size_t)B * c.ffn);
+    s->h_scale = (float*)take((size_t)B * sizeof(float));
+    s->blk_ws_bytes = rvllm_fp8_layer_block_workspace(c.ffn);   // (0 when ffn is not a multiple of 64: the kernel is not used then)
+    s->blk_ws = take(s->blk_ws_bytes ? s->blk_ws_bytes : 256);  // zeroed with the arena: the barrier words start at zero
     s->logits = (float*)take((size_t)B * c.vocab * sizeof(float));
     uint64_t aw = 0;
     for (int hd : {c.sliding_head_dim, c.global_head_dim}) {
@@ -272,12 +281,19 @@ int enqueue_step(rvllm_stack* s, int* launches) {
     n++;
     RV_TRY(rvllm_embedding_gather_launch(s->residual, s->head.embedding, s->tokens, B, H, c.vocab, st));
     n++;
+    // x_fp8 / x_scale hold the current layer's attention-block input (RMSNorm + quant of the residual) when the
+    // previous layer's block kernel has already produced it
+    bool x_ready = false;
     for (int l = 0; l < c.num_layers; l++) {
         const LayerState& L = s->ls[l];
         const rvllm_layer_weights& W = s->layers[l];
         const int es = 2;
-        RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
-                                                    W.attn_norm_gamma, c.dtype, st));
+        if (!x_ready) {
+            RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
+                                                        W.attn_norm_gamma, c.dtype, st));
+            n++;
+        }
+        x_ready = false;
         // QKV projection, RoPE, Q quantisation and the paged KV write: one launch where the library
         // takes the shape (head_dim 128, batch <= 32, tensor-core GEMM), else the GEMM and the RoPE kernel
         int fused = RVLLM_E_UNSUPPORTED;
@@ -298,25 +314,26 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                            s->positions, L.global ? s->slots_global : s->slots_sliding, B, c.heads,
                                            c.kv_heads, L.head_dim, L.head_dim, c.max_context,
                                            L.num_blocks * c.block_size, c.dtype, st));
-            n++;
+            n += 2;
         } else {
             RV_TRY(fused);
+            n++;
         }
         const float sm_scale = 1.0f / sqrtf((float)L.head_dim);
         const int* tables = L.global ? s->tables_global : s->tables_sliding;
-        bool o_done = false;
+        // Attention leaves its output in one of two forms.  (a) 16-bit values + per-(row, kv_head) maxima: one chunk
+        // per sequence on the tcgen05 kernel, batch <= 32 — the O projection quantises its own A tiles.  (b) FP8 rows +
+        // per-row scales: split-KV, the combine pass quantises (same bytes as attention -> per-token quantiser); also
+        // what the plain call + quantiser produce.
+        bool have16 = false;
         if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
-            // split-KV: the combine pass also does the per-token quantisation (same bytes as the
-            // plain attention call followed by the quantiser)
-            RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->x_fp8, s->x_scale, c.dtype, tables,
+            RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->attn_fp8, s->attn_scale, c.dtype, tables,
                                                 s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
                                                 s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads,
                                                 c.kv_heads, L.head_dim, c.block_size, L.max_blocks, L.num_blocks,
                                                 L.window_left, st));
+            n += 2;
         } else {
-            // One chunk per sequence.  Where the tcgen05 attention kernel runs and the batch fits one GEMM
-            // batch tile, it also leaves each row's partial absmax and the O projection quantises its own
-            // activation tiles from the 16-bit output: no quantiser launch, no FP8 copy (same bytes).
             int a16 = RVLLM_E_UNSUPPORTED;
             if (B <= 32 && c.gemm_impl != 1 &&
                 rvllm_paged_decode_kernel_for(c.heads, c.kv_heads, L.head_dim, c.block_size, L.num_blocks) == 4)
@@ -326,10 +343,8 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                                   c.heads, c.kv_heads, L.head_dim, c.block_size, L.max_blocks,
                                                   L.num_blocks, L.window_left, st);
             if (a16 == RVLLM_OK) {
-                RV_TRY(rvllm_fp8_gemm_residual_from16(s->residual, c.dtype, s->attn_out, s->attn_amax, c.kv_heads, W.o_w,
-                                                      W.o_scale, s->residual, B, H, L.q_dim, st));
-                o_done = true;
-                n--;
+                have16 = true;
+                n++;
             } else if (a16 != RVLLM_E_UNSUPPORTED) {
                 RV_TRY(a16);
             } else {
@@ -337,12 +352,35 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                               s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
                                               s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads, c.kv_heads,
                                               L.head_dim, c.block_size, L.max_blocks, L.num_blocks, L.window_left, st));
-                RV_TRY(rvllm_quantize_fp8_per_token_launch(B, L.q_dim, s->x_fp8, s->x_scale, s->attn_out, c.dtype, st));
+                RV_TRY(rvllm_quantize_fp8_per_token_launch(B, L.q_dim, s->attn_fp8, s->attn_scale, s->attn_out, c.dtype, st));
+                n += 2;
             }
         }
-        if (!o_done)
-            RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.o_w, s->x_scale, W.o_scale, s->residual,
-                                               B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
+        // Everything up to the next attention in one launch where the library takes the shape (batch <= 32, hidden a
+        // multiple of 128, ffn <= 4 * hidden): O projection, RMSNorm + quant, gate|up, act*up + quant, down, and the
+        // RMSNorm + quant that opens the next layer (or closes the stack).
+        int blk = RVLLM_E_UNSUPPORTED;
+        if (c.gemm_impl != 1 && c.fused_block != 0 && s->blk_ws_bytes > 0) {
+            const void* next_gamma = l + 1 < c.num_layers ? s->layers[l + 1].attn_norm_gamma : s->head.final_norm_gamma;
+            blk = rvllm_fp8_layer_block(B, H, c.ffn, L.q_dim, c.act, c.dtype, c.rms_eps, have16 ? s->attn_out : nullptr,
+                                        s->attn_amax, c.kv_heads, have16 ? nullptr : s->attn_fp8, s->attn_scale, W.o_w,
+                                        W.o_scale, s->residual, W.mlp_norm_gamma, next_gamma, s->x_fp8, s->x_scale,
+                                        W.gateup_w, W.gateup_scale, s->h_fp8, s->h_scale, W.down_w, W.down_scale,
+                                        s->blk_ws, s->blk_ws_bytes, RVLLM_BLOCK_ALL, st);
+        }
+        if (blk == RVLLM_OK) {
+            x_ready = true;
+            n++;
+            continue;
+        }
+        if (blk != RVLLM_E_UNSUPPORTED) RV_TRY(blk);
+        if (have16) {
+            RV_TRY(rvllm_fp8_gemm_residual_from16(s->residual, c.dtype, s->attn_out, s->attn_amax, c.kv_heads, W.o_w,
+                                                  W.o_scale, s->residual, B, H, L.q_dim, st));
+        } else {
+            RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->attn_fp8, W.o_w, s->attn_scale, W.o_scale,
+                                               s->residual, B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
+        }
         RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
                                                     W.mlp_norm_gamma, c.dtype, st));
         RV_TRY(rvllm_fp8_gemm_channelscale(s->gateup, c.dtype, s->x_fp8, W.gateup_w, s->x_scale, W.gateup_scale,
@@ -350,10 +388,13 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         RV_TRY(rvllm_fused_act_mul_fp8_quant_launch(B, c.ffn, c.act, s->x_fp8, s->x_scale, s->gateup, c.dtype, st));
         RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.down_w, s->x_scale, W.down_scale,
                                            s->residual, B, H, c.ffn, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
-        n += 9;
+        n += 5;
     }
-    RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
-                                                s->head.final_norm_gamma, c.dtype, st));
+    if (!x_ready) {
+        RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
+                                                    s->head.final_norm_gamma, c.dtype, st));
+        n++;
+    }
     RV_TRY(rvllm_fp8_gemm_channelscale(s->logits, RVLLM_OUT_F32, s->x_fp8, s->head.lm_head_w, s->x_scale,
                                        s->head.lm_head_scale, nullptr, B, c.vocab, H, c.gemm_impl, s->gemm_ws,
                                        s->gemm_ws_bytes, st));
@@ -361,7 +402,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
     rv_launch(advance_kernel, dim3(1), dim3(256), 0, s->stream, dim3(1, 1, 1), s->tokens, s->next_tokens, s->positions, s->prompt, c.prompt_len,
                                              s->history, s->step_counter, c.max_steps, B);
     RV_TRY(rv_launched("advance"));
-    n += 4;
+    n += 3;
     if (launches) *launches = n;
     return RVLLM_OK;
 }

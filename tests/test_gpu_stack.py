@@ -64,43 +64,69 @@ def bench_composition_shape(batch, **over):
     return tiny_shape(**cfg)
 
 
-@pytest.mark.parametrize("batch", [32, 4, 40])
-def test_bench_kernel_composition_against_oracle_chain(orc, batch):
-    """256 greedy steps of the composition the benchmark times — fused QKV+RoPE epilogue, tcgen05 attention
-    leaving per-row maxima, O projection quantising its own A tiles, cluster kernels for the row ops — at
-    batch 32; the split-KV form with the fused combine+quantise pass at batch 4; the unfused ten-launch
-    layer at batch 40.
+@pytest.mark.parametrize("batch,fused_block", [(32, 1), (32, 0), (4, 1), (4, 0), (40, 1)])
+def test_bench_kernel_composition_against_oracle_chain(orc, batch, fused_block):
+    """256 greedy steps of the compositions the benchmark times, against the oracle chain.
 
-    Launches per layer in one step's graph.  Fused (batch <= 32, one attention chunk per sequence): norm,
-    QKV+RoPE+KV-write, attention(+absmax), O-proj from 16-bit, norm, gate|up, act*up+quant, down = 8 (7
-    where the activation is folded into the gate|up launch); a global layer (head_dim 256: a head spans
-    two weight tiles) keeps the RoPE kernel = one more.  Unfused: norm, QKV, RoPE, attention, quantiser, O,
-    norm, gate|up, act, down = 10.  Plus six per step (bookkeeping, embedding, final norm, LM head, argmax,
-    token feedback)."""
+    batch 32, block kernel on : QKV+RoPE+KV-write epilogue, tcgen05 attention leaving per-row maxima, then ONE launch
+                                for O projection .. down projection .. next RMSNorm (what the headline number runs)
+    batch 32, block kernel off: the same with stand-alone kernels (O projection quantising its own A tiles, cluster
+                                kernels for the row ops)
+    batch 4                   : split-KV attention with the fused combine+quantise pass feeding either form
+    batch 40                  : above the 32-row forms: the unfused ten-launch layer
+
+    Launches in one step's graph (2 sliding head_dim-128 layers + 1 global head_dim-256 layer whose RoPE stays a
+    kernel of its own: a head spans two weight tiles; 5 per step for bookkeeping, embedding, LM head, argmax, token
+    feedback; the final RMSNorm is a launch unless the last block kernel did it):
+      batch 32 on : (norm, QKV, attention, block) + (QKV, attention, block) + (QKV, RoPE, attention, block) + 5 = 16
+      batch 32 off: 8 + 8 + 9 + final norm + 5 = 31
+      batch 4  on : attention is two launches (main + combine/quantise): 5 + 4 + 5 + 5 = 19
+      batch 4  off: 9 + 9 + 10 + 1 + 5 = 34
+      batch 40    : 10 + 10 + 10 + 1 + 5 = 36"""
     from oracle.chain import greedy_parity
     from rvllm_b200 import _lib
     steps = 256
-    cfg = bench_composition_shape(batch, max_context=8 + steps, max_steps=8 + steps)
+    cfg = bench_composition_shape(batch, max_context=8 + steps, max_steps=8 + steps, fused_block=fused_block)
     L = _lib.lib()
     nblk_s = batch * (cfg["sliding_window"] // cfg["block_size"] + 1)
     assert L.rvllm_paged_decode_kernel_for(32, 16, 128, 16, nblk_s) == 4      # the tcgen05 attention kernel
     assert L.rvllm_paged_decode_kernel_for(32, 16, 256, 16, nblk_s) == 4
     stack, w = make(cfg)
-    per_layer = stack.launches_per_step() - 6
     chunks = L.rvllm_paged_decode_max_chunks(batch, 16)
-    if batch == 32:
-        assert chunks == 1
-        assert per_layer in (2 * 7 + 8, 2 * 8 + 9), per_layer   # every fused path taken (act fused or not)
-    elif batch == 4:
-        assert chunks > 1
-        assert per_layer in (2 * 8 + 9, 2 * 9 + 10), per_layer  # fused QKV epilogue + combine-and-quantise pass
-    else:
-        assert per_layer == 3 * 10, per_layer
+    assert (chunks == 1) == (batch >= 32)
+    want = {(32, 1): 16, (32, 0): 31, (4, 1): 19, (4, 0): 34, (40, 1): 36}[(batch, fused_block)]
+    assert stack.launches_per_step() == want, stack.launches_per_step()
     prompt = np.random.default_rng(batch).integers(0, cfg["vocab"], (batch, cfg["prompt_len"]), dtype=np.int32)
     check_parity(greedy_parity(orc, stack, cfg, w, prompt, steps, LOGIT_TOL))
     from rvllm_b200 import gemm
     assert gemm.tc_status() == 0
     stack.close()
+
+
+def test_block_kernel_on_and_off_decode_the_same_tokens(orc):
+    """The block kernel computes the bytes of the kernels it replaces: the same weights and prompt decode to the same
+    tokens and bit-identical logits and residual with it on and off (batch 32: 16-bit attention output form; batch 4:
+    FP8 rows from the split-KV combine pass).  Run at the benchmark's own layer dimensions (two layers, small
+    vocabulary), where the stand-alone GEMMs pick the same split-K plans as the block kernel's stages; at small
+    widths the stand-alone plans differ and only the tolerance of the oracle comparison above applies."""
+    from rvllm_b200.stack import DecodeStack, gemma31b_shape, random_weights
+    for batch in (32, 4):
+        base = gemma31b_shape(batch, num_layers=2, global_every=2, vocab=4096, prompt_len=8, max_context=72, max_steps=72,
+                              sliding_window=32)
+        w = random_weights(base, seed=11)
+        prompt = np.random.default_rng(5).integers(0, base["vocab"], (batch, base["prompt_len"]), dtype=np.int32)
+        runs = []
+        for fb in (1, 0):
+            st = DecodeStack(dict(base, fused_block=fb), w)
+            st.reset(prompt)
+            st.run(56)
+            st.sync()
+            runs.append((st.tokens().copy(), st.debug_read(1).copy(), st.debug_read(0).copy(), st.launches_per_step()))
+            st.close()
+        assert runs[0][3] < runs[1][3]
+        assert np.array_equal(runs[0][0], runs[1][0])
+        assert np.array_equal(runs[0][1].view(np.uint32), runs[1][1].view(np.uint32))
+        assert np.array_equal(runs[0][2], runs[1][2])
 
 
 def test_graph_eager_and_pdl_variants_agree_bitwise(orc):
