@@ -151,6 +151,20 @@ int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void*
                                     int dtype, int impl, void* workspace, size_t workspace_size, void* stream);
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K);
 
+/* The greedy tail in two launches and without materialised logits: LM-head GEMM whose epilogue keeps, per 128-channel
+ * weight tile and batch row, only the best (logit, token id) — logit = a_scale[m] * (w_scale[n] * acc), the f32 value
+ * rvllm_fp8_gemm_channelscale would have stored, soft-capped first as cap * tanh(logit / cap) when softcap > 0 — and a
+ * merge over the tiles.  Ordering rule of the reference's argmax kernels (kernels/argmax.cu:16-25): greater value
+ * wins, the lower token id on ties, NaN is never a candidate, a row without candidates gives -1.  Same token as
+ * rvllm_fp8_gemm_channelscale (f32 out) -> [soft cap] -> rvllm_argmax_launch; the reference composes
+ * cublaslt.fp8_gemm -> logit_softcap -> ArgmaxLaunch (v3/crates/rvllm-runtime/src/gemma4_bring_up.rs:2119-2161) and has
+ * no fused counterpart.  A [M, K] FP8, W [vocab, K] FP8, out_tokens [M] i32.  The workspace
+ * (rvllm_fp8_gemm_lm_head_argmax_workspace bytes, 256-byte aligned) holds the per-tile winners. */
+size_t rvllm_fp8_gemm_lm_head_argmax_workspace(int M, int vocab);
+int rvllm_fp8_gemm_lm_head_argmax(int32_t* out_tokens, const void* a_fp8, const void* w_fp8, const float* a_scale,
+                                  const float* w_scale, int M, int vocab, int K, float softcap, void* workspace,
+                                  size_t workspace_bytes, void* stream);
+
 /* Everything between two attention calls of a decoder layer in ONE launch, for decode batches of at most 32
  * rows: O projection (+residual) -> RMSNorm + FP8 quant -> gate|up projection -> act(gate)*up + FP8 quant ->
  * down projection (+residual) -> RMSNorm + FP8 quant with the next layer's gain.  Reference: the six launches of
@@ -169,8 +183,8 @@ size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K);
  * h_scale [M]: act(gate)*up.  gateup_w [2*ffn, hidden] rows [gate | up]; o_w [hidden, o_k]; down_w [hidden, ffn].
  * stages: mask of RVLLM_BLOCK_* (all of them in production; a subset runs only those stages on the buffers given,
  * which is how each stage is tested against the stand-alone kernels).
- * workspace: rvllm_fp8_layer_block_workspace(ffn) bytes, 256-byte aligned.  Its first 256 bytes are the grid
- * barrier's counters: they must be zero before the first launch (one cudaMemsetAsync at set-up) and every launch
+ * workspace: rvllm_fp8_layer_block_workspace(hidden, ffn) bytes (a few MB: split-K partial tiles and partial row
+ * maxima), 256-byte aligned.  Its first 256 bytes are the grid barrier's counters: they must be zero before the first launch (one cudaMemsetAsync at set-up) and every launch
  * leaves them zero; calls that share a workspace must not overlap on the GPU.
  * Returns RVLLM_E_UNSUPPORTED for shapes it does not take (M > 32, hidden not a multiple of 128 or above 6144,
  * ffn not a multiple of 64 or above 4 * hidden, or a device on which the grid cannot be resident at once):
@@ -181,7 +195,7 @@ size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K);
 #define RVLLM_BLOCK_DOWN 8
 #define RVLLM_BLOCK_NORM_NEXT 16
 #define RVLLM_BLOCK_ALL 31
-size_t rvllm_fp8_layer_block_workspace(int ffn);
+size_t rvllm_fp8_layer_block_workspace(int hidden, int ffn);
 int rvllm_fp8_layer_block(int M, int hidden, int ffn, int o_k, int act, int dtype, float eps, const void* attn_out16,
                           const float* attn_amax, int amax_parts, const void* attn_fp8, const float* attn_scale,
                           const void* o_w, const float* o_scale, void* residual, const void* mlp_norm_gamma,
@@ -335,8 +349,9 @@ int rvllm_fused_norm_add_residual_launch(const void* gemm_out, int gemm_out_is_f
                                          int hidden, float eps, int dtype, void* stream);
 /* residual *= *scalar (ResidualScaleF16Launch, gemma4_launcher.rs:572-616; v3/kernels/residual_scale_f16.cu:13-27). */
 int rvllm_residual_scale_launch(void* residual, const void* scalar, int num_tokens, int hidden, int dtype, void* stream);
-/* logits = cap * tanh(logits / cap) in place on 16-bit logits (LogitSoftcapLaunch, gemma4_launcher.rs:953-996;
- * v3/kernels/logit_softcap.cu:12-31; call site v3/crates/rvllm-runtime/src/gemma4_bring_up.rs:2144-2151). */
+/* logits = cap * tanh(logits / cap) in place (LogitSoftcapLaunch, gemma4_launcher.rs:953-996;
+ * v3/kernels/logit_softcap.cu:12-31; call site v3/crates/rvllm-runtime/src/gemma4_bring_up.rs:2144-2151).  dtype
+ * RVLLM_F16 / RVLLM_BF16 as the reference kernel (16-bit logits), or RVLLM_OUT_F32 for f32 logits. */
 int rvllm_logit_softcap_launch(void* logits, int num_tokens, int vocab, float cap, int dtype, void* stream);
 
 /* FP8 encode / decode of a flat array with the kernels' own convert instructions

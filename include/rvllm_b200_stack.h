@@ -6,7 +6,7 @@
  * reference): RMSNorm+FP8 quant -> QKV GEMM -> RoPE + Q quant + paged FP8 KV write ->
  * split-KV decode attention -> per-token quant -> O GEMM (+residual, in place) ->
  * RMSNorm+FP8 quant -> gate|up GEMM -> act*up+quant -> down GEMM (+residual); then final
- * RMSNorm+quant -> LM-head GEMM (f32 logits) -> argmax -> token feedback and position /
+ * RMSNorm+quant -> LM-head GEMM (f32 logits) -> [soft cap] -> argmax -> token feedback and position /
  * slot bookkeeping on the device (what the reference does with three small host uploads
  * per step, v3/crates/rvllm-runtime/src/gemma4_serve.rs:884-901).  Sliding layers keep a
  * ring cache (page % table length) and attend the last `sliding_window` tokens.
@@ -50,6 +50,10 @@ typedef struct {
                             fixed ring of sliding_window tokens per sequence */
     int fused_block;     /* 1: where the shape allows (batch <= 32), everything between two attention calls is one
                             launch (rvllm_fp8_layer_block); 0: always the stand-alone kernels.  Same bytes either way. */
+    int fused_argmax;    /* 1: the LM head keeps per-tile argmax winners and a merge picks the token
+                            (rvllm_fp8_gemm_lm_head_argmax; no f32 logits are written, debug read 1 is refused);
+                            0: f32 logits, then argmax.  Same tokens either way. */
+    float logit_softcap; /* > 0: logits pass through cap * tanh(x / cap) before the argmax; 0 = none */
 } rvllm_stack_config;
 
 typedef struct {

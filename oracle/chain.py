@@ -72,6 +72,9 @@ class OracleChain:
             resid = o.fp8_gemm(h8, L["down_w"], hs, L["down_scale"], residual=resid, out_kind=dt)
         x8, xs = o.rmsnorm_fp8_quant(resid, self.head["final_norm_gamma"], c["rms_eps"], dt)
         logits = o.fp8_gemm(x8, self.head["lm_head_w"], xs, self.head["lm_head_scale"], out_kind=2)
+        cap = np.float32(c.get("logit_softcap", 0.0))
+        if cap > 0:  # logit_softcap_kernel's arithmetic on f32 logits: cap * tanhf(x * (1 / cap))
+            logits = (cap * np.tanh(logits * (np.float32(1.0) / cap))).astype(np.float32)
         self.pos += 1
         return logits
 

@@ -66,7 +66,9 @@ SIGNATURES = {
     "rvllm_fp8_gemm_tc_reduce": (None, [_i32]),
     "rvllm_fp8_gemm_residual_from16": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "rvllm_fp8_gemm_qkv_rope_fp8kv": (_i32, [_vp] * 4 + [_i32] * 6 + [_vp] * 10 + [_i32] * 2 + [_vp]),
-    "rvllm_fp8_layer_block_workspace": (_sz, [_i32]),
+    "rvllm_fp8_gemm_lm_head_argmax_workspace": (_sz, [_i32, _i32]),
+    "rvllm_fp8_gemm_lm_head_argmax": (_i32, [_vp] * 5 + [_i32] * 3 + [_f32, _vp, _sz, _vp]),
+    "rvllm_fp8_layer_block_workspace": (_sz, [_i32, _i32]),
     "rvllm_fp8_layer_block": (_i32, [_i32] * 6 + [_f32, _vp, _vp, _i32] + [_vp] * 16 + [_sz, _i32, _vp]),
     "rvllm_fa_sm89_abi_version": (_i32, []),
     "fa_sm89_fp8_output_dtype": (_i32, []),

@@ -351,10 +351,13 @@ int rvllm_logit_softcap_launch(void* logits, int num_tokens, int vocab, float ca
     if (num_tokens <= 0 || vocab <= 0) return rv_fail(RVLLM_E_INVALID, "zero dim");          // gemma4_launcher.rs:960-963
     if (!isfinite(cap) || cap <= 0.0f) return rv_fail(RVLLM_E_INVALID, "cap must be > 0");   // :964-966
     if (!logits) return rv_fail(RVLLM_E_INVALID, "null device pointer");
-    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16 && dtype != RVLLM_OUT_F32)
+        return rv_fail(RVLLM_E_INVALID, "dtype must be f16, bf16 or f32");
     dim3 grid(num_tokens), block(block_for((uint32_t)vocab));
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == RVLLM_F16)
+    if (dtype == RVLLM_OUT_F32)
+        rv_launch(logit_softcap_f32_kernel, grid, block, 0, s, dim3(1, 1, 1), (float*)logits, vocab, cap);
+    else if (dtype == RVLLM_F16)
         rv_launch(logit_softcap_kernel, grid, block, 0, s, dim3(1, 1, 1), (__half*)logits, vocab, cap);
     else
         rv_launch(logit_softcap_bf16_kernel, grid, block, 0, s, dim3(1, 1, 1), (__nv_bfloat16*)logits, vocab, cap);

@@ -307,9 +307,45 @@ int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void*
                                                 stream);
 }
 
-size_t rvllm_fp8_layer_block_workspace(int ffn) {
-    if (ffn <= 0 || ffn % 64 != 0) return 0;
-    return rvblk::blk_workspace_bytes(ffn);
+size_t rvllm_fp8_gemm_lm_head_argmax_workspace(int M, int vocab) {
+    if (M <= 0 || vocab <= 0) return 0;
+    const size_t tiles = ((size_t)vocab + 127) / 128;
+    return 2 * (((size_t)M * tiles * 4 + 255) & ~(size_t)255);
+}
+
+int rvllm_fp8_gemm_lm_head_argmax(int32_t* out_tokens, const void* a_fp8, const void* w_fp8, const float* a_scale,
+                                  const float* w_scale, int M, int vocab, int K, float softcap, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    GemmArgs g = {out_tokens, RVLLM_OUT_F32, a_fp8, w_fp8, a_scale, w_scale, nullptr, M, vocab, K};
+    int rc = validate_gemm(g);
+    if (rc) return rc;
+    if (!isfinite(softcap) || softcap < 0.0f) return rv_fail(RVLLM_E_INVALID, "softcap must be finite and >= 0 (0 = none)");
+    if (K % 16 != 0) return rv_fail(RVLLM_E_UNSUPPORTED, "K must be a multiple of 16");
+    const size_t need = rvllm_fp8_gemm_lm_head_argmax_workspace(M, vocab);
+    if (!workspace || !rv_aligned(workspace, 256) || workspace_bytes < need)
+        return rv_fail(RVLLM_E_WORKSPACE, "argmax workspace missing, misaligned or too small");
+    rvtc::TcArgs t;
+    t.out = nullptr;
+    t.out_kind = RVLLM_OUT_F32;
+    t.a = a_fp8;
+    t.w = w_fp8;
+    t.a_scale = a_scale;
+    t.w_scale = w_scale;
+    t.residual = nullptr;
+    t.M = M;
+    t.N = vocab;
+    t.K = K;
+    t.arg_val = (float*)workspace;
+    t.arg_idx = (int*)((char*)workspace + need / 2);
+    t.softcap = softcap;
+    rc = rvtc::launch_argmax(t, out_tokens, (cudaStream_t)stream);
+    if (rc == -3) return RVLLM_E_UNSUPPORTED;
+    return rc;
+}
+
+size_t rvllm_fp8_layer_block_workspace(int hidden, int ffn) {
+    if (ffn <= 0 || ffn % 64 != 0 || hidden <= 0 || hidden % 128 != 0) return 0;
+    return rvblk::blk_workspace_bytes(ffn, hidden);
 }
 
 int rvllm_fp8_layer_block(int M, int hidden, int ffn, int o_k, int act, int dtype, float eps, const void* attn_out16,
@@ -338,7 +374,7 @@ int rvllm_fp8_layer_block(int M, int hidden, int ffn, int o_k, int act, int dtyp
         !rv_aligned(h_fp8, 16) || (attn_out16 && !rv_aligned(attn_out16, 16)) || (attn_fp8 && !rv_aligned(attn_fp8, 16)) ||
         (residual && !rv_aligned(residual, 16)))
         return rv_fail(RVLLM_E_INVALID, "operands must be 16-byte aligned");
-    if (!workspace || !rv_aligned(workspace, 256) || workspace_bytes < rvblk::blk_workspace_bytes(ffn))
+    if (!workspace || !rv_aligned(workspace, 256) || workspace_bytes < rvblk::blk_workspace_bytes(ffn, hidden))
         return rv_fail(RVLLM_E_WORKSPACE, "layer-block workspace missing, misaligned or too small");
     rvblk::BlkArgs g = {};
     g.M = M;

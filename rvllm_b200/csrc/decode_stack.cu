@@ -132,6 +132,8 @@ struct rvllm_stack {
     float* h_scale;      // [B]
     void* blk_ws;        // layer-block kernel: grid-barrier words + partial row maxima
     size_t blk_ws_bytes;
+    void* arg_ws;        // fused greedy tail: per-tile (logit, token) winners
+    size_t arg_ws_bytes;
     float* logits;       // [B, vocab]
     void* attn_ws;
     size_t attn_ws_bytes;
@@ -167,6 +169,8 @@ int validate_cfg(const rvllm_stack_config* c) {
     if (c->gemm_impl < 0 || c->gemm_impl > 2) return rv_fail(RVLLM_E_INVALID, "gemm_impl must be 0, 1 or 2");
     if (c->kv_pool_blocks < 0) return rv_fail(RVLLM_E_INVALID, "kv_pool_blocks must be >= 0");
     if (c->fused_block != 0 && c->fused_block != 1) return rv_fail(RVLLM_E_INVALID, "fused_block must be 0 or 1");
+    if (c->fused_argmax != 0 && c->fused_argmax != 1) return rv_fail(RVLLM_E_INVALID, "fused_argmax must be 0 or 1");
+    if (!isfinite(c->logit_softcap) || c->logit_softcap < 0.0f) return rv_fail(RVLLM_E_INVALID, "logit_softcap must be >= 0");
     return RVLLM_OK;
 }
 
@@ -226,8 +230,10 @@ size_t layout(rvllm_stack* s, uint8_t* base) {
     s->attn_scale = (float*)take((size_t)B * sizeof(float));
     s->h_fp8 = take((size_t)B * c.ffn);
     s->h_scale = (float*)take((size_t)B * sizeof(float));
-    s->blk_ws_bytes = rvllm_fp8_layer_block_workspace(c.ffn);   // (0 when ffn is not a multiple of 64: the kernel is not used then)
+    s->blk_ws_bytes = rvllm_fp8_layer_block_workspace(c.hidden, c.ffn);   // (0 when the shape is never taken: the kernel is not used then)
     s->blk_ws = take(s->blk_ws_bytes ? s->blk_ws_bytes : 256);  // zeroed with the arena: the barrier words start at zero
+    s->arg_ws_bytes = rvllm_fp8_gemm_lm_head_argmax_workspace(B, c.vocab);
+    s->arg_ws = take(s->arg_ws_bytes);
     s->logits = (float*)take((size_t)B * c.vocab * sizeof(float));
     uint64_t aw = 0;
     for (int hd : {c.sliding_head_dim, c.global_head_dim}) {
@@ -395,14 +401,31 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                                     s->head.final_norm_gamma, c.dtype, st));
         n++;
     }
-    RV_TRY(rvllm_fp8_gemm_channelscale(s->logits, RVLLM_OUT_F32, s->x_fp8, s->head.lm_head_w, s->x_scale,
-                                       s->head.lm_head_scale, nullptr, B, c.vocab, H, c.gemm_impl, s->gemm_ws,
-                                       s->gemm_ws_bytes, st));
-    RV_TRY(rvllm_argmax_launch(B, c.vocab, s->logits, s->next_tokens, 0, st));
+    // Greedy tail: the LM head keeps only each weight tile's best (logit, token) and a merge picks the row's winner
+    // (no [batch, vocab] f32 logits in HBM); or the LM head into f32 logits, the optional soft cap, argmax.
+    int tail = RVLLM_E_UNSUPPORTED;
+    if (c.fused_argmax != 0 && c.gemm_impl != 1)
+        tail = rvllm_fp8_gemm_lm_head_argmax(s->next_tokens, s->x_fp8, s->head.lm_head_w, s->x_scale, s->head.lm_head_scale,
+                                             B, c.vocab, H, c.logit_softcap, s->arg_ws, s->arg_ws_bytes, st);
+    if (tail == RVLLM_OK) {
+        n += 2;
+    } else {
+        if (tail != RVLLM_E_UNSUPPORTED) RV_TRY(tail);
+        RV_TRY(rvllm_fp8_gemm_channelscale(s->logits, RVLLM_OUT_F32, s->x_fp8, s->head.lm_head_w, s->x_scale,
+                                           s->head.lm_head_scale, nullptr, B, c.vocab, H, c.gemm_impl, s->gemm_ws,
+                                           s->gemm_ws_bytes, st));
+        n++;
+        if (c.logit_softcap > 0.0f) {
+            RV_TRY(rvllm_logit_softcap_launch(s->logits, B, c.vocab, c.logit_softcap, RVLLM_OUT_F32, st));
+            n++;
+        }
+        RV_TRY(rvllm_argmax_launch(B, c.vocab, s->logits, s->next_tokens, 0, st));
+        n++;
+    }
     rv_launch(advance_kernel, dim3(1), dim3(256), 0, s->stream, dim3(1, 1, 1), s->tokens, s->next_tokens, s->positions, s->prompt, c.prompt_len,
                                              s->history, s->step_counter, c.max_steps, B);
     RV_TRY(rv_launched("advance"));
-    n += 3;
+    n += 1;
     if (launches) *launches = n;
     return RVLLM_OK;
 }
@@ -701,7 +724,12 @@ int rvllm_stack_debug_read(rvllm_stack* s, int what, void* host_out, size_t byte
     const void* src = nullptr;
     size_t have = 0;
     if (what == 0) { src = s->residual; have = (size_t)s->cfg.batch * s->cfg.hidden * 2; }
-    else if (what == 1) { src = s->logits; have = (size_t)s->cfg.batch * s->cfg.vocab * 4; }
+    else if (what == 1) {
+        if (s->cfg.fused_argmax != 0 && s->cfg.gemm_impl != 1)
+            return rv_fail(RVLLM_E_INVALID, "logits are not materialised when the argmax is fused into the LM head");
+        src = s->logits;
+        have = (size_t)s->cfg.batch * s->cfg.vocab * 4;
+    }
     else if (what == 2) { src = s->positions; have = (size_t)s->cfg.batch * 4; }
     else return rv_fail(RVLLM_E_INVALID, "unknown buffer");
     if (bytes > have) return rv_fail(RVLLM_E_INVALID, "buffer is smaller than requested");

@@ -88,6 +88,11 @@ struct TcParams {
     const void* a16;
     const float* amax_part;
     int amax_parts;
+    // EPI_ARGMAX only: nothing is stored but each weight tile's best (value, output channel) per batch row,
+    // arg_val / arg_idx [M][tiles]; softcap > 0 applies cap * tanh(x / cap) to the value first
+    float* arg_val;
+    int* arg_idx;
+    float softcap;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -210,7 +215,15 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
     return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
 }
 
-constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2, EPI_QKV_ROPE = 3, EPI_RESIDUAL_A16 = 4;
+constexpr int EPI_SCALE = 0, EPI_RESIDUAL = 1, EPI_F32 = 2, EPI_QKV_ROPE = 3, EPI_RESIDUAL_A16 = 4, EPI_ARGMAX = 5;
+
+// Greedy-argmax candidates: a candidate wins if its value is greater, or equal with a lower index; index -1 = no
+// candidate (NaN is never one); -inf may win.  The rule of the reference's argmax kernels (kernels/argmax.cu:16-25).
+__device__ __forceinline__ bool arg_better(float cv, int ci, float bv, int bi) {
+    if (ci < 0) return false;
+    if (bi < 0) return true;
+    return cv > bv || (cv == bv && ci < bi);
+}
 
 constexpr int MAX_STAGES = 8;
 constexpr int HEADER_BYTES = 1024;  // barriers + TMEM address holder, in front of the ring
@@ -253,6 +266,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr bool A16 = EPI == EPI_RESIDUAL_A16;           // A tiles are quantised here from 16-bit activations
     constexpr bool RES = EPI == EPI_RESIDUAL || A16;        // residual epilogue
     __shared__ float s_ascale[A16 ? BN : 1], s_ainv[A16 ? BN : 1];
+    constexpr bool ARG = EPI == EPI_ARGMAX;                 // per-tile argmax partials instead of stored logits
+    __shared__ float s_argv[ARG ? 4 * BN : 1];
+    __shared__ int s_argi[ARG ? 4 * BN : 1];
     auto a_scale_of = [&](int m) -> float { return A16 ? s_ascale[m - m0] : p.a_scale[m]; };
     rv::pdl_launch();
     if (threadIdx.x == 0) {
@@ -543,13 +559,15 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (sp < S) sum += recv[(size_t)(sp * LC + lc) * TILE_W + r];
             const float as = pre ? as_p : a_scale_of(m);
             const float ws = pre ? ws_p : p.w_scale[n];
-            float val = as * (ws * sum);  // same association as the unsplit epilogue
             const size_t o = (size_t)m * p.N + n;
             if (EPI == EPI_F32) {
-                reinterpret_cast<float*>(p.out)[o] = val;
+                reinterpret_cast<float*>(p.out)[o] = as * (ws * sum);  // same association as the unsplit epilogue
             } else {
-                if (RES)
-                    val += pre ? res_p : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                float val;
+                if (RES)  // one rounding for scale-and-add, spelled out so that every form of the epilogue agrees
+                    val = fmaf(as, ws * sum, pre ? res_p : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]));
+                else
+                    val = as * (ws * sum);
                 reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
             }
         };
@@ -578,7 +596,37 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[j] = 0u;
             }
-            if (S > 1) {
+            if constexpr (ARG) {
+                // the logit this element would have been, (soft-capped,) then the best of the warp's 32 output channels
+                const float inv_cap = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int m = m0 + c0 + j;
+                    float bv = -CUDART_INF_F;
+                    int bi = -1;
+                    if (m < p.M && n < p.N) {
+                        float val = a_scale_of(m) * (ws * __uint_as_float(v[j]));
+                        if (p.softcap > 0.0f) val = p.softcap * tanhf(val * inv_cap);
+                        if (val == val) {
+                            bv = val;
+                            bi = n;
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                        if (arg_better(ov, oi, bv, bi)) {
+                            bv = ov;
+                            bi = oi;
+                        }
+                    }
+                    if (lane == 0) {
+                        s_argv[quarter * BN + c0 + j] = bv;
+                        s_argi[quarter * BN + c0 + j] = bi;
+                    }
+                }
+            } else if (S > 1) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) part[(size_t)(c0 + j) * TILE_W + r] = __uint_as_float(v[j]);
             } else {
@@ -592,7 +640,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             reinterpret_cast<float*>(p.out)[o] = val;
                         } else {
                             if (RES)
-                                val += rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                                val = fmaf(a_scale_of(m), ws * __uint_as_float(v[j]),
+                                           rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]));
                             reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
                         }
                     }
@@ -638,7 +687,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     reinterpret_cast<float*>(p.out)[o] = val;
                 } else {
                     if (RES)
-                        val += have_res ? res : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]);
+                        val = fmaf(as, ws * sum, have_res ? res : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]));
                     reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
                 }
             }
@@ -680,9 +729,68 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     }
     __syncthreads();
+    if constexpr (ARG) {
+        // the tile's winner per batch row: the four warps' winners in output-channel order
+        for (int c = (int)threadIdx.x; c < BN; c += THREADS) {
+            float bv = -CUDART_INF_F;
+            int bi = -1;
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                if (arg_better(s_argv[q * BN + c], s_argi[q * BN + c], bv, bi)) {
+                    bv = s_argv[q * BN + c];
+                    bi = s_argi[q * BN + c];
+                }
+            if (m0 + c < p.M) {
+                p.arg_val[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = bv;
+                p.arg_idx[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = bi;
+            }
+        }
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// Second half of the fused greedy tail: the row's winner over the per-tile winners.  grid = rows, block = 256.
+__global__ void __launch_bounds__(256) argmax_merge_kernel(const float* __restrict__ val, const int* __restrict__ idx,
+                                                          int tiles, int* __restrict__ out) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    rv::pdl_launch();
+    rv::pdl_wait();
+    const int row = blockIdx.x;
+    float bv = -CUDART_INF_F;
+    int bi = -1;
+    for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+        const float v = val[(size_t)row * tiles + t];
+        const int i = idx[(size_t)row * tiles + t];
+        if (arg_better(v, i, bv, bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (arg_better(ov, oi, bv, bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = bv;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (arg_better(sv[w], si[w], bv, bi)) {
+                bv = sv[w];
+                bi = si[w];
+            }
+        out[row] = bi;
     }
 }
 
@@ -699,6 +807,9 @@ struct TcArgs {
     const void* a16 = nullptr;          // EPI_RESIDUAL_A16: 16-bit activations instead of `a` / `a_scale`
     const float* amax_part = nullptr;
     int amax_parts = 0;
+    float* arg_val = nullptr;           // EPI_ARGMAX
+    int* arg_idx = nullptr;
+    float softcap = 0.0f;
 };
 
 inline size_t workspace_bytes(int, int, int) { return 0; }
@@ -815,6 +926,11 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     p.a16 = g.a16;
     p.amax_part = g.amax_part;
     p.amax_parts = g.amax_parts;
+    p.arg_val = g.arg_val;
+    p.arg_idx = g.arg_idx;
+    p.softcap = g.softcap;
+    if (EPI == EPI_ARGMAX && (splits != 1 || !g.arg_val || !g.arg_idx))
+        return rvhost::fail_msg(-3, "the argmax epilogue needs an unsplit launch and its partial buffers");
     if (EPI == EPI_RESIDUAL_A16 && (!g.a16 || !g.amax_part || g.amax_parts <= 0 || BN > 32))
         return rvhost::fail_msg(-3, "the 16-bit activation form needs a16, partial maxima and a batch tile of at most 32 rows");
     if (EPI == EPI_QKV_ROPE && (!push || !rope))
@@ -858,6 +974,15 @@ int launch_epi(const TcArgs& g, int splits, int stages, cudaStream_t s) {
 inline int pick_splits(int M, int N, int K, int bn) {
     const int tiles = ((N + TILE_W - 1) / TILE_W) * ((M + bn - 1) / bn);
     const int kblocks = (K + BK - 1) / BK;
+    // 256-row batch tiles (M > 128) are tensor-bound, one CTA per SM: split only while the tiles leave SMs idle
+    // (measured at M = 512 on the QKV shape: 117 us split three ways with the pull reduction, against 155 us for
+    // four times the work unsplit)
+    if (bn >= 256) {
+        int s2 = 148 / tiles;
+        if (s2 > 8) s2 = 8;
+        while (s2 > 1 && kblocks / s2 < 4) s2--;
+        return s2 < 1 ? 1 : s2;
+    }
     int s = (360 + tiles / 2) / tiles;
     if (s > 8) s = 8;
     while (s > 1 && kblocks / s < 4) s--;
@@ -929,6 +1054,31 @@ inline int launch_residual_a16(const TcArgs& g, int dtype, cudaStream_t s) {
                           : launch_one<16, EPI_RESIDUAL_A16, __nv_bfloat16>(g, pl.splits, pl.stages, s);
     return dtype == 0 ? launch_one<32, EPI_RESIDUAL_A16, __half>(g, pl.splits, pl.stages, s)
                       : launch_one<32, EPI_RESIDUAL_A16, __nv_bfloat16>(g, pl.splits, pl.stages, s);
+}
+
+// LM head with the greedy argmax in the epilogue: per-tile winners into arg_val / arg_idx [M][ceil(N / 128)], then the
+// merge kernel.  Always an unsplit launch (a vocabulary-sized N has thousands of tiles; the plan would not split it).
+inline int launch_argmax(const TcArgs& g, int* out_tokens, cudaStream_t s) {
+    if (g.K % 16 != 0) return rvhost::fail_msg(-3, "tcgen05 GEMM needs K to be a multiple of 16");
+    Plan pl = plan_for(g.M, g.N, g.K);
+    pl.splits = 1;
+    pl.stages = tune().stages.load() > 0 ? tune().stages.load() : pick_stages(pl.bn, 1);
+    int rc;
+    switch (pl.bn) {
+        case 16: rc = launch_one<16, EPI_ARGMAX, __half>(g, 1, pl.stages, s); break;
+        case 32: rc = launch_one<32, EPI_ARGMAX, __half>(g, 1, pl.stages, s); break;
+        case 64: rc = launch_one<64, EPI_ARGMAX, __half>(g, 1, pl.stages, s); break;
+        case 128: rc = launch_one<128, EPI_ARGMAX, __half>(g, 1, pl.stages, s); break;
+        default: rc = launch_one<256, EPI_ARGMAX, __half>(g, 1, pl.stages, s); break;
+    }
+    if (rc) return rc;
+    const int tiles = (g.N + TILE_W - 1) / TILE_W;
+    if (rv_launch(argmax_merge_kernel, dim3(g.M), dim3(256), 0, s, dim3(1, 1, 1), (const float*)g.arg_val, (const int*)g.arg_idx,
+                  tiles, out_tokens) != cudaSuccess) {
+        cudaGetLastError();
+        return rvhost::fail_msg(-2, "argmax merge launch failed");
+    }
+    return 0;
 }
 
 inline int read_status(int* out, bool reset) {

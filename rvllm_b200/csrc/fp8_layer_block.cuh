@@ -13,14 +13,16 @@
 // step.  Here the CTAs stay resident, meet at grid-wide barriers, and each CTA's TMA producer keeps
 // fetching the next stage's weight tiles (they depend on nothing) while the barrier is in flight.
 //
-// Geometry: hidden = 128 * T.  Grid (T, 8), cluster (1, 8, 1): G = 8 T CTAs, all resident at once (three per
-// SM; the host checks the occupancy before it launches).  CTA (c, s), linear id j = 8 c + s:
-//   O, down   : weight tile c (128 output channels), K slice s of 8; the cluster reduces its partials by
-//               pushing them into the finishing CTA's receive buffer (distributed shared memory).
+// Geometry: hidden = 128 * T.  Grid (T, 8): G = 8 T CTAs, all resident at once (three per SM; the host checks
+// the occupancy before it launches; no clusters, so nothing constrains where a CTA lands).  CTA (c, s), linear
+// id j = 8 c + s:
+//   O, down   : weight tile c (128 output channels), K slice s of 8; the f32 partial tile goes to a small
+//               workspace in L2 (8 x 32 x hidden floats), the row's owner sums the eight slices in slice order.
 //   gate|up   : unit j = 64 gate rows + the 64 up rows of the same columns as ONE 128-row tcgen05 operand
 //               (two 64-row TMA boxes), whole K; gate and up of a column then sit in the same CTA, so
 //               act(gate)*up needs no exchange.  ffn / 64 <= G units; CTAs beyond that idle in this stage.
-//   RMSNorm   : CTA j < M owns row j.
+//   rows      : CTA j < M owns batch row j: it finishes the split-K sum of the row (+ residual), and runs the
+//               RMSNorm + quantisation on the values it just produced.
 // Warp roles as in the stand-alone GEMM: warp 0 lane 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2-5 = A-tile builder (O stage) / epilogue / row kernels / grid barrier.
 //
@@ -35,11 +37,10 @@ namespace rvblk {
 using namespace rvtc;
 
 constexpr int BN = 32;            // batch rows per tile (M <= 32)
-constexpr int CL = 8;             // CTAs per cluster = K slices of the O / down stages
-constexpr int LC = BN / CL;       // batch columns a CTA finishes in a split-K stage
+constexpr int CL = 8;             // K slices of the O / down stages (gridDim.y)
 constexpr int STAGES = 2;         // TMA ring depth: three CTAs of ~60 KB share an SM
 constexpr int STAGE_BYTES = TILE_W * BK + BN * BK;   // 16 KB weights + 4 KB activations
-constexpr int SCRATCH_BYTES = TILE_W * (BN + 1) * 4; // gate|up exchange tile [128][33] f32; also the receive buffer / a row
+constexpr int SCRATCH_BYTES = TILE_W * (BN + 1) * 4; // gate|up exchange tile [128][33] f32; also a row + its partial sums
 constexpr int MAX_HIDDEN = 6144;  // a row (2 B / value) + 1024 partial sums must fit the scratch area
 constexpr int BLK_HEADER = 2048;  // barriers, TMEM address, per-row scales and small reduction arrays, in front of the ring
 constexpr int SMEM_BYTES = 1024 + BLK_HEADER + STAGES * STAGE_BYTES + SCRATCH_BYTES;
@@ -70,6 +71,7 @@ struct BlkParams {
     const float* d_wscale;
     unsigned int* bar;        // [0] arrivals, [32] departures (separate 128-byte lines); zero between launches
     float* amax_ws;           // [F / 64][BN] partial row maxima of act(gate)*up
+    float* part;              // [CL][BN][H] f32 split-K partial tiles of the O / down stage
 };
 
 // ---- small helpers -------------------------------------------------------------------------------------
@@ -125,7 +127,7 @@ __device__ __forceinline__ void grid_barrier(unsigned int* arrive, unsigned int 
 // 1e-12; x * (1 / scale).  Bytes and scale equal that kernel's.  scratch: [H] 16-bit row, then NV floats.
 template <typename T>
 __device__ __forceinline__ void norm_quant_row(const BlkParams& p, const void* gamma_v, int row, int t, uint8_t* scratch,
-                                               float* s_small) {
+                                               float* s_small, bool row_staged) {
     const int H = p.H;
     T* srow = reinterpret_cast<T*>(scratch);
     float* partial = reinterpret_cast<float*>(scratch + (((size_t)H * 2 + 15) & ~(size_t)15));
@@ -134,9 +136,11 @@ __device__ __forceinline__ void norm_quant_row(const BlkParams& p, const void* g
     int NV = H < 1024 ? H : 1024;
     NV -= NV % 32;
     const int nvec = H >> 3;
-    for (int v = t; v < nvec; v += EPI_THREADS)   // the row was written by other CTAs in this launch: read through L2
-        reinterpret_cast<uint4*>(srow)[v] = __ldcg(reinterpret_cast<const uint4*>(x) + v);
-    epi_sync();
+    if (!row_staged) {  // (else the caller has just produced the row into `scratch`)
+        for (int v = t; v < nvec; v += EPI_THREADS)
+            reinterpret_cast<uint4*>(srow)[v] = __ldcg(reinterpret_cast<const uint4*>(x) + v);
+        epi_sync();
+    }
     for (int v = t; v < NV; v += EPI_THREADS) {
         float ss = 0.0f;
         for (int i = v; i < H; i += NV) {
@@ -215,8 +219,7 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
     uint64_t* acc_ready = empty + STAGES;                        // the stage's accumulator is complete
     uint64_t* acc_free = acc_ready + 1;                          // the epilogue has read the accumulator
     uint64_t* gate = acc_free + 1;                               // the activations of the next GEMM stage exist
-    uint64_t* recv_bar = gate + 1;                               // all split-K partials for this CTA have landed
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(recv_bar + 1);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(gate + 1);
     float* s_ascale = reinterpret_cast<float*>(header + 256);    // [BN] activation scale of the current GEMM stage
     float* s_ainv = s_ascale + BN;                               // [BN]
     float* s_small = s_ainv + BN;                                // [40] reductions of the row kernels
@@ -245,7 +248,6 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
         mbar_init(acc_ready, 1);
         mbar_init(acc_free, 4);
         mbar_init(gate, 1);
-        mbar_init(recv_bar, (uint32_t)CL * 4u);
         fence_barrier_init();
         // This thread is also the TMA producer.  Weights depend on nothing: the first O-stage tiles are on their
         // way before the block, the cluster or the predecessor kernel are waited for.
@@ -260,10 +262,6 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    // "this CTA runs and its barriers exist": remote stores and remote arrivals are safe once every CTA of the
-    // cluster has said so (the CTAs of a cluster start together, so this is a short wait)
-    cluster_arrive();
-    cluster_wait();
 
     if (warp == 0) {
         // ================================================================ TMA producer
@@ -370,29 +368,17 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
         const int r = quarter * 32 + lane;                 // row of the weight tile held by this thread
         unsigned int* bar_arrive = p.bar;
         unsigned int* bar_depart = p.bar + 32;
-        uint32_t acc_uses = 0, recv_uses = 0, barriers = 0;
+        uint32_t acc_uses = 0, barriers = 0;
         int it = 0;
         bool alive = true;
-        float* recv = reinterpret_cast<float*>(scratch);   // [CL][LC][TILE_W]
 
-        // split-K epilogue shared by the O and the down stage: push the partial tile to the finishing CTAs, meet,
-        // sum in cluster-rank order, scale, add the residual, store.  a_scale_of(m) for this stage is in s_ascale.
-        auto splitk_epilogue = [&](int n_kb, const float* w_scale) {
-            // scales and residual of this thread's output elements do not depend on the MMAs: fetch them first
-            float pre_res[LC];
-            const int n = tile * TILE_W + t;  // this thread finishes output channel n for the CTA's LC batch rows
-            const float ws_n = w_scale[n];
-#pragma unroll
-            for (int lc = 0; lc < LC; lc++) {
-                const int m = lc * CL + split;
-                // (in the down stage this is the value this same thread stored in the O stage)
-                pre_res[lc] = m < p.M ? ld16_cg<OutT>(reinterpret_cast<const OutT*>(p.residual) + (size_t)m * p.H + n) : 0.0f;
-            }
+        // Epilogue of a split-K stage (O, down): this CTA's f32 partial tile [BN rows][128 channels] goes to the
+        // workspace, slice-major, so that a warp stores 128 contiguous bytes per batch row.
+        auto store_partial = [&](int n_kb) {
             bool ready = true;
             if (n_kb > 0) ready = mbar_wait(acc_ready, acc_uses & 1u, 3);
             tc_fence_after();
-            const uint32_t slot = smem_u32(recv) + (uint32_t)((split * LC) * TILE_W + r) * 4u;  // [split][0][r]
-            uint32_t owner = 0, lc_off = 0;
+            float* dst = p.part + ((size_t)split * BN) * p.H + (size_t)tile * TILE_W + r;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t v[16];
@@ -404,13 +390,8 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                     for (int q = 0; q < 16; q++) v[q] = 0u;
                 }
 #pragma unroll
-                for (int q = 0; q < 16; q++) {
-                    st_peer_f32(slot + lc_off, owner, __uint_as_float(v[q]));
-                    if (++owner == (uint32_t)CL) {
-                        owner = 0;
-                        lc_off += TILE_W * 4;
-                    }
-                }
+                for (int q = 0; q < 16; q++)
+                    if (c0 + q < p.M) __stcg(dst + (size_t)(c0 + q) * p.H, __uint_as_float(v[q]));
             }
             tc_fence_before();
             if (n_kb > 0) {
@@ -418,30 +399,44 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                 if (lane == 0) mbar_arrive(acc_free);
                 acc_uses++;
             }
-            asm volatile("fence.acq_rel.cluster;" ::: "memory");
-            __syncwarp();
-            if (lane < CL) mbar_arrive_peer(recv_bar, (uint32_t)lane);
-            mbar_wait_cluster(recv_bar, recv_uses & 1u, 4);
-            recv_uses++;
+        };
+
+        // Row owner (CTA j < M, row j), after the grid barrier that follows a split-K stage: sum the eight slices in
+        // slice order, scale, add the residual, store the new residual row — out = a_scale * (w_scale * sum) +
+        // residual, the stand-alone GEMM's expression and summation order.  The row is left in `scratch` (16-bit) for
+        // the RMSNorm that follows.
+        auto finish_row = [&](int row, float a_scale, const float* w_scale) {
+            OutT* srow = reinterpret_cast<OutT*>(scratch);
+            OutT* res = reinterpret_cast<OutT*>(p.residual) + (size_t)row * p.H;
+            const float* part = p.part + (size_t)row * p.H;
+            const int nvec = p.H >> 2;
+            for (int v = t; v < nvec; v += EPI_THREADS) {
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // (0 + first slice: the stand-alone kernel's order, signed zeros included)
 #pragma unroll
-            for (int lc = 0; lc < LC; lc++) {
-                const int m = lc * CL + split;
-                if (m >= p.M) continue;
-                float sum = 0.0f;
-#pragma unroll
-                for (int sp = 0; sp < CL; sp++) sum += recv[(size_t)(sp * LC + lc) * TILE_W + t];
-                const float val = s_ascale[m] * (ws_n * sum) + pre_res[lc];  // same association as the stand-alone GEMM
-                reinterpret_cast<OutT*>(p.residual)[(size_t)m * p.H + n] = rv::T16<OutT>::from_f32_sat(val);
+                for (int sp = 0; sp < CL; sp++) {
+                    const float4 x = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * BN * p.H) + v);
+                    sum.x += x.x;
+                    sum.y += x.y;
+                    sum.z += x.z;
+                    sum.w += x.w;
+                }
+                const float4 ws = *reinterpret_cast<const float4*>(w_scale + 4 * v);
+                const uint2 rb = __ldcg(reinterpret_cast<const uint2*>(res) + v);
+                const float2 r01 = rv::T16<OutT>::to_f32x2(rb.x), r23 = rv::T16<OutT>::to_f32x2(rb.y);
+                uint2 o;
+                o.x = rv::pack2_sat<OutT>(fmaf(a_scale, ws.x * sum.x, r01.x), fmaf(a_scale, ws.y * sum.y, r01.y));
+                o.y = rv::pack2_sat<OutT>(fmaf(a_scale, ws.z * sum.z, r23.x), fmaf(a_scale, ws.w * sum.w, r23.y));
+                reinterpret_cast<uint2*>(res)[v] = o;
+                reinterpret_cast<uint2*>(srow)[v] = o;
             }
+            epi_sync();
         };
 
         rv::pdl_wait();  // everything below reads what earlier kernels wrote
 
         // ---------------------------------------------------------------- O projection
         if (do_o && !o_a16) {
-            if (t < BN) s_ascale[t] = t < p.M ? p.attn_scale[t] : 0.0f;
-            epi_sync();
-            splitk_epilogue(nO, p.o_wscale);
+            store_partial(nO);
         } else if (do_o) {
             if (t < BN) {  // per-row activation scale from the partial maxima the attention kernel left
                 float amax = 0.0f;
@@ -499,13 +494,26 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(afull + s);
             }
-            splitk_epilogue(nO, p.o_wscale);
+            store_partial(nO);
         }
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 10);
 
-        // ---------------------------------------------------------------- RMSNorm + quant (input of gate|up)
-        if ((p.phases & PH_N1) && j < p.M) norm_quant_row<OutT>(p, p.gamma1, j, t, scratch, s_small);
+        // ---------------------------------------------------------------- rows: finish O, RMSNorm + quant (input of gate|up)
+        if (j < p.M) {
+            if (do_o) {
+                float a_scale;
+                if (o_a16) {  // the per-token quantiser's scale from the partial maxima the attention kernel left
+                    float amax = 0.0f;
+                    for (int q = 0; q < p.amax_parts; q++) amax = fmaxf(amax, p.attn_amax[(size_t)j * p.amax_parts + q]);
+                    a_scale = rv::row_scale(amax);
+                } else {
+                    a_scale = p.attn_scale[j];
+                }
+                finish_row(j, a_scale, p.o_wscale);
+            }
+            if (p.phases & PH_N1) norm_quant_row<OutT>(p, p.gamma1, j, t, scratch, s_small, /*row_staged=*/do_o);
+        }
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 11);
         if (t == 0) mbar_arrive(gate);  // x8 / xs exist: the producer may fetch the gate|up activations
@@ -584,7 +592,6 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                 o.w = rv::f32x4_to_e4m3x4(y[12] * inv, y[13] * inv, y[14] * inv, y[15] * inv);
                 *reinterpret_cast<uint4*>(p.h8 + (size_t)lane * p.F + (size_t)j * 64 + w4 * 16) = o;
             }
-            if (t < BN) s_ascale[t] = scale;  // (t = lane here for w4 == 0) activation scale of the down stage; rows >= M are never stored
         }
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 13);
@@ -592,18 +599,15 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
         it += nD;
 
         // ---------------------------------------------------------------- down projection
-        if (do_d) {
-            if (!(p.phases & PH_GU)) {
-                if (t < BN) s_ascale[t] = t < p.M ? __ldcg(p.hs + t) : 0.0f;
-            }
-            epi_sync();
-            splitk_epilogue(nD, p.d_wscale);
-        }
+        if (do_d) store_partial(nD);
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 14);
 
-        // ---------------------------------------------------------------- RMSNorm + quant for the next layer
-        if ((p.phases & PH_N2) && p.gamma2 && j < p.M) norm_quant_row<OutT>(p, p.gamma2, j, t, scratch, s_small);
+        // ---------------------------------------------------------------- rows: finish down, RMSNorm + quant for the next layer
+        if (j < p.M) {
+            if (do_d) finish_row(j, __ldcg(p.hs + j), p.d_wscale);
+            if ((p.phases & PH_N2) && p.gamma2) norm_quant_row<OutT>(p, p.gamma2, j, t, scratch, s_small, /*row_staged=*/do_d);
+        }
 
         // leave: the last CTA out puts the barrier words back to zero for the next launch
         epi_sync();
@@ -617,10 +621,7 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
             }
         }
     }
-    // no CTA of a cluster may exit while a peer can still store into its shared memory
     __syncwarp();
-    cluster_arrive();
-    cluster_wait();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
@@ -654,9 +655,10 @@ struct BlkArgs {
     size_t workspace_bytes;
 };
 
-// workspace: 256 bytes of barrier words (zero before the first launch; every launch leaves them zero), then the
-// [ffn / 64][32] partial row maxima
-inline size_t blk_workspace_bytes(int F) { return 256 + (size_t)(F / 64) * BN * sizeof(float); }
+// workspace: 256 bytes of barrier words (zero before the first launch; every launch leaves them zero), the
+// [ffn / 64][32] partial row maxima, the [8][32][hidden] f32 split-K partial tiles
+inline size_t blk_amax_bytes(int F) { return ((size_t)(F / 64) * BN * sizeof(float) + 255) & ~(size_t)255; }
+inline size_t blk_workspace_bytes(int F, int H) { return 256 + blk_amax_bytes(F) + (size_t)CL * BN * H * sizeof(float); }
 
 // Whether the shape is taken: M <= 32, hidden a multiple of 128 up to 6144, ffn a multiple of 64 with at most
 // one gate|up unit per CTA (ffn <= 4 * hidden), K of the O projection a multiple of 16.
@@ -674,38 +676,37 @@ template <typename OutT> int launch_block_t(const BlkArgs& g, cudaStream_t s) {
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = s;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = CL;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    // The grid-wide barriers need every CTA resident at once: ask the runtime how many clusters of this kernel fit
-    // on the device (once per device and grid size) and refuse shapes that do not.
+    // The grid-wide barriers need every CTA resident at once: ask the runtime how many CTAs of this kernel an SM
+    // holds (once per device) and refuse grids that do not fit.
     {
         static std::mutex mu;
-        static std::unordered_map<long long, int> fits;  // (device << 32 | clusters) -> max co-resident clusters
+        static std::unordered_map<int, int> capacity;  // device -> CTAs of this kernel resident at once
         const int dev = rv_current_device();
-        const long long key = ((long long)dev << 32) | (unsigned)cfg.gridDim.x;
         std::lock_guard<std::mutex> lock(mu);
-        auto it = fits.find(key);
-        int max_clusters = 0;
-        if (it == fits.end()) {
-            if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess) {
+        auto it = capacity.find(dev);
+        int cap = 0;
+        if (it == capacity.end()) {
+            int per_sm = 0, sms = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, SMEM_BYTES) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev < 0 ? 0 : dev) != cudaSuccess) {
                 cudaGetLastError();
-                max_clusters = 0;
+                per_sm = sms = 0;
             }
-            fits.emplace(key, max_clusters);
+            cap = per_sm * sms;
+            capacity.emplace(dev, cap);
         } else {
-            max_clusters = it->second;
+            cap = it->second;
         }
-        if (max_clusters < (int)cfg.gridDim.x) return rvhost::fail_msg(-3, "layer block: the grid would not be resident at once on this device");
+        if (cap < (int)(cfg.gridDim.x * cfg.gridDim.y))
+            return rvhost::fail_msg(-3, "layer block: the grid would not be resident at once on this device");
     }
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
     if (rv_pdl_enabled()) {
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.numAttrs = 2;
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
     }
     CUtensorMap mwo, mwgu, mwd, mao, mx8, mh8;
     if (g.attn16) mao = CUtensorMap{};  // unused in the 16-bit form
@@ -739,6 +740,7 @@ template <typename OutT> int launch_block_t(const BlkArgs& g, cudaStream_t s) {
     p.d_wscale = g.d_wscale;
     p.bar = (unsigned int*)g.workspace;
     p.amax_ws = (float*)((char*)g.workspace + 256);
+    p.part = (float*)((char*)g.workspace + 256 + blk_amax_bytes(g.F));
     if (cudaLaunchKernelEx(&cfg, kern, mwo, mwgu, mwd, mao, mx8, mh8, p) != cudaSuccess) {
         cudaGetLastError();
         return rvhost::fail_msg(-2, "layer-block kernel launch failed");

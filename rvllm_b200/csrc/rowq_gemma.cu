@@ -257,6 +257,16 @@ __device__ __forceinline__ void rope_cache_fp8kv_body(const T* q_in, const T* k_
                                           num_cache_slots);                                                             \
     }
 
+// f32 logits (this library's LM head writes f32): the same arithmetic without the 16-bit round trip
+extern "C" __global__ void __launch_bounds__(1024) logit_softcap_f32_kernel(float* logits, int vocab, float cap) {
+    rv::pdl_launch();
+    rv::pdl_wait();
+    if (!logits || vocab <= 0 || !isfinite(cap) || cap <= 0.0f) return;
+    const float inv_cap = 1.0f / cap;
+    float* row = logits + (long long)blockIdx.x * vocab;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) row[i] = cap * tanhf(row[i] * inv_cap);
+}
+
 RV_GEMMA_ENTRIES(, __half)
 RV_GEMMA_ENTRIES(_bf16, __nv_bfloat16)
 #undef RV_GEMMA_ENTRIES

@@ -19,7 +19,8 @@ class StackConfig(C.Structure):
                                        "sliding_head_dim", "global_head_dim", "sliding_window", "global_every",
                                        "act", "dtype", "batch", "block_size", "max_context", "max_steps",
                                        "prompt_len", "gemm_impl")] + \
-               [("rms_eps", C.c_float), ("rope_theta", C.c_float), ("seed", C.c_uint64), ("kv_pool_blocks", C.c_int), ("fused_block", C.c_int)]
+               [("rms_eps", C.c_float), ("rope_theta", C.c_float), ("seed", C.c_uint64), ("kv_pool_blocks", C.c_int), ("fused_block", C.c_int),
+                ("fused_argmax", C.c_int), ("logit_softcap", C.c_float)]
 
 
 class LayerWeights(C.Structure):
@@ -70,7 +71,7 @@ def gemma31b_shape(batch: int, **over) -> dict:
     cfg = dict(hidden=5376, ffn=21504, vocab=262144, num_layers=62, heads=32, kv_heads=16, sliding_head_dim=128,
                global_head_dim=256, sliding_window=1024, global_every=6, act=ACT_SILU, dtype=BF16, batch=batch,
                block_size=16, max_context=1024, max_steps=1024, prompt_len=512, gemm_impl=0, rms_eps=1e-6,
-               rope_theta=10000.0, seed=3, kv_pool_blocks=0, fused_block=1)
+               rope_theta=10000.0, seed=3, kv_pool_blocks=0, fused_block=1, fused_argmax=1, logit_softcap=0.0)
     cfg.update(over)
     return cfg
 
@@ -81,7 +82,7 @@ def tiny_shape(batch: int = 4, **over) -> dict:
     cfg = dict(hidden=512, ffn=2048, vocab=2048, num_layers=1, heads=8, kv_heads=4, sliding_head_dim=64,
                global_head_dim=64, sliding_window=64, global_every=1, act=ACT_SILU, dtype=F16, batch=batch,
                block_size=16, max_context=512, max_steps=512, prompt_len=128, gemm_impl=0, rms_eps=1e-6,
-               rope_theta=10000.0, seed=0, kv_pool_blocks=0, fused_block=1)
+               rope_theta=10000.0, seed=0, kv_pool_blocks=0, fused_block=1, fused_argmax=0, logit_softcap=0.0)
     cfg.update(over)
     return cfg
 

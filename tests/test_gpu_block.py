@@ -82,7 +82,7 @@ class Block:
     def __init__(self, c, act):
         from rvllm_b200 import _lib
         self.c, self.act, self.L = c, act, _lib.lib()
-        self.ws_bytes = int(self.L.rvllm_fp8_layer_block_workspace(c["F"]))
+        self.ws_bytes = int(self.L.rvllm_fp8_layer_block_workspace(c["H"], c["F"]))
         self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device="cuda")   # the barrier words start at zero
 
     def run(self, stages, residual, x8, xs, h8, hs, attn_fp8=None, attn_scale=None):
@@ -168,10 +168,10 @@ def test_layer_block_with_fp8_attention_rows(M, H, F, KO):
 def test_layer_block_rejects_shapes_it_does_not_take():
     from rvllm_b200 import _lib
     L = _lib.lib()
-    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    t = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
     p, s = t.data_ptr(), _lib.current_stream()
 
-    def call(M=4, H=512, F=1024, KO=512, ws=None, wsb=1 << 16, stages=ALL):
+    def call(M=4, H=512, F=1024, KO=512, ws=None, wsb=1 << 20, stages=ALL):
         return L.rvllm_fp8_layer_block(M, H, F, KO, 0, 1, 1e-6, p, p, 1, None, None, p, p, p, p, p, p, p, p, p, p, p, p, p,
                                        p if ws is None else ws, wsb, stages, s)
     assert call(M=33) == _lib.E_UNSUPPORTED

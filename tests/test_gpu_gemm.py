@@ -325,3 +325,48 @@ def test_residual_gemm_from_16bit_activations_equals_quantiser_then_gemm(orc, dt
     torch.cuda.synchronize()
     assert rc == 0 and gemm.tc_status() == 0
     assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("M", [1, 32, 130])
+@pytest.mark.parametrize("softcap", [0.0, 30.0])
+def test_lm_head_argmax_epilogue_equals_logits_then_argmax(orc, M, softcap):
+    """The LM head that keeps only per-tile argmax winners against f32 logits -> [soft cap] -> argmax (C ABI): same
+    tokens, including exact ties (two identical weight rows: the lower token id wins), a row whose logits are all
+    NaN (-1) and a ragged last weight tile."""
+    from rvllm_b200 import _lib, gemm
+    from rvllm_b200.launchers import ArgmaxLaunch
+    L = _lib.lib()
+    V, K = 32768 + 40, 512
+    g = np.random.default_rng(M)
+    w, w_s = datagen.quant_rows(orc, g.standard_normal((V, K), dtype=np.float32) * 0.02)
+    a, a_s = datagen.quant_rows(orc, g.standard_normal((M, K), dtype=np.float32))
+    want_first = orc.argmax_f32(orc.fp8_gemm(a, w, a_s, w_s, out_kind=2))
+    # plant a tie for row 0: a later row of W equal to the winning row (bytes and scale)
+    lo = int(want_first[0])
+    hi = (lo + 5000) % V
+    lo, hi = min(lo, hi), max(lo, hi)
+    w[hi], w_s[hi] = w[int(want_first[0])], w_s[int(want_first[0])]
+    w[lo], w_s[lo] = w[int(want_first[0])], w_s[int(want_first[0])]
+    if M > 2:
+        a_s[2] = np.nan                                    # every logit of row 2 is NaN
+    d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    A, AS, W, WS = d(a), d(a_s), d(w), d(w_s)
+    logits = torch.empty((M, V), dtype=torch.float32, device="cuda")
+    gemm.fp8_gemm_channelscale(logits, A, W, AS, WS, impl=TC)
+    if softcap > 0:
+        _lib.check(L.rvllm_logit_softcap_launch(logits.data_ptr(), M, V, softcap, 2, _lib.current_stream()), "softcap f32")
+    want = torch.empty(M, dtype=torch.int32, device="cuda")
+    ArgmaxLaunch(M, V).launch(logits, want)
+    n = int(L.rvllm_fp8_gemm_lm_head_argmax_workspace(M, V))
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    got = torch.full((M,), -5, dtype=torch.int32, device="cuda")
+    _lib.check(L.rvllm_fp8_gemm_lm_head_argmax(got.data_ptr(), A.data_ptr(), W.data_ptr(), AS.data_ptr(), WS.data_ptr(), M, V, K,
+                                               softcap, ws.data_ptr(), n, _lib.current_stream()), "lm_head_argmax")
+    torch.cuda.synchronize()
+    assert gemm.tc_status() == 0
+    assert got.tolist() == want.tolist()
+    assert got[0].item() == lo
+    if M > 2:
+        assert got[2].item() == -1
+    assert L.rvllm_fp8_gemm_lm_head_argmax(got.data_ptr(), A.data_ptr(), W.data_ptr(), AS.data_ptr(), WS.data_ptr(), M, V, K,
+                                           softcap, ws.data_ptr(), 16, _lib.current_stream()) == _lib.E_WORKSPACE

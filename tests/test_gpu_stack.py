@@ -59,7 +59,7 @@ def bench_composition_shape(batch, **over):
     graph takes is taken here too (see expected_launches)."""
     from rvllm_b200.stack import tiny_shape
     cfg = dict(hidden=1024, ffn=2048, vocab=2048, num_layers=3, heads=32, kv_heads=16, sliding_head_dim=128,
-               global_head_dim=256, sliding_window=32, global_every=3, dtype=1, batch=batch, prompt_len=8)
+               global_head_dim=256, sliding_window=32, global_every=3, dtype=1, batch=batch, prompt_len=8, fused_argmax=1)
     cfg.update(over)
     return tiny_shape(**cfg)
 
@@ -112,7 +112,7 @@ def test_block_kernel_on_and_off_decode_the_same_tokens(orc):
     from rvllm_b200.stack import DecodeStack, gemma31b_shape, random_weights
     for batch in (32, 4):
         base = gemma31b_shape(batch, num_layers=2, global_every=2, vocab=4096, prompt_len=8, max_context=72, max_steps=72,
-                              sliding_window=32)
+                              sliding_window=32, fused_argmax=0)
         w = random_weights(base, seed=11)
         prompt = np.random.default_rng(5).integers(0, base["vocab"], (batch, base["prompt_len"]), dtype=np.int32)
         runs = []
@@ -184,6 +184,29 @@ def test_step_host_matches_device_feedback(orc):
     stack.close()
 
 
+@pytest.mark.parametrize("softcap", [0.0, 30.0])
+def test_fused_greedy_tail_decodes_the_same_tokens(orc, softcap):
+    """LM head with the argmax in its epilogue (no logits in memory) against LM head -> [soft cap] -> argmax: the same
+    tokens over 48 steps, and the soft-capped run against the oracle chain."""
+    from oracle.chain import greedy_parity
+    from rvllm_b200.stack import DecodeStack, random_weights
+    base = bench_composition_shape(32, max_context=64, max_steps=64, vocab=40960, logit_softcap=softcap)
+    w = random_weights(base, seed=13)
+    prompt = np.random.default_rng(6).integers(0, base["vocab"], (32, base["prompt_len"]), dtype=np.int32)
+    toks = []
+    for fused in (1, 0):
+        st = DecodeStack(dict(base, fused_argmax=fused), w)
+        st.reset(prompt)
+        st.run(48)
+        st.sync()
+        toks.append(st.tokens().copy())
+        if fused and softcap > 0:
+            check_parity(greedy_parity(orc, st, dict(base, fused_argmax=1), w, prompt, 24, LOGIT_TOL))
+        st.close()
+    # 320 weight tiles: the LM head is unsplit in both forms, so the compared values are the same f32 numbers
+    assert np.array_equal(toks[0], toks[1])
+
+
 def test_run_past_max_context_is_refused_before_any_launch(orc):
     from rvllm_b200 import InvalidArgument
     from rvllm_b200.stack import tiny_shape
@@ -218,7 +241,7 @@ def test_ragged_contexts_and_shared_block_pool(orc):
     from rvllm_b200.stack import DecodeStack, random_weights
     steps = 16
     contexts = np.array([5, 130, 33, 0, 77, 200], np.int32)
-    base = bench_composition_shape(6, max_context=256, max_steps=steps + 4, prompt_len=0)
+    base = bench_composition_shape(6, max_context=256, max_steps=steps + 4, prompt_len=0, fused_argmax=0)
     w = random_weights(base, seed=9)
     need = int(sum((int(c) + steps + 4 + 15) // 16 for c in contexts))
     runs = []
