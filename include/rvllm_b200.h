@@ -354,6 +354,13 @@ int rvllm_residual_scale_launch(void* residual, const void* scalar, int num_toke
  * RVLLM_F16 / RVLLM_BF16 as the reference kernel (16-bit logits), or RVLLM_OUT_F32 for f32 logits. */
 int rvllm_logit_softcap_launch(void* logits, int num_tokens, int vocab, float cap, int dtype, void* stream);
 
+/* FP8 weights with 128 x 128 block scales (scale f32 [ceil(N/128), ceil(K/128)]) times 16-bit activations, 16-bit out:
+ * the alternative weight-scale layout of the Gemma-4 executor.  Fp8GemvF16InLaunch (gemma4_launcher.rs:839-886; kernel
+ * fp8_gemv_blockwise_wpr_native_f16in_kernel, kernels/fp8_gemv.cu:811-891): grid (ceil(N/8), M), block 256, one warp per
+ * output row; M is a handful of rows (decode).  K a multiple of 8. */
+int rvllm_fp8_gemv_blockscale_launch(void* out, const void* w_fp8, const float* block_scale, const void* x16, int M, int N,
+                                     int K, int dtype, void* stream);
+
 /* FP8 encode / decode of a flat array with the kernels' own convert instructions
  * (used by the bit-exactness tests; not on the decode path). */
 int rvllm_e4m3_encode_f32(void* out_u8, const float* in, size_t n, void* stream);

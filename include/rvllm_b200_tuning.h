@@ -43,6 +43,11 @@ void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant)
  * 0 restores the automatic choice.  Tuning aid, process-wide. */
 void rvllm_paged_decode_ring(int units);
 
+/* What the layer-block kernel's residency check sees on the current device: CTAs of the kernel one SM holds and the
+ * number of SMs (their product must cover the grid of 8 * hidden / 128 CTAs), from the device's per-SM limits.  The
+ * last argument is ignored.  Diagnostic. */
+int rvllm_fp8_layer_block_capacity(int* ctas_per_sm, int* sms, int carveout_percent);
+
 /* Host-only self-test of the per-device "set up once" bookkeeping that guards cudaFuncSetAttribute
  * (the attribute belongs to a device, not to the process).  Touches no CUDA API; 0 = pass. */
 int rvllm_b200_selftest_device_once(void);

@@ -322,6 +322,15 @@ def rope_cache_fp8kv(qkv16, heads, kv_heads, head_dim, cos16, sin16, positions, 
          "rope_cache_fp8kv")
     return q_fp8
 
+
+def fp8_gemv_blockscale(w, block_scale, x16, dtype=F16):
+    """W [N, K] u8, block_scale f32 [ceil(N/128), ceil(K/128)], x16 [M, K] bits -> out [M, N] bits."""
+    N, K = w.shape
+    M = x16.shape[0]
+    out = np.empty((M, N), np.uint16)
+    _chk(lib().orc_fp8_gemv_blockscale(_p(out), _p(w), _p(block_scale), _p(x16), M, N, K, dtype), "fp8_gemv_blockscale")
+    return out
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

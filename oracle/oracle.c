@@ -996,6 +996,41 @@ int orc_rope_cache_fp8kv(const uint16_t *q_in, const uint16_t *k_in, const uint1
     return 0;
 }
 
+/* fp8_gemv_blockwise_wpr_native_f16in_kernel, kernels/fp8_gemv.cu:811-891: out[m, n] =
+ * f16(sum_k dec(W[n,k]) * scale[n/128][k/128] * x[m,k]) with the kernel's order: lane l of the
+ * row's warp takes k = 8l + 256i, two accumulation chains (first four / last four of the
+ * eight, each term (w*s)*x folded into the chain with one fma), chains added, shuffle-down
+ * tree (lane 0's pairing is the xor butterfly's).  K a multiple of 8. */
+int orc_fp8_gemv_blockscale(uint16_t *out, const uint8_t *w, const float *scale, const uint16_t *x,
+                            int M, int N, int K, int dtype) {
+    if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || !out || !w || !scale || !x) return -1;
+    lut_init();
+    int ncb = (K + 127) / 128;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++) {
+        const float *srow = scale + (size_t)(n >> 7) * ncb;
+        const uint8_t *wr = w + (size_t)n * K;
+        for (int m = 0; m < M; m++) {
+            const uint16_t *xr = x + (size_t)m * K;
+            float lane_acc[32];
+            for (int l = 0; l < 32; l++) {
+                float a0 = 0.0f, a1 = 0.0f;
+                for (int k = l * 8; k + 7 < K; k += 256) {
+                    float s0 = srow[k >> 7], s4 = srow[(k + 4) >> 7];
+                    for (int e = 0; e < 4; e++) a0 = fmaf(orc_e4m3_decode(wr[k + e]) * s0, orc_h2f(xr[k + e], dtype), a0);
+                    for (int e = 4; e < 8; e++) a1 = fmaf(orc_e4m3_decode(wr[k + e]) * s4, orc_h2f(xr[k + e], dtype), a1);
+                }
+                lane_acc[l] = a0 + a1;
+            }
+            for (int off = 16; off > 0; off >>= 1)
+                for (int l = 0; l + off < 32; l++)
+                    if (l < off) lane_acc[l] = lane_acc[l] + lane_acc[l + off];
+            out[(size_t)m * N + n] = orc_f2h(lane_acc[0], dtype);
+        }
+    }
+    return 0;
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

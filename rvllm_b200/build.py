@@ -44,6 +44,8 @@ PTX_MODULES = {
     "residual_scale_f16": "rowq_gemma.cu",
     "logit_softcap": "rowq_gemma.cu",
     "fused_rope_cache_fp8kv": "rowq_gemma.cu",
+    # 128 x 128 block-scaled FP8 weights x 16-bit activations (the f16-input warp-per-row entry point only)
+    "fp8_gemv": "rowq_blockscale.cu",
 }
 REVISION = "b200f8e4d0c1"
 

@@ -17,6 +17,7 @@
 #include "greedy_argmax_cluster.cuh"
 #include "rope_kv_write.cu"
 #include "rowq_gelu.cu"
+#include "rowq_blockscale.cu"
 #include "rowq_gemma.cu"
 #include "rowq_rmsnorm.cu"
 #include "rowq_silu.cu"
@@ -395,6 +396,25 @@ int rvllm_rope_cache_fp8kv_launch(const void* q_in, const void* k_in, const void
                   slot_mapping, q_scale_ptr, kv_scale_ptr, num_tokens, num_heads, num_kv_heads, head_dim, max_positions,
                   num_cache_slots);
     return rv_launched("rope_cache_fp8kv");
+}
+
+int rvllm_fp8_gemv_blockscale_launch(void* out, const void* w_fp8, const float* block_scale, const void* x16, int M, int N,
+                                     int K, int dtype, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return rv_fail(RVLLM_E_INVALID, "M, N, K must be > 0");
+    if (!out || !w_fp8 || !block_scale || !x16) return rv_fail(RVLLM_E_INVALID, "null device pointer");
+    if (K % 8 != 0 || !rv_aligned(w_fp8, 8) || !rv_aligned(x16, 8))
+        return rv_fail(RVLLM_E_INVALID, "K must be a multiple of 8 and W / x 8-byte aligned");
+    if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    dim3 grid((N + 7) / 8, M), block(256);
+    const int ncb = (K + 127) / 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RVLLM_F16)
+        rv_launch(fp8_gemv_blockwise_wpr_native_f16in_kernel, grid, block, 0, s, dim3(1, 1, 1), (__half*)out,
+                  (const unsigned char*)w_fp8, block_scale, (const __half*)x16, M, N, K, ncb);
+    else
+        rv_launch(fp8_gemv_blockwise_wpr_native_bf16in_kernel, grid, block, 0, s, dim3(1, 1, 1), (__nv_bfloat16*)out,
+                  (const unsigned char*)w_fp8, block_scale, (const __nv_bfloat16*)x16, M, N, K, ncb);
+    return rv_launched("fp8_gemv_blockscale");
 }
 
 int rvllm_embedding_gather_launch(void* out, const void* table, const int32_t* token_ids, int num_tokens,

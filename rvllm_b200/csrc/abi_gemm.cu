@@ -343,6 +343,11 @@ int rvllm_fp8_gemm_lm_head_argmax(int32_t* out_tokens, const void* a_fp8, const 
     return rc;
 }
 
+int rvllm_fp8_layer_block_capacity(int* ctas_per_sm, int* sms, int carveout_percent) {
+    if (!ctas_per_sm || !sms) return rv_fail(RVLLM_E_INVALID, "null argument");
+    return rvblk::block_capacity(ctas_per_sm, sms, carveout_percent) == 0 ? RVLLM_OK : rv_fail(RVLLM_E_LAUNCH, "occupancy query failed");
+}
+
 size_t rvllm_fp8_layer_block_workspace(int hidden, int ffn) {
     if (ffn <= 0 || ffn % 64 != 0 || hidden <= 0 || hidden % 128 != 0) return 0;
     return rvblk::blk_workspace_bytes(ffn, hidden);
@@ -374,6 +379,9 @@ int rvllm_fp8_layer_block(int M, int hidden, int ffn, int o_k, int act, int dtyp
         !rv_aligned(h_fp8, 16) || (attn_out16 && !rv_aligned(attn_out16, 16)) || (attn_fp8 && !rv_aligned(attn_fp8, 16)) ||
         (residual && !rv_aligned(residual, 16)))
         return rv_fail(RVLLM_E_INVALID, "operands must be 16-byte aligned");
+    if ((o_scale && !rv_aligned(o_scale, 16)) || (down_scale && !rv_aligned(down_scale, 16)) ||
+        (mlp_norm_gamma && !rv_aligned(mlp_norm_gamma, 16)) || (next_norm_gamma && !rv_aligned(next_norm_gamma, 16)))
+        return rv_fail(RVLLM_E_INVALID, "weight scales and norm gains must be 16-byte aligned");
     if (!workspace || !rv_aligned(workspace, 256) || workspace_bytes < rvblk::blk_workspace_bytes(ffn, hidden))
         return rv_fail(RVLLM_E_WORKSPACE, "layer-block workspace missing, misaligned or too small");
     rvblk::BlkArgs g = {};

@@ -902,12 +902,15 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     const int min_stages = push ? 2 : C::MIN_STAGES;
     if (stages < min_stages) stages = min_stages;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    while (stages > min_stages && C::smem_bytes(stages, push) > 227 * 1024) stages--;
+    // dynamic shared memory this instantiation may ask for: the 227 KB per-CTA limit less its static arrays
+    // (per-row scales of the 16-bit activation form, per-warp winners of the argmax epilogue)
+    constexpr int SMEM_LIMIT = 227 * 1024 - (EPI == EPI_ARGMAX ? 32 * BN : 8 * BN) - 256;
+    while (stages > min_stages && C::smem_bytes(stages, push) > SMEM_LIMIT) stages--;
     static RvDeviceOnce smem_once;  // per kernel instantiation and device: allow the largest ring once
     {
         int most = MAX_STAGES;
         const bool may_push = BN <= 32;  // the largest footprint this instantiation can be launched with
-        while (most > C::MIN_STAGES && C::smem_bytes(most, may_push) > 227 * 1024) most--;
+        while (most > C::MIN_STAGES && C::smem_bytes(most, may_push) > SMEM_LIMIT) most--;
         if (rv_allow_smem(smem_once, kern, C::smem_bytes(most, may_push)))
             return rvhost::fail_msg(-2, "cannot raise dynamic shared memory for the tcgen05 GEMM");
     }

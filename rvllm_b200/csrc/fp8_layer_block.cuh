@@ -676,8 +676,7 @@ template <typename OutT> int launch_block_t(const BlkArgs& g, cudaStream_t s) {
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = s;
-    // The grid-wide barriers need every CTA resident at once: ask the runtime how many CTAs of this kernel an SM
-    // holds (once per device) and refuse grids that do not fit.
+    // The grid-wide barriers need every CTA resident at once: refuse grids larger than the device holds.
     {
         static std::mutex mu;
         static std::unordered_map<int, int> capacity;  // device -> CTAs of this kernel resident at once
@@ -687,11 +686,7 @@ template <typename OutT> int launch_block_t(const BlkArgs& g, cudaStream_t s) {
         int cap = 0;
         if (it == capacity.end()) {
             int per_sm = 0, sms = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, SMEM_BYTES) != cudaSuccess ||
-                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev < 0 ? 0 : dev) != cudaSuccess) {
-                cudaGetLastError();
-                per_sm = sms = 0;
-            }
+            if (block_capacity_of(kern, &per_sm, &sms) != 0) per_sm = sms = 0;
             cap = per_sm * sms;
             capacity.emplace(dev, cap);
         } else {
@@ -746,6 +741,37 @@ template <typename OutT> int launch_block_t(const BlkArgs& g, cudaStream_t s) {
         return rvhost::fail_msg(-2, "layer-block kernel launch failed");
     }
     return 0;
+}
+
+// CTAs of the kernel one SM holds, from the per-SM limits: shared memory (dynamic + the per-CTA reservation),
+// registers (allocated per warp in units of 256), threads, and tensor memory (512 columns, 32 per CTA).  The
+// runtime's occupancy query is not used: it answers 1 for every kernel that allocates tensor memory, whatever its
+// footprint, while the hardware co-schedules such CTAs as long as their columns fit (a profiler capture of the
+// stand-alone GEMM, 63 KB and 84 registers, shows three per SM).
+template <typename K> inline int block_capacity_of(K kern, int* per_sm, int* sms) {
+    const int dev = rv_current_device();
+    cudaFuncAttributes fa;
+    int smem_sm = 0, smem_res = 0, regs_sm = 0, thr_sm = 0;
+    if (dev < 0 || cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
+        cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&smem_res, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&thr_sm, cudaDevAttrMaxThreadsPerMultiProcessor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    const int regs_warp = ((fa.numRegs * 32 + 255) / 256) * 256;
+    int n = smem_sm / (SMEM_BYTES + (int)fa.sharedSizeBytes + smem_res);
+    const int by_regs = regs_sm / (regs_warp * (THREADS / 32)), by_thr = thr_sm / THREADS, by_tmem = 512 / 32;
+    n = n < by_regs ? n : by_regs;
+    n = n < by_thr ? n : by_thr;
+    n = n < by_tmem ? n : by_tmem;
+    *per_sm = n;
+    return 0;
+}
+inline int block_capacity(int* per_sm, int* sms, int) {
+    return block_capacity_of(fp8_layer_block_kernel<__nv_bfloat16>, per_sm, sms);
 }
 
 inline int launch_block(const BlkArgs& g, cudaStream_t s) {

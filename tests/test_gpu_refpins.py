@@ -405,3 +405,34 @@ def test_residual_scale_and_logit_softcap_bit_exact_vs_reference_kernels(orc):
     assert np.abs(gb - want.astype(np.int32)).max() <= 1                                 # device tanhf vs libm tanhf
     assert L.rvllm_logit_softcap_launch(lg.data_ptr(), 2, vocab, 0.0, 0, s) == _lib.E_INVALID   # cap must be > 0
     assert L.rvllm_logit_softcap_launch(lg.data_ptr(), 0, vocab, 30.0, 0, s) == _lib.E_INVALID  # zero dim
+
+
+@needs_ref
+@pytest.mark.parametrize("M,N,K", [(1, 5376, 4096), (4, 1000, 5376), (2, 8192, 21504)])
+def test_blockscale_gemv_bit_exact_vs_reference_kernel(orc, M, N, K):
+    """FP8 weights with 128 x 128 block scales x f16 activations: the reference's warp-per-row kernel
+    (kernels/fp8_gemv.cu:811-891) against this repository's entry point of the same name and its C launcher."""
+    from rvllm_b200 import _lib
+    g = np.random.default_rng(N + K)
+    w = g.integers(0, 256, (N, K), dtype=np.uint8)
+    w[(w & 0x7F) == 0x7F] ^= 1                                     # no NaN codes
+    ncb = (K + 127) // 128
+    sc = g.uniform(0.002, 0.02, ((N + 127) // 128, ncb)).astype(np.float32)
+    x_b = orc.to_bits16(g.standard_normal((M, K)).astype(np.float32), 0)
+    W, SC, X = d(w), d(sc), dev16(x_b)
+    outs = {}
+    for tag, mod in (("ref", H.reference("fp8_gemv")), ("ours", H.ours("fp8_gemv"))):
+        o = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+        # geometry of Fp8GemvF16InLaunch::launch (gemma4_launcher.rs:882-883)
+        mod.launch("fp8_gemv_blockwise_wpr_native_f16in_kernel", ((N + 7) // 8, M), (256,), 0,
+                   [H.P(o), H.P(W), H.P(SC), H.P(X), H.I(M), H.I(N), H.I(K), H.I(ncb)])
+        outs[tag] = o
+    o = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    _lib.check(_lib.lib().rvllm_fp8_gemv_blockscale_launch(o.data_ptr(), W.data_ptr(), SC.data_ptr(), X.data_ptr(), M, N, K, 0,
+                                                           _lib.current_stream()), "fp8_gemv_blockscale")
+    torch.cuda.synchronize()
+    assert torch.equal(outs["ours"].view(torch.int16), outs["ref"].view(torch.int16))
+    assert torch.equal(o.view(torch.int16), outs["ref"].view(torch.int16))
+    want = orc.fp8_gemv_blockscale(w, sc, x_b, 0)
+    gb = bits(outs["ref"]).astype(np.int32)
+    assert np.abs(gb - want.astype(np.int32)).max() <= 1 and (gb != want).mean() <= 0.01
