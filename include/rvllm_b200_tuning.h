@@ -48,6 +48,12 @@ void rvllm_paged_decode_ring(int units);
  * last argument is ignored.  Diagnostic. */
 int rvllm_fp8_layer_block_capacity(int* ctas_per_sm, int* sms, int carveout_percent);
 
+/* Stage timing of the layer-block kernel: while a device buffer of (8 * hidden / 128) x 16 u64 is set, every launch
+ * writes %globaltimer stamps of its stage boundaries into it, one row per CTA (0 start, 1 predecessor done, 2/7/12
+ * accumulator of the O / gate|up / down stage complete, 3-4, 5-6, 8-9, 10-11, 13-14 before / after the five grid
+ * barriers, 15 end).  NULL switches it off (the default). */
+void rvllm_fp8_layer_block_trace(void* device_u64_buffer);
+
 /* Host-only self-test of the per-device "set up once" bookkeeping that guards cudaFuncSetAttribute
  * (the attribute belongs to a device, not to the process).  Touches no CUDA API; 0 = pass. */
 int rvllm_b200_selftest_device_once(void);

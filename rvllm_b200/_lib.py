@@ -68,6 +68,7 @@ SIGNATURES = {
     "rvllm_fp8_gemm_qkv_rope_fp8kv": (_i32, [_vp] * 4 + [_i32] * 6 + [_vp] * 10 + [_i32] * 2 + [_vp]),
     "rvllm_fp8_gemm_lm_head_argmax_workspace": (_sz, [_i32, _i32]),
     "rvllm_fp8_gemm_lm_head_argmax": (_i32, [_vp] * 5 + [_i32] * 3 + [_f32, _vp, _sz, _vp]),
+    "rvllm_fp8_layer_block_trace": (None, [_vp]),
     "rvllm_fp8_layer_block_capacity": (_i32, [C.POINTER(_i32), C.POINTER(_i32), _i32]),
     "rvllm_fp8_layer_block_workspace": (_sz, [_i32, _i32]),
     "rvllm_fp8_layer_block": (_i32, [_i32] * 6 + [_f32, _vp, _vp, _i32] + [_vp] * 16 + [_sz, _i32, _vp]),

@@ -343,6 +343,10 @@ int rvllm_fp8_gemm_lm_head_argmax(int32_t* out_tokens, const void* a_fp8, const 
     return rc;
 }
 
+void rvllm_fp8_layer_block_trace(void* device_u64_buffer) {
+    rvblk::trace_buffer().store((unsigned long long*)device_u64_buffer);
+}
+
 int rvllm_fp8_layer_block_capacity(int* ctas_per_sm, int* sms, int carveout_percent) {
     if (!ctas_per_sm || !sms) return rv_fail(RVLLM_E_INVALID, "null argument");
     return rvblk::block_capacity(ctas_per_sm, sms, carveout_percent) == 0 ? RVLLM_OK : rv_fail(RVLLM_E_LAUNCH, "occupancy query failed");

@@ -72,6 +72,7 @@ struct BlkParams {
     unsigned int* bar;        // [0] arrivals, [32] departures (separate 128-byte lines); zero between launches
     float* amax_ws;           // [F / 64][BN] partial row maxima of act(gate)*up
     float* part;              // [CL][BN][H] f32 split-K partial tiles of the O / down stage
+    unsigned long long* trace;  // null, or [G][16] %globaltimer stamps of the stage boundaries (tuning runs)
 };
 
 // ---- small helpers -------------------------------------------------------------------------------------
@@ -90,6 +91,11 @@ __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned in
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    return v;
+}
 __device__ __forceinline__ float ldcg_f32(const float* p) { return __ldcg(p); }
 // 16-bit value read through L2 (it may have been written by another SM earlier in this launch)
 template <typename T> __device__ __forceinline__ float ld16_cg(const T* p) {
@@ -371,12 +377,17 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
         uint32_t acc_uses = 0, barriers = 0;
         int it = 0;
         bool alive = true;
+        auto stamp = [&](int k) {
+            if (p.trace && t == 0) p.trace[(size_t)j * 16 + k] = global_timer();
+        };
+        stamp(0);
 
         // Epilogue of a split-K stage (O, down): this CTA's f32 partial tile [BN rows][128 channels] goes to the
         // workspace, slice-major, so that a warp stores 128 contiguous bytes per batch row.
-        auto store_partial = [&](int n_kb) {
+        auto store_partial = [&](int n_kb, int stamp_id) {
             bool ready = true;
             if (n_kb > 0) ready = mbar_wait(acc_ready, acc_uses & 1u, 3);
+            stamp(stamp_id);
             tc_fence_after();
             float* dst = p.part + ((size_t)split * BN) * p.H + (size_t)tile * TILE_W + r;
 #pragma unroll 1
@@ -433,10 +444,11 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
         };
 
         rv::pdl_wait();  // everything below reads what earlier kernels wrote
+        stamp(1);
 
         // ---------------------------------------------------------------- O projection
         if (do_o && !o_a16) {
-            store_partial(nO);
+            store_partial(nO, 2);
         } else if (do_o) {
             if (t < BN) {  // per-row activation scale from the partial maxima the attention kernel left
                 float amax = 0.0f;
@@ -494,10 +506,12 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(afull + s);
             }
-            store_partial(nO);
+            store_partial(nO, 2);
         }
+        stamp(3);
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 10);
+        stamp(4);
 
         // ---------------------------------------------------------------- rows: finish O, RMSNorm + quant (input of gate|up)
         if (j < p.M) {
@@ -514,8 +528,10 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
             }
             if (p.phases & PH_N1) norm_quant_row<OutT>(p, p.gamma1, j, t, scratch, s_small, /*row_staged=*/do_o);
         }
+        stamp(5);
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 11);
+        stamp(6);
         if (t == 0) mbar_arrive(gate);  // x8 / xs exist: the producer may fetch the gate|up activations
         it += nG;                       // (the ring iterations of the gate|up stage belong to the producer and the MMA warp)
 
@@ -528,6 +544,7 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
             if (t < BN) s_ascale[t] = t < p.M ? __ldcg(p.xs + t) : 0.0f;
             epi_sync();
             bool ready = mbar_wait(acc_ready, acc_uses & 1u, 3);
+            stamp(7);
             tc_fence_after();
             // TMEM lane r = row r of the operand: rows 0..63 gate channels 64 j + r, rows 64..127 up channels of the same columns
             const int wrow = r < 64 ? j * 64 + r : p.F + j * 64 + (r - 64);
@@ -571,8 +588,10 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                 p.amax_ws[(size_t)j * BN + lane] = fmaxf(fmaxf(s_part[lane], s_part[BN + lane]),
                                                          fmaxf(s_part[2 * BN + lane], s_part[3 * BN + lane]));
         }
+        stamp(8);
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 12);
+        stamp(9);
         if (p.phases & PH_GU) {
             // row maxima over all units: thread (w4, lane) takes units w4, w4 + 4, ... of row `lane`
             float am = 0.0f;
@@ -593,15 +612,19 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
                 *reinterpret_cast<uint4*>(p.h8 + (size_t)lane * p.F + (size_t)j * 64 + w4 * 16) = o;
             }
         }
+        stamp(10);
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 13);
+        stamp(11);
         if (t == 0) mbar_arrive(gate);  // h8 / hs exist
         it += nD;
 
         // ---------------------------------------------------------------- down projection
-        if (do_d) store_partial(nD);
+        if (do_d) store_partial(nD, 12);
+        stamp(13);
         barriers++;
         grid_barrier(bar_arrive, (unsigned int)G * barriers, t, 14);
+        stamp(14);
 
         // ---------------------------------------------------------------- rows: finish down, RMSNorm + quant for the next layer
         if (j < p.M) {
@@ -610,6 +633,7 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
         }
 
         // leave: the last CTA out puts the barrier words back to zero for the next launch
+        stamp(15);
         epi_sync();
         if (t == 0) {
             __threadfence();
@@ -630,6 +654,13 @@ fp8_layer_block_kernel(const __grid_constant__ CUtensorMap map_wo, const __grid_
 }
 
 // ---- host side -------------------------------------------------------------------------------------------
+// Tuning runs: a device buffer of G x 16 u64 that the next launches stamp with %globaltimer at their stage
+// boundaries (null = off, the default).
+inline std::atomic<unsigned long long*>& trace_buffer() {
+    static std::atomic<unsigned long long*> p{nullptr};
+    return p;
+}
+
 struct BlkArgs {
     int M, H, F, KO, act, dtype, phases;
     float eps;
@@ -736,6 +767,7 @@ template <typename OutT> int launch_block_t(const BlkArgs& g, cudaStream_t s) {
     p.bar = (unsigned int*)g.workspace;
     p.amax_ws = (float*)((char*)g.workspace + 256);
     p.part = (float*)((char*)g.workspace + 256 + blk_amax_bytes(g.F));
+    p.trace = trace_buffer().load();
     if (cudaLaunchKernelEx(&cfg, kern, mwo, mwgu, mwd, mao, mx8, mh8, p) != cudaSuccess) {
         cudaGetLastError();
         return rvhost::fail_msg(-2, "layer-block kernel launch failed");
