@@ -42,7 +42,7 @@ def measured_peaks():
         with open(p) as f:
             d = json.load(f)
         return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, device copy)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+    return 6650.0, "fallback (no MEASURED_PEAKS.json: an earlier device-copy measurement of the same part)"
 
 
 # ----------------------------------------------------------------------------- byte model
@@ -690,6 +690,71 @@ def ragged_replica_run(torch, cfg, weights, per_gpu_batch, steps, lo=1024, hi=16
     return res
 
 
+# ----------------------------------------------------------------------------- the one-launch layer block, stage by stage
+def layer_block_trace(torch, cfg, batch, reps=5):
+    """The layer-block kernel (O projection .. next RMSNorm in one launch, CTAs resident behind grid-wide barriers)
+    alone at the benchmark's layer dimensions, cycling over three weight sets (1.1 GB, larger than L2): device time
+    per launch, and the kernel's own %globaltimer stamps of its stage boundaries, reduced over the CTAs."""
+    import numpy as np
+    from rvllm_b200 import _lib
+    from rvllm_b200.stack import _quant_weight
+    L = _lib.lib()
+    M, H, F, KO = batch, cfg["hidden"], cfg["ffn"], cfg["heads"] * cfg["sliding_head_dim"]
+    tdt = torch.float16 if cfg["dtype"] == 0 else torch.bfloat16
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    sets = []
+    for _ in range(3):
+        o_w, o_s = _quant_weight(H, KO, gen, 0.02)
+        gu_w, gu_s = _quant_weight(2 * F, H, gen, 0.02)
+        d_w, d_s = _quant_weight(H, F, gen, 0.02)
+        sets.append((o_w, o_s, gu_w, gu_s, d_w, d_s))
+    attn = (torch.randn((M, KO), generator=gen, device="cuda") * 0.5).to(tdt)
+    amax = attn.float().abs().reshape(M, 16, KO // 16).amax(dim=2).contiguous()
+    res = torch.randn((M, H), generator=gen, device="cuda").to(tdt)
+    g1 = torch.ones(H, dtype=tdt, device="cuda")
+    x8 = torch.empty((M, H), dtype=torch.uint8, device="cuda")
+    xs = torch.empty(M, dtype=torch.float32, device="cuda")
+    h8 = torch.empty((M, F), dtype=torch.uint8, device="cuda")
+    hs = torch.empty(M, dtype=torch.float32, device="cuda")
+    wsb = int(L.rvllm_fp8_layer_block_workspace(H, F))
+    ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+    st = _lib.current_stream()
+
+    def launch(i):
+        o_w, o_s, gu_w, gu_s, d_w, d_s = sets[i % 3]
+        _lib.check(L.rvllm_fp8_layer_block(M, H, F, KO, cfg["act"], cfg["dtype"], cfg["rms_eps"], attn.data_ptr(), amax.data_ptr(),
+                                           16, None, None, o_w.data_ptr(), o_s.data_ptr(), res.data_ptr(), g1.data_ptr(),
+                                           g1.data_ptr(), x8.data_ptr(), xs.data_ptr(), gu_w.data_ptr(), gu_s.data_ptr(),
+                                           h8.data_ptr(), hs.data_ptr(), d_w.data_ptr(), d_s.data_ptr(), ws.data_ptr(), wsb, 31,
+                                           st), "fp8_layer_block")
+    sec = time_launches(torch, launch, 30, warm=6)
+    G = H // 128 * 8
+    tr = torch.zeros((G, 16), dtype=torch.int64, device="cuda")
+    L.rvllm_fp8_layer_block_trace(tr.data_ptr())
+    names = ["start", "predecessor done", "O accumulator complete", "O partials stored", "after barrier 1",
+             "rows: O finished + RMSNorm", "after barrier 2", "gate|up accumulator complete", "act*up partial maxima stored",
+             "after barrier 3", "act*up quantised", "after barrier 4", "down accumulator complete", "down partials stored",
+             "after barrier 5", "rows: down finished + RMSNorm (end)"]
+    acc = np.zeros((reps, 16, 3))
+    try:
+        for r in range(reps):
+            launch(r)
+            torch.cuda.synchronize()
+            t = tr.cpu().numpy().astype(np.float64)
+            t = (t - t[:, 0].min()) / 1e3
+            acc[r, :, 0], acc[r, :, 1], acc[r, :, 2] = t.min(axis=0), t.mean(axis=0), t.max(axis=0)
+    finally:
+        L.rvllm_fp8_layer_block_trace(None)
+    m = acc.mean(axis=0)
+    weights = sum(t.numel() for t in (sets[0][0], sets[0][2], sets[0][4]))
+    peak, _ = measured_peaks()
+    return {"kernel": "fp8_layer_block_kernel", "batch": M, "hidden": H, "ffn": F, "o_k": KO, "us_per_launch": sec * 1e6,
+            "weight_bytes_per_launch": weights, "frac_of_hbm_peak": weights / sec / 1e9 / peak,
+            "stamps_us": [{"point": n, "first_cta": m[k, 0], "mean": m[k, 1], "last_cta": m[k, 2]} for k, n in enumerate(names)],
+            "note": "%globaltimer, 0.26 us resolution; first / mean / last over the 336 CTAs, mean of %d launches" % reps}
+
+
 def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None, profiler_range=False, seeded=False):
     import numpy as np
     from rvllm_b200.stack import DecodeStack
@@ -807,7 +872,7 @@ def run_gpu_arm(args, cfg):
         "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (bf16 activations)" if cfg["dtype"] == 1 else "fp8_e4m3 x fp8_e4m3 -> f32 (f16 activations)",
         "data": "synthetic", "config": workload_config(cfg, B),
         "gpu_launches": main["launches_per_step"] * args.steps, "clocks": main["clocks"],
-        "weights_gb": weights.nbytes() / 1e9, "setup_s": setup_s,
+        "weights_gb": weights.nbytes() / 1e9, "setup_s": setup_s, "fused_block": cfg["fused_block"],
         "collective": "none on the data path (independent replicas); NCCL only for the barrier around the timed "
                       "region and the max-over-ranks of the device times" if world > 1 else "none (one GPU)",
         "greedy_tokens_tail": main["greedy_tokens_tail"],
@@ -887,6 +952,10 @@ def main():
                     help="only the GEMM sweep: four projection shapes x M in {1, 8, 32, 128, 512, 2048}, and the FP8 peak")
     ap.add_argument("--ragged-attention", action="store_true",
                     help="only the decode attention at batch 64 with contexts uniform in [512, 32768]")
+    ap.add_argument("--fused-block", type=int, default=0, choices=[0, 1],
+                    help="1: run the step with the one-launch layer block (O projection .. next RMSNorm) instead of the chain")
+    ap.add_argument("--layer-block-trace", action="store_true",
+                    help="only the layer-block kernel alone at the layer dimensions, with its stage-boundary time stamps")
     ap.add_argument("--vs-ref-kernels", action="store_true",
                     help="only the ours / reference kernel table (needs oracle/_ref)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -903,7 +972,8 @@ def main():
     args = ap.parse_args()
     from rvllm_b200.stack import gemma31b_shape
     need = 512 + max(args.warmup, 3) + args.steps + args.e2e_steps + 8
-    cfg = gemma31b_shape(args.batch, num_layers=args.layers, max_context=(need + 255) // 256 * 256, max_steps=need)
+    cfg = gemma31b_shape(args.batch, num_layers=args.layers, max_context=(need + 255) // 256 * 256, max_steps=need,
+                         fused_block=args.fused_block)
     if args.roofline_only:
         import torch
         from rvllm_b200.stack import Weights, _quant_weight
@@ -916,7 +986,7 @@ def main():
         peak, src = measured_peaks()
         print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
         return
-    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels:
+    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels or args.layer_block_trace:
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
@@ -926,6 +996,8 @@ def main():
             print(json.dumps({"attention_ragged": ragged_attention(torch, cfg)}))
         if args.vs_ref_kernels:
             print(json.dumps({"ref_kernels": reference_kernel_table(torch, cfg)}))
+        if args.layer_block_trace:
+            print(json.dumps({"layer_block": layer_block_trace(torch, cfg, args.batch)}))
         return
     if args.attention_only:
         import torch

@@ -172,7 +172,7 @@ def test_missing_artifact_name_and_fail_closed_load(tmp_path):
     with pytest.raises(RvllmError) as e:
         vm.artifact("silu")
     assert "silu" in str(e.value)
-    with pytest.raises(RvllmError):          # "HELLO PTX" is not PTX, and this box may have no driver: either way an error
+    with pytest.raises(RvllmError):          # "HELLO PTX" is not PTX, and a host without a CUDA driver cannot load anything: either way an error
         vm.load_ptx("argmax")
     with pytest.raises(RvllmError):
         vm.dlopen("argmax")                  # a PTX artifact is not a shared object
