@@ -437,20 +437,22 @@ def fp8_tensor_peak(torch, seconds=2.0):
     return out_d
 
 
-def gemm_sweep(torch, cfg):
+def gemm_sweep(torch, cfg, shapes=None, ms=None, with_peak=True):
     """Four projection shapes x M in {1, 8, 32, 128, 512, 2048} through the C ABI: per-token activation scales,
     per-channel weight scales, 16-bit output (the O and down shapes with the fused residual).  Each launch of a
     row cycles to another copy of the weights so that the stream comes from HBM (copies x bytes > L2)."""
     from rvllm_b200 import gemm
     peak, peak_src = measured_peaks()
-    fp8 = fp8_tensor_peak(torch)
+    fp8 = fp8_tensor_peak(torch) if with_peak else None
     rows = []
     tdt = torch.float16 if cfg["dtype"] == 0 else torch.bfloat16
     for name, N, K, residual in PROJECTIONS:
+        if shapes and name not in shapes:
+            continue
         copies = max(2, int(300e6 // (N * K)) + 1)
         ws = [torch.randint(0, 120, (N, K), dtype=torch.uint8, device="cuda") for _ in range(copies)]
         w_s = torch.full((N,), 0.001, dtype=torch.float32, device="cuda")
-        for M in SWEEP_M:
+        for M in (ms or SWEEP_M):
             a = torch.randint(0, 120, (M, K), dtype=torch.uint8, device="cuda")
             a_s = torch.full((M,), 0.01, dtype=torch.float32, device="cuda")
             out = torch.zeros((M, N), dtype=tdt, device="cuda")
@@ -463,7 +465,7 @@ def gemm_sweep(torch, cfg):
             flops = 2.0 * M * N * K
             rows.append({"shape": name, "N": N, "K": K, "M": M, "us": sec * 1e6, "gbs": algo / sec / 1e9,
                          "frac_hbm": algo / sec / 1e9 / peak, "tflops": flops / sec / 1e12,
-                         "frac_fp8": flops / sec / 1e12 / fp8["burst_tflops"], "weight_copies": copies})
+                         "frac_fp8": flops / sec / 1e12 / fp8["burst_tflops"] if fp8 else None, "weight_copies": copies})
             del a, out
         del ws
     assert gemm.tc_status() == 0, "a bounded wait in the tcgen05 GEMM ran out"
@@ -950,6 +952,9 @@ def main():
     ap.add_argument("--ragged-steps", type=int, default=128)
     ap.add_argument("--gemm-sweep", action="store_true",
                     help="only the GEMM sweep: four projection shapes x M in {1, 8, 32, 128, 512, 2048}, and the FP8 peak")
+    ap.add_argument("--sweep-shapes", default="", help="--gemm-sweep: only these projections (comma list of qkv,o,gateup,down)")
+    ap.add_argument("--sweep-m", default="", help="--gemm-sweep: only these batch sizes (comma list)")
+    ap.add_argument("--no-fp8-peak", action="store_true", help="--gemm-sweep: skip the 8192^3 peak measurement (small case for ncu)")
     ap.add_argument("--ragged-attention", action="store_true",
                     help="only the decode attention at batch 64 with contexts uniform in [512, 32768]")
     ap.add_argument("--fused-block", type=int, default=0, choices=[0, 1],
@@ -991,7 +996,8 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
         if args.gemm_sweep:
-            print(json.dumps(gemm_sweep(torch, cfg)))
+            print(json.dumps(gemm_sweep(torch, cfg, [x for x in args.sweep_shapes.split(",") if x],
+                                        [int(x) for x in args.sweep_m.split(",") if x], not args.no_fp8_peak)))
         if args.ragged_attention:
             print(json.dumps({"attention_ragged": ragged_attention(torch, cfg)}))
         if args.vs_ref_kernels:
