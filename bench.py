@@ -754,7 +754,7 @@ def layer_block_trace(torch, cfg, batch, reps=5):
     return {"kernel": "fp8_layer_block_kernel", "batch": M, "hidden": H, "ffn": F, "o_k": KO, "us_per_launch": sec * 1e6,
             "weight_bytes_per_launch": weights, "frac_of_hbm_peak": weights / sec / 1e9 / peak,
             "stamps_us": [{"point": n, "first_cta": m[k, 0], "mean": m[k, 1], "last_cta": m[k, 2]} for k, n in enumerate(names)],
-            "note": "%globaltimer, 0.26 us resolution; first / mean / last over the 336 CTAs, mean of %d launches" % reps}
+            "note": "globaltimer stamps, 0.26 us resolution; first / mean / last over the %d CTAs, mean of %d launches" % (G, reps)}
 
 
 def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, barrier=None, profiler_range=False, seeded=False):

@@ -81,7 +81,9 @@ int rvllm_stack_config_validate(const rvllm_stack_config* cfg);
 /* Device bytes rvllm_stack_create will allocate (scratch + KV caches + bookkeeping). */
 uint64_t rvllm_stack_device_bytes(const rvllm_stack_config* cfg);
 
-/* layers[num_layers]; all pointers must stay valid for the life of the stack. */
+/* layers[num_layers]; all pointers must stay valid for the life of the stack.  The stack launches on a stream of
+ * its own and does not wait for any other: the weights must be completely written (synchronise the stream that
+ * produced them) before this call. */
 int rvllm_stack_create(rvllm_stack** out, const rvllm_stack_config* cfg, const rvllm_layer_weights* layers,
                        const rvllm_head_weights* head);
 void rvllm_stack_destroy(rvllm_stack* s);

@@ -145,6 +145,9 @@ def random_weights(cfg: dict, seed: int = 3, std: float = 0.02) -> Weights:
     w.head["embedding"] = emb
     w.head["final_norm_gamma"] = torch.ones(H, dtype=tdt, device="cuda")
     w.head["lm_head_w"], w.head["lm_head_scale"] = _quant_weight(cfg["vocab"], H, gen, std)
+    # the tensors are written by kernels on torch's stream; a decode stack runs on its own stream and does not
+    # wait for them, so they must be complete before they are handed over
+    torch.cuda.synchronize()
     return w
 
 
@@ -153,6 +156,10 @@ class DecodeStack:
         L = _bind()
         self.cfg = dict(cfg)
         self.weights = weights  # keeps the device memory alive
+        if weights.layers:
+            import torch
+
+            torch.cuda.synchronize()  # weights may still be in flight on another stream (see rvllm_stack_create)
         self._c = StackConfig(**cfg)
         check(L.rvllm_stack_config_validate(C.byref(self._c)), "stack config")
         layers = (LayerWeights * cfg["num_layers"])()

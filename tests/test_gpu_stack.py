@@ -123,6 +123,9 @@ def test_block_kernel_on_and_off_decode_the_same_tokens(orc):
             st.sync()
             runs.append((st.tokens().copy(), st.debug_read(1).copy(), st.debug_read(0).copy(), st.launches_per_step()))
             st.close()
+            from rvllm_b200 import gemm
+            status = gemm.tc_status()
+            assert status == 0, "a bounded wait ran out (site %d, CTA %d)" % (status >> 16, status & 0xffff)
         assert runs[0][3] < runs[1][3]
         assert np.array_equal(runs[0][0], runs[1][0])
         assert np.array_equal(runs[0][1].view(np.uint32), runs[1][1].view(np.uint32))
