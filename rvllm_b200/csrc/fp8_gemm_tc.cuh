@@ -225,6 +225,12 @@ __device__ __forceinline__ bool arg_better(float cv, int ci, float bv, int bi) {
     return cv > bv || (cv == bv && ci < bi);
 }
 
+// Meeting point of the four epilogue warps alone (named barrier 1; the block-wide barrier is 0).
+__device__ __forceinline__ void epi_warps_sync() {
+    __syncwarp();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
 constexpr int MAX_STAGES = 8;
 constexpr int HEADER_BYTES = 1024;  // barriers + TMEM address holder, in front of the ring
 
@@ -267,8 +273,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr bool RES = EPI == EPI_RESIDUAL || A16;        // residual epilogue
     __shared__ float s_ascale[A16 ? BN : 1], s_ainv[A16 ? BN : 1];
     constexpr bool ARG = EPI == EPI_ARGMAX;                 // per-tile argmax partials instead of stored logits
-    __shared__ float s_argv[ARG ? 4 * BN : 1];
-    __shared__ int s_argi[ARG ? 4 * BN : 1];
+    __shared__ float s_as[A16 ? 1 : BN];                    // unsplit epilogue: the batch rows' activation scales
     auto a_scale_of = [&](int m) -> float { return A16 ? s_ascale[m - m0] : p.a_scale[m]; };
     rv::pdl_launch();
     if (threadIdx.x == 0) {
@@ -577,15 +582,40 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int e = (int)threadIdx.x + PRE * THREADS; e < LC * TILE_W; e += THREADS) finish(e, false, 0.0f, 0.0f, 0.0f);
         }
     } else if (EPI != EPI_QKV_ROPE) {  // (the fused QKV epilogue exists in the push form only; the host launches no other)
-    float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32, only when S > 1
+    float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32: split-K partials, or the logits of the argmax form
     if (warp >= EPI_WARP0) {
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32 * quarter ...
         const int r = quarter * 32 + lane;
         const int n = n0 + r;
+        // Everything the epilogue needs besides the accumulator is fetched while the main loop still runs: a load
+        // inside the column loop below cannot be moved above the stores between the columns, so each column
+        // would pay a trip to L2 after the last MMA.
+        const float ws = (n < p.N) ? p.w_scale[n] : 0.0f;
+        if constexpr (!A16) {
+            if (S == 1) {
+                for (int c = r; c < BN; c += 128) s_as[c] = (m0 + c < p.M) ? p.a_scale[m0 + c] : 0.0f;
+                epi_warps_sync();
+            }
+        }
+        auto as_col = [&](int c) -> float { return A16 ? s_ascale[c] : s_as[c]; };  // (S == 1 only)
+        // residual values one 16-column group ahead (out and residual may be one buffer: every element is read
+        // before any store of its group, and by the thread that stores it)
+        float res_nx[RES ? 16 : 1];
+        auto fetch_res = [&](int c0) {
+            if constexpr (RES) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int m = m0 + c0 + j;
+                    res_nx[j] = (S == 1 && c0 + j < BN && m < p.M && n < p.N)
+                                    ? rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n])
+                                    : 0.0f;
+                }
+            }
+        };
+        fetch_res(0);
         bool ready = true;
         if (nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
         tc_fence_after();
-        const float ws = (n < p.N) ? p.w_scale[n] : 0.0f;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
             uint32_t v[16];
@@ -596,35 +626,20 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[j] = 0u;
             }
+            float res_cur[RES ? 16 : 1];
+            if constexpr (RES) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) res_cur[j] = res_nx[j];
+                if (S == 1) fetch_res(c0 + 16);
+            }
             if constexpr (ARG) {
-                // the logit this element would have been, (soft-capped,) then the best of the warp's 32 output channels
+                // the logit this element would have been (soft-capped), into the idle ring as [batch row][channel]
                 const float inv_cap = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f;
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
-                    const int m = m0 + c0 + j;
-                    float bv = -CUDART_INF_F;
-                    int bi = -1;
-                    if (m < p.M && n < p.N) {
-                        float val = a_scale_of(m) * (ws * __uint_as_float(v[j]));
-                        if (p.softcap > 0.0f) val = p.softcap * tanhf(val * inv_cap);
-                        if (val == val) {
-                            bv = val;
-                            bi = n;
-                        }
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                        if (arg_better(ov, oi, bv, bi)) {
-                            bv = ov;
-                            bi = oi;
-                        }
-                    }
-                    if (lane == 0) {
-                        s_argv[quarter * BN + c0 + j] = bv;
-                        s_argi[quarter * BN + c0 + j] = bi;
-                    }
+                    float val = as_col(c0 + j) * (ws * __uint_as_float(v[j]));
+                    if (p.softcap > 0.0f) val = p.softcap * tanhf(val * inv_cap);
+                    part[(size_t)(c0 + j) * TILE_W + r] = val;
                 }
             } else if (S > 1) {
 #pragma unroll
@@ -634,14 +649,12 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int j = 0; j < 16; j++) {
                     const int m = m0 + c0 + j;
                     if (m < p.M && n < p.N) {
-                        float val = a_scale_of(m) * (ws * __uint_as_float(v[j]));
+                        float val = as_col(c0 + j) * (ws * __uint_as_float(v[j]));
                         const size_t o = (size_t)m * p.N + n;
                         if (EPI == EPI_F32) {
                             reinterpret_cast<float*>(p.out)[o] = val;
                         } else {
-                            if (RES)
-                                val = fmaf(a_scale_of(m), ws * __uint_as_float(v[j]),
-                                           rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]));
+                            if (RES) val = fmaf(as_col(c0 + j), ws * __uint_as_float(v[j]), res_cur[RES ? j : 0]);
                             reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
                         }
                     }
@@ -649,6 +662,41 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             }
         }
         tc_fence_before();
+        if constexpr (ARG) {
+            // The tile's winner per batch row.  Four threads share a row, 32 channels each; lane l starts at
+            // channel l of its quarter, so the 32 lanes of a warp read 32 different banks.  The candidate rule
+            // does not depend on the order in which candidates meet.
+            epi_warps_sync();
+            const int t = (int)threadIdx.x - EPI_WARP0 * 32, q = t & 3;
+            for (int c = t >> 2; c < BN; c += 32) {
+                float bv = -CUDART_INF_F;
+                int bi = -1;
+                const float* rowp = part + (size_t)c * TILE_W + q * 32;
+#pragma unroll 8
+                for (int i = 0; i < 32; i++) {
+                    const int ch = (i + lane) & 31;
+                    const float val = rowp[ch];
+                    const int idx = n0 + q * 32 + ch;
+                    if (val == val && idx < p.N && arg_better(val, idx, bv, bi)) {
+                        bv = val;
+                        bi = idx;
+                    }
+                }
+#pragma unroll
+                for (int o = 1; o <= 2; o <<= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (arg_better(ov, oi, bv, bi)) {
+                        bv = ov;
+                        bi = oi;
+                    }
+                }
+                if (q == 0 && m0 + c < p.M) {
+                    p.arg_val[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = bv;
+                    p.arg_idx[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = bi;
+                }
+            }
+        }
     }
     if (S > 1) {
         // This CTA finishes elements e = split*THREADS + tid (+ k * S*THREADS).  Their scales and residual
@@ -715,37 +763,41 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int e = e_first + j * e_step;
             if (e < BN * TILE_W) finish(e, sums[j], pre_a[j], pre_w[j], true, pre_res[j]);
         }
-        for (int e = e_first + PRE * e_step; e < BN * TILE_W; e += e_step) {
-            float sum = 0.0f;
+        // The rest in groups of PRE as well: all loads of a group, then its stores.  (A load placed after a
+        // store cannot be moved above it — out and residual may be one buffer — so element-by-element code
+        // pays a full load latency per element.)
+        for (int e0 = e_first + PRE * e_step; e0 < BN * TILE_W; e0 += PRE * e_step) {
+            float g_sum[PRE], g_a[PRE], g_w[PRE], g_res[PRE];
 #pragma unroll
-            for (int s = 0; s < 8; s++)
-                if (s < S) sum += peer[s][e];
-            const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
-            const bool in = m < p.M && n < p.N;
-            finish(e, sum, in ? a_scale_of(m) : 0.0f, in ? p.w_scale[n] : 0.0f, false, 0.0f);
+            for (int j = 0; j < PRE; j++) {
+                const int e = e0 + j * e_step;
+                g_sum[j] = g_a[j] = g_w[j] = g_res[j] = 0.0f;
+                if (e < BN * TILE_W) {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < 8; s++)
+                        if (s < S) sum += peer[s][e];
+                    g_sum[j] = sum;
+                    const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
+                    if (m < p.M && n < p.N) {
+                        g_a[j] = a_scale_of(m);
+                        g_w[j] = p.w_scale[n];
+                        if (RES)
+                            g_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PRE; j++) {
+                const int e = e0 + j * e_step;
+                if (e < BN * TILE_W) finish(e, g_sum[j], g_a[j], g_w[j], true, g_res[j]);
+            }
         }
         if (!e_rest_done) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
     }
     __syncthreads();
-    if constexpr (ARG) {
-        // the tile's winner per batch row: the four warps' winners in output-channel order
-        for (int c = (int)threadIdx.x; c < BN; c += THREADS) {
-            float bv = -CUDART_INF_F;
-            int bi = -1;
-#pragma unroll
-            for (int q = 0; q < 4; q++)
-                if (arg_better(s_argv[q * BN + c], s_argi[q * BN + c], bv, bi)) {
-                    bv = s_argv[q * BN + c];
-                    bi = s_argi[q * BN + c];
-                }
-            if (m0 + c < p.M) {
-                p.arg_val[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = bv;
-                p.arg_idx[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = bi;
-            }
-        }
-    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -904,7 +956,7 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     // dynamic shared memory this instantiation may ask for: the 227 KB per-CTA limit less its static arrays
     // (per-row scales of the 16-bit activation form, per-warp winners of the argmax epilogue)
-    constexpr int SMEM_LIMIT = 227 * 1024 - (EPI == EPI_ARGMAX ? 32 * BN : 8 * BN) - 256;
+    constexpr int SMEM_LIMIT = 227 * 1024 - 8 * BN - 256;  // (static shared memory: at most two floats per batch row)
     while (stages > min_stages && C::smem_bytes(stages, push) > SMEM_LIMIT) stages--;
     static RvDeviceOnce smem_once;  // per kernel instantiation and device: allow the largest ring once
     {
