@@ -12,6 +12,7 @@ import concurrent.futures as cf
 import hashlib
 import json
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -57,6 +58,25 @@ def _run(cmd):
     return r.stdout
 
 
+# Kernels whose launch plan counts on three 192-thread CTAs per SM (18 warps): each of the SM's four
+# schedulers owns 16384 registers, so a warp may take at most 16384 / 5 / 32 = 102 -> 96 registers per thread
+# (allocated in eights).  One register more and only 16 warps fit: two CTAs per SM, the 336-CTA launches of
+# the decode step run in two waves (measured: down projection 25 -> 37 us).
+REG_BUDGET = 96
+REG_BUDGET_KERNELS = (r"fp8_gemm_tc_kernelILi16E", r"fp8_gemm_tc_kernelILi32E", r"fp8_layer_block_kernel")
+
+
+def check_register_budget(ptxas_log):
+    """Raises if a kernel named in REG_BUDGET_KERNELS was compiled with more than REG_BUDGET registers."""
+    over = []
+    for m in re.finditer(r"Compiling entry function '([^']+)'(?:.*\n)*?.*Used (\d+) registers", ptxas_log):
+        name, regs = m.group(1), int(m.group(2))
+        if any(re.search(k, name) for k in REG_BUDGET_KERNELS) and regs > REG_BUDGET:
+            over.append("%s: %d registers" % (name, regs))
+    if over:
+        raise RuntimeError("register budget of %d exceeded (third CTA per SM lost):\n  %s" % (REG_BUDGET, "\n  ".join(over)))
+
+
 def _newer(target, sources):
     if not os.path.exists(target):
         return True
@@ -79,10 +99,9 @@ def build_library(force=False, verbose=False):
 
     def compile_one(unit):
         obj = os.path.join(OBJ, os.path.splitext(unit)[0] + ".o")
-        cmd = [NVCC, *ARCH, *COMMON, "-c", os.path.join(CSRC, unit), "-o", obj]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
+        cmd = [NVCC, *ARCH, *COMMON, "-Xptxas=-v", "-c", os.path.join(CSRC, unit), "-o", obj]
         log = _run(cmd)
+        check_register_budget(log)
         return obj, log
 
     with cf.ThreadPoolExecutor(max_workers=len(units)) as ex:

@@ -600,9 +600,12 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         auto as_col = [&](int c) -> float { return A16 ? s_ascale[c] : s_as[c]; };  // (S == 1 only)
         // residual values one 16-column group ahead (out and residual may be one buffer: every element is read
         // before any store of its group, and by the thread that stores it)
-        float res_nx[RES ? 16 : 1];
+        // (batch tiles of 64 rows and more only: the smaller ones are launched split, and the registers this
+        // costs would take their third CTA per SM)
+        constexpr bool RES_AHEAD = RES && BN >= 64;
+        float res_nx[RES_AHEAD ? 16 : 1];
         auto fetch_res = [&](int c0) {
-            if constexpr (RES) {
+            if constexpr (RES_AHEAD) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const int m = m0 + c0 + j;
@@ -626,8 +629,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[j] = 0u;
             }
-            float res_cur[RES ? 16 : 1];
-            if constexpr (RES) {
+            float res_cur[RES_AHEAD ? 16 : 1];
+            if constexpr (RES_AHEAD) {
 #pragma unroll
                 for (int j = 0; j < 16; j++) res_cur[j] = res_nx[j];
                 if (S == 1) fetch_res(c0 + 16);
@@ -654,7 +657,10 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         if (EPI == EPI_F32) {
                             reinterpret_cast<float*>(p.out)[o] = val;
                         } else {
-                            if (RES) val = fmaf(as_col(c0 + j), ws * __uint_as_float(v[j]), res_cur[RES ? j : 0]);
+                            if (RES)
+                                val = fmaf(as_col(c0 + j), ws * __uint_as_float(v[j]),
+                                           RES_AHEAD ? res_cur[RES_AHEAD ? j : 0]
+                                                     : rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[o]));
                             reinterpret_cast<OutT*>(p.out)[o] = rv::T16<OutT>::from_f32_sat(val);
                         }
                     }

@@ -128,3 +128,17 @@ def test_missing_library_is_a_hard_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.RvllmError):
         _lib.lib()
+
+
+def test_build_register_budget_check():
+    """The build refuses a kernel that counts on three CTAs per SM when ptxas gave it more than 96 registers."""
+    from rvllm_b200 import build
+
+    ok = ("ptxas info    : Compiling entry function '_ZN4rvtc18fp8_gemm_tc_kernelILi32ELi1E13__nv_bfloat16EEv' for 'sm_100a'\n"
+          "ptxas info    : Function properties for x\n    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads\n"
+          "ptxas info    : Used 96 registers, used 2 barriers, 128 bytes smem\n"
+          "ptxas info    : Compiling entry function '_ZN4rvtc18fp8_gemm_tc_kernelILi256ELi1E13__nv_bfloat16EEv' for 'sm_100a'\n"
+          "ptxas info    : Used 120 registers, used 2 barriers\n")
+    build.check_register_budget(ok)  # the 256-row tile runs one CTA per SM: no budget
+    with pytest.raises(RuntimeError, match="register budget"):
+        build.check_register_budget(ok.replace("Used 96 registers", "Used 97 registers"))
