@@ -142,9 +142,12 @@ int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const 
                                    const void* w_fp8, const float* w_scale, const void* residual, int M, int N, int K,
                                    void* stream);
 
-/* gate|up projection + act(gate)*up + per-token FP8 re-quantisation in one call
+/* gate|up projection + act(gate)*up + per-token FP8 re-quantisation behind one call
  * (reference: GEMM at layer_exec.rs:484-494 followed by FusedSiluMulFp8QuantLaunch :509).
  * W [2*I, K] rows [gate(0..I) | up(I..2I)]; out_fp8 [M, I]; out_scale [M].
+ * One call, two launches: the GEMM writes its [M, 2*I] 16-bit result into the workspace and the
+ * act-mul-quant row kernel reads it back (at a decode batch the buffer stays in L2).  The single-launch form
+ * of this stage is the gate|up stage of rvllm_fp8_layer_block (RVLLM_BLOCK_GATEUP_ACT), same bytes.
  * Needs rvllm_fp8_gemm_gateup_workspace(M, I, K) bytes of workspace. */
 int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void* a_fp8, const void* w_fp8,
                                     const float* a_scale, const float* w_scale, int M, int I, int K, int act,
@@ -289,7 +292,9 @@ int rvllm_paged_decode_fp8_quant(const void* q_fp8, const void* k_cache_fp8, con
  * more than the built-in scratch is refused with RVLLM_E_WORKSPACE and nothing is launched.  It
  * calls no allocating routine.  The first call on each device looks up the scratch's device
  * address (once, with that device current), so make that first call before any stream capture
- * begins.  All calls on a device share the one array and it keeps the last call's contents
+ * begins; no call after that first one touches anything but the launch.  (cudaDeviceReset destroys the
+ * context the address belongs to: a process that resets a device must not use this entry point on it
+ * afterwards.)  All calls on a device share the one array and it keeps the last call's contents
  * (nothing in it needs clearing between calls): two calls whose kernels overlap on the GPU — on
  * different streams — race on it; keep them on one stream or order them with events. */
 size_t rvllm_paged_decode_static_scratch_bytes(void);

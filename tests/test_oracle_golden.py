@@ -159,6 +159,32 @@ def test_silu_quant_and_identity_rope(orc):
     assert out[0, 3] == 0x7E and out[0, 0] == 0x00 and out[0, 2] & 0x80
 
 
+# ---- gemma4_reference.rs:352-382 (partial RoPE golden vector: 32 heads x 512, rotary 128, position 7) ----
+def test_gemma4_global_partial_rope_golden_vector(orc):
+    heads, hd, rot = 32, 512, 128
+    x = np.zeros((1, (heads + 2) * hd), np.float32)           # one KV head behind the 32 query heads
+    x[0, 0], x[0, hd // 2], x[0, 1], x[0, hd // 2 + 1], x[0, rot // 2] = 1.0, 2.0, 3.0, 4.0, 7.0
+    cos = np.ones((8, rot // 2), np.float32)
+    sin = np.zeros((8, rot // 2), np.float32)
+    cos[7, 0], sin[7, 0], cos[7, 1], sin[7, 1] = 0.5, 0.8660254, -0.25, 0.96824586
+    kc = np.zeros((4, 1, hd), np.uint8)
+    vc = np.zeros_like(kc)
+    ksc, vsc = np.zeros(4, np.float32), np.zeros(4, np.float32)
+    q8, qs = orc.rope_fp8kv(orc.to_bits16(x, 0), heads, 1, hd, rot, orc.to_bits16(cos, 0), orc.to_bits16(sin, 0),
+                            np.array([7], np.int32), np.array([2], np.int32), kc, vc, ksc, vsc)
+    # The kernel form works on 16-bit tables and stores E4M3 with the head's scale (absmax 7 -> 7 / 448): the
+    # golden values must come back to within the table's 16-bit rounding plus half an E4M3 step at their size.
+    assert qs[0, 0] == np.float32(7.0) / np.float32(448.0)
+    deq = orc.e4m3_decode(q8[0, 0]) * qs[0, 0]
+    expected = {0: -1.2320508, hd // 2: 1.8660254, 1: -4.6229835, hd // 2 + 1: 1.9047375}
+    for idx, want in expected.items():
+        step = 2.0 ** (np.floor(np.log2(abs(want) / qs[0, 0])) - 3) * qs[0, 0]   # E4M3 spacing at this magnitude
+        assert abs(deq[idx] - want) <= 0.5 * step + 3e-3, (idx, deq[idx], want)
+    assert deq[rot // 2] == 7.0                                  # outside the rotary span: untouched
+    mag = q8 & 0x7F                                              # (0 * -0.25 is -0: code 0x80 as the kernels store it)
+    assert not mag[0, 1:].any() and not np.delete(mag[0, 0], list(expected) + [rot // 2]).any()
+
+
 # ---- 16-bit conversions used everywhere: exhaustive against numpy/torch ---------------
 def test_half_conversions_exhaustive(orc):
     torch = pytest.importorskip("torch")
