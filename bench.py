@@ -808,6 +808,41 @@ def run_batch(torch, cfg, weights, B, steps, warmup, e2e_steps, sampler=None, ba
     return res
 
 
+ABLATE_BITS = [(1, "RMSNorm + quant (attention block)"), (2, "QKV GEMM + RoPE / KV write"), (4, "decode attention"),
+               (8, "O projection + residual"), (16, "RMSNorm + quant (MLP block)"), (32, "gate|up GEMM"),
+               (64, "act-mul-quant"), (128, "down projection + residual")]
+
+
+def ablation(torch, cfg, weights, batches, steps):
+    """What each launch of a layer costs inside the decode graph: the step timed in full and with that launch left
+    out of every layer (the tokens of such a step mean nothing; its neighbours' work does not depend on the data).
+    Kernel time that overlaps with a neighbour under programmatic dependent launch does not show up here, time the
+    chain loses around the launch does."""
+    from rvllm_b200 import _lib
+    L = _lib.lib()
+    out = {}
+    for B in batches:
+        def timed(mask):
+            L.rvllm_stack_debug_skip(mask)
+            try:
+                r = run_batch(torch, cfg, weights, B, steps, 3, 0, seeded=True)
+            finally:
+                L.rvllm_stack_debug_skip(0)
+            return r
+        full = timed(0)
+        rows = []
+        for bit, name in ABLATE_BITS:
+            r = timed(bit)
+            rows.append({"launch": name, "ms_per_step_without": r["ms_per_step"],
+                         "us_per_layer": (full["ms_per_step"] - r["ms_per_step"]) * 1e3 / cfg["num_layers"]})
+        tail = timed(255)
+        out[str(B)] = {"ms_per_step": full["ms_per_step"], "layers": cfg["num_layers"], "per_launch": rows,
+                       "sum_us_per_layer": sum(x["us_per_layer"] for x in rows),
+                       "step_us_per_layer": (full["ms_per_step"] - tail["ms_per_step"]) * 1e3 / cfg["num_layers"],
+                       "ms_per_step_tail_only": tail["ms_per_step"]}
+    return out
+
+
 def greedy_parity_block(steps):
     """The composition the headline number times (fused QKV+RoPE epilogue, tcgen05 attention leaving per-row
     maxima, O projection quantising its own A tiles, fused gate|up activation, cluster argmax) decoded greedily at
@@ -959,6 +994,7 @@ def main():
                     help="only the decode attention at batch 64 with contexts uniform in [512, 32768]")
     ap.add_argument("--fused-block", type=int, default=0, choices=[0, 1],
                     help="1: run the step with the one-launch layer block (O projection .. next RMSNorm) instead of the chain")
+    ap.add_argument("--ablate", default="", help="only the in-graph cost of each launch of a layer, for these batches (comma list)")
     ap.add_argument("--layer-block-trace", action="store_true",
                     help="only the layer-block kernel alone at the layer dimensions, with its stage-boundary time stamps")
     ap.add_argument("--vs-ref-kernels", action="store_true",
@@ -991,7 +1027,7 @@ def main():
         peak, src = measured_peaks()
         print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
         return
-    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels or args.layer_block_trace:
+    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels or args.layer_block_trace or args.ablate:
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
@@ -1004,6 +1040,10 @@ def main():
             print(json.dumps({"ref_kernels": reference_kernel_table(torch, cfg)}))
         if args.layer_block_trace:
             print(json.dumps({"layer_block": layer_block_trace(torch, cfg, args.batch)}))
+        if args.ablate:
+            from rvllm_b200.stack import random_weights
+            w = random_weights(cfg, seed=3)
+            print(json.dumps({"ablation": ablation(torch, cfg, w, [int(x) for x in args.ablate.split(",")], args.steps)}))
         return
     if args.attention_only:
         import torch

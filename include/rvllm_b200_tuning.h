@@ -39,9 +39,21 @@ void rvllm_fp8_gemm_tc_reduce(int mode);
  * 4 = tcgen05 / TMEM / TMA; 0 picks 4 where the shape allows it, else 3, else 2).
  * Process-wide; the workspace query and the launch always use the same values. */
 void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant);
+/* Split-KV on the tcgen05 kernel with a 16-bit output: 1 (default) = the chunks of a (sequence, KV head) form one
+ * thread-block cluster (at most 8 chunks, each at least one 128-token tile) and the chunk-0 CTA merges the partials
+ * out of its own shared memory — no workspace traffic, no combine launch; 0 = partials through the workspace and the
+ * combine kernel, as the other variants do.  Process-wide. */
+void rvllm_paged_decode_cluster_combine(int enabled);
 /* Depth of the tcgen05 kernel's K/V ring in 16 KB units (2..8 for head_dim 128, 3..8 for 256);
  * 0 restores the automatic choice.  Tuning aid, process-wide. */
 void rvllm_paged_decode_ring(int units);
+
+/* Timing aid: decode stacks created while a mask is set leave the marked launches out of every layer of their step
+ * (1 attention-block RMSNorm, 2 QKV GEMM (+RoPE / KV write), 4 attention, 8 O projection, 16 MLP RMSNorm, 32 gate|up,
+ * 64 act-mul-quant, 128 down projection).  The tokens such a stack emits mean nothing; step time with a launch left
+ * out, against the full step, is what that launch costs inside the graph (its kernel time less whatever overlapped
+ * with its neighbours).  0 = off, the default; process-wide. */
+void rvllm_stack_debug_skip(int mask);
 
 /* What the layer-block kernel's residency check sees on the current device: CTAs of the kernel one SM holds and the
  * number of SMs (their product must cover the grid of 8 * hidden / 128 CTAs), from the device's per-SM limits.  The

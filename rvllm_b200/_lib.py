@@ -42,6 +42,8 @@ SIGNATURES = {
     "rvllm_b200_set_pdl": (None, [_i32]),
     "rvllm_b200_get_pdl": (_i32, []),
     "rvllm_b200_selftest_device_once": (_i32, []),
+    "rvllm_stack_debug_skip": (None, [_i32]),
+    "rvllm_paged_decode_cluster_combine": (None, [_i32]),
     "rvllm_fused_rmsnorm_fp8_quant_validate": (_i32, [_u32, _u32, _f32]),
     "rvllm_fused_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _i32, _vp]),
     "rvllm_fused_add_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),

@@ -16,6 +16,7 @@
 // straddle a change.
 static std::atomic<int> g_target_ctas{rvattn::TARGET_CTAS};
 static std::atomic<int> g_min_chunk_tokens{rvattn::MIN_CHUNK_TOKENS};
+static std::atomic<int> g_cluster_combine{1};
 static std::atomic<int> g_ring_units{0};  // tcgen05 kernel: K/V ring depth in 16 KB units, 0 = automatic
 static std::atomic<int> g_variant{0};  // 0 automatic (tcgen05 kernel where the shape allows, else 3, else 2), 1 FP32-pipe kernel,
                            // 2 mma.sync scores + FP32-pipe P.V, 3 both products on mma.sync, 4 tcgen05 / TMA
@@ -82,6 +83,8 @@ int rvllm_paged_decode_kernel_for(int num_heads, int num_kv_heads, int head_dim,
     return 2;
 }
 
+void rvllm_paged_decode_cluster_combine(int enabled) { g_cluster_combine = enabled != 0; }
+
 void rvllm_paged_decode_ring(int units) { g_ring_units = units > 0 ? units : 0; }
 
 int rvllm_paged_decode_tc_status(int* status, int reset) {
@@ -124,8 +127,11 @@ int launch_umma(const rvattn::Params& p, cudaStream_t s) {
         int units = ring > 0 ? ring : rvua::pick_units<HD>((long long)p.kv_heads * p.max_chunks * p.batch);
         if (units < C::MIN_UNITS) units = C::MIN_UNITS;
         if (units > rvua::MAX_UNITS) units = rvua::MAX_UNITS;
-        rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)C::smem_bytes(units), s,
-                  dim3(1, 1, 1), mk, mv, p, units);
+        // cluster-combine form: the chunks of a (sequence, KV head) are one cluster, the receive area sits behind the rest
+        const size_t recv = p.cluster_combine ? (size_t)C::recv_bytes(p.max_chunks, p.heads / p.kv_heads) : 0;
+        while (units > C::MIN_UNITS && C::smem_bytes(units) + recv > (size_t)C::smem_bytes(rvua::MAX_UNITS)) units--;
+        rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)C::smem_bytes(units) + recv, s,
+                  dim3(1, p.cluster_combine ? p.max_chunks : 1, 1), mk, mv, p, units);
         return rv_launched("paged_decode_fp8 (tcgen05)");
     } else {
         return rv_fail(RVLLM_E_UNSUPPORTED, "tcgen05 decode attention needs head_dim 128 or 256");
@@ -191,7 +197,7 @@ int launch_attn(const rvattn::Params& p, const QuantOut& qo, cudaStream_t s) {
                   p.max_chunks, p.min_chunk_tokens);
         return rv_launched("paged_decode_fp8_combine_quant");
     }
-    if (p.max_chunks > 1) {
+    if (p.max_chunks > 1 && !p.cluster_combine) {
         rv_launch((rvattn::paged_decode_fp8_combine_kernel<HD, OutT>), dim3(p.batch * p.heads), dim3(HD < 256 ? HD : 256), 0,
                   s, dim3(1, 1, 1), (const float*)p.workspace, (OutT*)p.out, (const int*)p.context_lens, p.heads, p.block_size, p.max_blocks_per_seq,
             p.window_size_left, p.max_chunks, p.min_chunk_tokens);
@@ -274,8 +280,22 @@ static int decode_core(const QuantOut& qo, const void* q_fp8, const void* k_cach
     p.min_chunk_tokens = g_min_chunk_tokens;
     p.force_partial = qo.fp8 ? 1 : 0;
     p.amax_out = qo.amax;
-    if (qo.amax && (chunks != 1 || g_variant == 1 || g_variant == 2 || g_variant == 3 || !rvua::supports(p, head_dim)))
-        return rv_fail(RVLLM_E_UNSUPPORTED, "the per-token absmax output needs the tcgen05 kernel and a single chunk");
+    p.cluster_combine = 0;
+    const bool umma = (g_variant == 4 || g_variant == 0) && rvua::supports(p, head_dim);
+    if (umma && chunks > 1 && !qo.fp8 && g_cluster_combine.load() != 0) {
+        // Split-KV without the workspace round trip and the combine launch: up to 8 chunks of at least one
+        // 128-token tile, one thread-block cluster per (sequence, KV head), merged in the chunk-0 CTA.
+        int cc = chunks < 8 ? chunks : 8;
+        const int group = num_heads / num_kv_heads;
+        while (cc > 1 && cc * group * (head_dim + 2) * 4 > rvua::MAX_RECV_BYTES) cc--;
+        if (cc > 1) {
+            p.max_chunks = cc;
+            p.min_chunk_tokens = rvua::TOK;
+            p.cluster_combine = 1;
+        }
+    }
+    if (qo.amax && !(umma && (chunks == 1 || p.cluster_combine)))
+        return rv_fail(RVLLM_E_UNSUPPORTED, "the per-token absmax output needs the tcgen05 kernel with one chunk or the cluster merge");
     cudaStream_t s = (cudaStream_t)stream;
     return out_dtype == RVLLM_F16 ? launch_attn_hd<__half>(p, qo, head_dim, s)
                                   : launch_attn_hd<__nv_bfloat16>(p, qo, head_dim, s);

@@ -10,10 +10,12 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <vector>
 
 #include "../../include/rvllm_b200.h"
 #include "../../include/rvllm_b200_stack.h"
+#include "../../include/rvllm_b200_tuning.h"
 #include "common.cuh"
 #include "host_util.h"
 
@@ -108,6 +110,7 @@ struct rvllm_stack {
     rvllm_head_weights head;
     std::vector<LayerState> ls;
     cudaStream_t stream = nullptr;
+    int skip_mask = 0;  // timing aid: launches left out of the step (rvllm_stack_debug_skip at creation time)
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int launches = 0;
@@ -274,8 +277,13 @@ namespace {
         if (rc_ != RVLLM_OK) return rc_; \
     } while (0)
 
+// Timing aid (rvllm_stack_debug_skip): launches left out of the steps of stacks created while it is set.
+std::atomic<int> g_skip_mask{0};
+
 // Enqueues one decode step on the stack's stream; counts launches when asked.
 int enqueue_step(rvllm_stack* s, int* launches) {
+    const int skip = s->skip_mask;
+    auto on = [skip](int bit) { return (skip & bit) == 0; };
     const rvllm_stack_config& c = s->cfg;
     const int B = c.batch, H = c.hidden;
     void* st = (void*)s->stream;
@@ -294,7 +302,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         const LayerState& L = s->ls[l];
         const rvllm_layer_weights& W = s->layers[l];
         const int es = 2;
-        if (!x_ready) {
+        if (!x_ready && on(1)) {
             RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
                                                         W.attn_norm_gamma, c.dtype, st));
             n++;
@@ -303,7 +311,8 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         // QKV projection, RoPE, Q quantisation and the paged KV write: one launch where the library
         // takes the shape (head_dim 128, batch <= 32, tensor-core GEMM), else the GEMM and the RoPE kernel
         int fused = RVLLM_E_UNSUPPORTED;
-        if (L.head_dim == 128 && c.gemm_impl != 1)
+        if (!on(2)) fused = RVLLM_OK, n--;  // (left out: timing aid)
+        else if (L.head_dim == 128 && c.gemm_impl != 1)
             fused = rvllm_fp8_gemm_qkv_rope_fp8kv(s->x_fp8, W.qkv_w, s->x_scale, W.qkv_scale, B, H, c.heads, c.kv_heads,
                                                   L.head_dim, c.dtype, s->q_fp8, s->q_scale, L.k_cache, L.v_cache,
                                                   L.k_scale, L.v_scale, L.global ? s->cos_g : s->cos_s,
@@ -327,22 +336,19 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         }
         const float sm_scale = 1.0f / sqrtf((float)L.head_dim);
         const int* tables = L.global ? s->tables_global : s->tables_sliding;
-        // Attention leaves its output in one of two forms.  (a) 16-bit values + per-(row, kv_head) maxima: one chunk
-        // per sequence on the tcgen05 kernel, batch <= 32 — the O projection quantises its own A tiles.  (b) FP8 rows +
-        // per-row scales: split-KV, the combine pass quantises (same bytes as attention -> per-token quantiser); also
+        // Attention leaves its output in one of two forms.  (a) 16-bit values + per-(row, kv_head) maxima: the tcgen05
+        // kernel at batch <= 32 — the O projection quantises its own A tiles.  (b) FP8 rows + per-row scales: split-KV
+        // through the workspace, the combine pass quantises (same bytes as attention -> per-token quantiser); also
         // what the plain call + quantiser produce.
         bool have16 = false;
-        if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
-            RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->attn_fp8, s->attn_scale, c.dtype, tables,
-                                                s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
-                                                s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads,
-                                                c.kv_heads, L.head_dim, c.block_size, L.max_blocks, L.num_blocks,
-                                                L.window_left, st));
-            n += 2;
+        const bool try16 = B <= 32 && c.gemm_impl != 1 &&
+                           rvllm_paged_decode_kernel_for(c.heads, c.kv_heads, L.head_dim, c.block_size, L.num_blocks) == 4;
+        if (!on(4)) {
+            have16 = try16;  // (left out: timing aid)
         } else {
+            // (a) first: single chunk, or split-KV merged inside a thread-block cluster (small batches)
             int a16 = RVLLM_E_UNSUPPORTED;
-            if (B <= 32 && c.gemm_impl != 1 &&
-                rvllm_paged_decode_kernel_for(c.heads, c.kv_heads, L.head_dim, c.block_size, L.num_blocks) == 4)
+            if (try16)
                 a16 = rvllm_paged_decode_fp8_amax(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, s->attn_amax,
                                                   tables, s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale,
                                                   L.v_scale, s->q_scale, nullptr, nullptr, nullptr, sm_scale, B,
@@ -353,6 +359,13 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                 n++;
             } else if (a16 != RVLLM_E_UNSUPPORTED) {
                 RV_TRY(a16);
+            } else if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
+                RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->attn_fp8, s->attn_scale, c.dtype, tables,
+                                                    s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
+                                                    s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads,
+                                                    c.kv_heads, L.head_dim, c.block_size, L.max_blocks, L.num_blocks,
+                                                    L.window_left, st));
+                n += 2;
             } else {
                 RV_TRY(rvllm_paged_decode_fp8(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, tables,
                                               s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
@@ -380,21 +393,27 @@ int enqueue_step(rvllm_stack* s, int* launches) {
             continue;
         }
         if (blk != RVLLM_E_UNSUPPORTED) RV_TRY(blk);
-        if (have16) {
+        if (!on(8)) {
+            n--;
+        } else if (have16) {
             RV_TRY(rvllm_fp8_gemm_residual_from16(s->residual, c.dtype, s->attn_out, s->attn_amax, c.kv_heads, W.o_w,
                                                   W.o_scale, s->residual, B, H, L.q_dim, st));
         } else {
             RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->attn_fp8, W.o_w, s->attn_scale, W.o_scale,
                                                s->residual, B, H, L.q_dim, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
         }
-        RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
-                                                    W.mlp_norm_gamma, c.dtype, st));
-        RV_TRY(rvllm_fp8_gemm_channelscale(s->gateup, c.dtype, s->x_fp8, W.gateup_w, s->x_scale, W.gateup_scale,
-                                           nullptr, B, 2 * c.ffn, H, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
-        RV_TRY(rvllm_fused_act_mul_fp8_quant_launch(B, c.ffn, c.act, s->x_fp8, s->x_scale, s->gateup, c.dtype, st));
-        RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.down_w, s->x_scale, W.down_scale,
-                                           s->residual, B, H, c.ffn, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
-        n += 5;
+        if (on(16))
+            RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
+                                                        W.mlp_norm_gamma, c.dtype, st));
+        if (on(32))
+            RV_TRY(rvllm_fp8_gemm_channelscale(s->gateup, c.dtype, s->x_fp8, W.gateup_w, s->x_scale, W.gateup_scale,
+                                               nullptr, B, 2 * c.ffn, H, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
+        if (on(64))
+            RV_TRY(rvllm_fused_act_mul_fp8_quant_launch(B, c.ffn, c.act, s->x_fp8, s->x_scale, s->gateup, c.dtype, st));
+        if (on(128))
+            RV_TRY(rvllm_fp8_gemm_channelscale(s->residual, c.dtype, s->x_fp8, W.down_w, s->x_scale, W.down_scale,
+                                               s->residual, B, H, c.ffn, c.gemm_impl, s->gemm_ws, s->gemm_ws_bytes, st));
+        n += 5 - !on(16) - !on(32) - !on(64) - !on(128);
     }
     if (!x_ready) {
         RV_TRY(rvllm_fused_rmsnorm_fp8_quant_launch(B, H, c.rms_eps, s->x_fp8, s->x_scale, s->residual,
@@ -518,6 +537,7 @@ int rvllm_stack_create(rvllm_stack** out, const rvllm_stack_config* cfg, const r
     }
     rvllm_stack* s = new rvllm_stack();
     s->cfg = *cfg;
+    s->skip_mask = g_skip_mask.load();
     s->layers.assign(layers, layers + cfg->num_layers);
     s->head = *head;
     s->arena_bytes = layout(s, nullptr);
@@ -714,6 +734,8 @@ int rvllm_stack_read_tokens(rvllm_stack* s, int first, int count, int32_t* out) 
                               cudaMemcpyDeviceToHost), "read history"));
     return count;
 }
+
+void rvllm_stack_debug_skip(int mask) { g_skip_mask = mask; }
 
 int rvllm_stack_steps_done(rvllm_stack* s) { return s ? s->steps_done : -1; }
 int rvllm_stack_launches_per_step(const rvllm_stack* s) { return s ? s->launches : -1; }

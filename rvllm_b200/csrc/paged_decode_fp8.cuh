@@ -75,7 +75,9 @@ struct Params {
     int max_chunks;
     int min_chunk_tokens;  // a sequence is cut into ceil(attended / this) chunks, at most max_chunks
     int force_partial;     // always leave partials in the workspace (the fused combine+quant pass reads them)
-    float* amax_out;       // tcgen05 kernel, single chunk: max |rounded output| per (sequence, kv_head), or null
+    float* amax_out;       // tcgen05 kernel, 16-bit output: max |rounded output| per (sequence, kv_head), or null
+    int cluster_combine;   // tcgen05 kernel: the chunks of a (sequence, kv_head) are one thread-block cluster and the
+                           // chunk-0 CTA merges their partials out of its own shared memory (no workspace, no combine launch)
 };
 
 // Upper bound on chunks per sequence for a launch shape; the workspace-size query and the

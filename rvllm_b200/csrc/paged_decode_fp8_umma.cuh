@@ -130,6 +130,14 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
                  "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
 }
+// 4-byte store into the shared memory of cluster rank `rank`, at the offset `local_saddr` has in this CTA.
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_saddr, uint32_t rank, float v) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "st.shared::cluster.f32 [ra], %2;\n\t}" ::"r"(local_saddr), "r"(rank), "f"(v)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {  // one MUFU; far-negative arguments give 0
@@ -175,7 +183,10 @@ template <int HD> struct Cfg {
     static constexpr int Q_BYTES = HALVES * NQ * PANEL;  // 2 KB per panel
     static constexpr int AUX_BYTES = 1024;               // barriers, TMEM holder, reduction scratch
     static constexpr int smem_bytes(int units) { return 1024 + units * UNIT + P_BYTES + Q_BYTES + AUX_BYTES; }
+    // cluster-combine form: partials of `chunks` CTAs x `group` query heads, [HD + 2] floats each, behind the rest
+    static constexpr int recv_bytes(int chunks, int group) { return chunks * group * (HD + 2) * 4; }
 };
+constexpr int MAX_RECV_BYTES = 24 * 1024;
 
 // Three-term E4M3 expansion of x in [0, 256]: x ~= hi + mid + lo with relative error ~2^-12.
 __device__ __forceinline__ void split3(float x, uint8_t& hi, uint8_t& mid, uint8_t& lo) {
@@ -211,8 +222,10 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 1);
     float* red = reinterpret_cast<float*>(aux + 256);      // [2][4][8] tile maxima, then [4][8] sums (96 floats)
     unsigned* s_bad = reinterpret_cast<unsigned*>(aux + 256 + 96 * 4);
+    float* recv = reinterpret_cast<float*>(aux + C::AUX_BYTES);  // cluster-combine form only: [chunk][head][HD + 2]
 
     rv::pdl_launch();
+    if (p.cluster_combine) asm volatile("barrier.cluster.arrive.release;" ::: "memory");  // "this CTA runs"
     const int kvh = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.heads / p.kv_heads;
@@ -618,6 +631,15 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                         const OutT stored = rv::T16<OutT>::from_f32(v);
                         out[((size_t)b * p.heads + head) * HD + d] = stored;
                         amax = fmaxf(amax, fabsf(rv::T16<OutT>::to_f32(stored)));  // fmaxf drops a NaN, as the quantiser does
+                    } else if (p.cluster_combine) {
+                        // staged in this CTA's own slot 0 (for chunk 0 that is its final place); sent to the
+                        // chunk-0 CTA further down, once that CTA is known to run
+                        float* st = recv + (size_t)k * PSTRIDE;
+                        st[d] = any_bad ? CUDART_NAN_F : acc[k];
+                        if (d == 0) {
+                            st[HD] = (m_run[k] - 8.0f) * 0.6931471805599453f;
+                            st[HD + 1] = any_bad ? CUDART_NAN_F : L;
+                        }
                     } else {
                         float* ws = p.workspace + (((size_t)b * p.heads + head) * p.max_chunks + chunk) * PSTRIDE;
                         ws[d] = any_bad ? CUDART_NAN_F : acc[k];
@@ -637,6 +659,55 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 p.amax_out[(size_t)b * p.kv_heads + kvh] = fmaxf(fmaxf(red[64], red[65]), fmaxf(red[66], red[67]));
         }
         tc_fence_before();
+    }
+    if (p.cluster_combine) {
+        // Every thread of every CTA of the cluster, active or not, passes these barriers: first "all CTAs of the
+        // cluster run" (the arrival was the kernel's first statement; shared memory of a CTA that has not started
+        // must not be written), then "the partials are in the chunk-0 CTA's shared memory".
+        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+        if (chunk != 0 && active && nchunks > 1 && warp >= 2) {
+            bar_softmax();  // the staged partial is complete
+            const uint32_t dst = smem_u32(recv + (size_t)chunk * nh * PSTRIDE);
+            for (int i = tid - 64; i < nh * PSTRIDE; i += 128) st_cluster_f32(dst + (uint32_t)i * 4u, 0u, recv[i]);
+        }
+        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+        if (chunk == 0 && active && nchunks > 1 && warp >= 2) {
+            // The merge of the combine kernel, chunk by chunk in order (same arithmetic, same order), then the
+            // store and the per-(sequence, KV head) maximum of the single-chunk path.
+            const int row = (warp - 2) * 32 + lane;
+            int m_start, m_len;
+            rvattn::attend_interval(ctx, p.window_size_left, m_start, m_len);
+            const int m_size = (m_len + nchunks - 1) / nchunks;
+            float amax = 0.0f;
+#pragma unroll
+            for (int h = 0; h < HALVES; h++) {
+                const int d = h * PANEL + row;
+                for (int k = 0; k < nh; k++) {
+                    float M = -1e20f, L = 0.0f, A = 0.0f;
+                    for (int c = 0; c < nchunks && c * m_size < m_len; c++) {  // (a chunk past the end stored nothing)
+                        const float* src = recv + (size_t)(c * nh + k) * PSTRIDE;
+                        const float mc = src[HD], lc = src[HD + 1];
+                        const float Mn = fmaxf(M, mc);
+                        const float ea = __expf(M - Mn), eb = __expf(mc - Mn);
+                        A = A * ea + src[d] * eb;
+                        L = L * ea + lc * eb;
+                        M = Mn;
+                    }
+                    const OutT stored = rv::T16<OutT>::from_f32(L > 0.0f ? A / L : A);
+                    out[((size_t)b * p.heads + (size_t)kvh * group + k) * HD + d] = stored;
+                    amax = fmaxf(amax, fabsf(rv::T16<OutT>::to_f32(stored)));
+                }
+            }
+            if (p.amax_out) {
+                amax = rv::warp_max(amax);
+                bar_softmax();
+                if (lane == 0) red[64 + (warp - 2)] = amax;
+                bar_softmax();
+                if (warp == 2 && lane == 0)
+                    p.amax_out[(size_t)b * p.kv_heads + kvh] = fmaxf(fmaxf(red[64], red[65]), fmaxf(red[66], red[67]));
+            }
+        }
     }
     __syncthreads();
     if (warp == 1) {

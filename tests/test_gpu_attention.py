@@ -213,8 +213,13 @@ def test_fused_quant_epilogue_equals_attention_then_quantiser(orc, dtype, batch,
     t = {k: dev(c[k]) for k in ("q", "k", "v", "tables", "ctx", "ks", "vs", "qs")}
     ws = torch.empty(max(La.quant_workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
     out16 = torch.empty((batch, Hh * HD), dtype=dtype, device="cuda")
-    La.launch(t["q"], t["k"], t["v"], out16, t["tables"], t["ctx"], workspace=ws, k_scale_cache=t["ks"],
-              v_scale_cache=t["vs"], q_scale_cache=t["qs"])
+    from rvllm_b200 import _lib
+    _lib.lib().rvllm_paged_decode_cluster_combine(0)   # both sides through the workspace: the same chunks, the same merge
+    try:
+        La.launch(t["q"], t["k"], t["v"], out16, t["tables"], t["ctx"], workspace=ws, k_scale_cache=t["ks"],
+                  v_scale_cache=t["vs"], q_scale_cache=t["qs"])
+    finally:
+        _lib.lib().rvllm_paged_decode_cluster_combine(1)
     b1 = torch.empty((batch, Hh * HD), dtype=torch.uint8, device="cuda")
     s1 = torch.empty(batch, dtype=torch.float32, device="cuda")
     QuantizeFp8PerTokenLaunch(batch, Hh * HD).launch(b1, s1, out16)
@@ -444,3 +449,47 @@ def test_attention_absmax_output(orc, kernel_variant, dtype, HD, window, ctxs):
     assert np.array_equal(got, want)
     ref = np.abs(got.reshape(B, 16, 2 * HD)).max(axis=2)
     assert np.array_equal(amax.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("HD,window,ctxs", [
+    (128, 1023, [516]), (128, 1023, [0, 1, 127, 128, 129, 600, 1024, 1500]), (128, -1, [3000, 5]),
+    (256, -1, [516]), (256, -1, [300, 17, 900, 128, 4000, 1025]), (256, 1023, [2000, 64])])
+def test_split_kv_merged_inside_a_cluster(orc, kernel_variant, dtype, HD, window, ctxs):
+    """Small batches on the tcgen05 kernel: the chunks of a (sequence, KV head) are one thread-block cluster and the
+    chunk-0 CTA merges them.  Against the oracle (the reference parity bench's rule), against the workspace form
+    (other chunk boundaries: same rule), and the per-(sequence, KV head) maxima against the stored output exactly."""
+    from rvllm_b200 import _lib
+    from rvllm_b200.attention import PagedDecodeParams
+    if kernel_variant != 4:
+        pytest.skip("the cluster merge exists in the tcgen05 kernel only")
+    L = _lib.lib()
+    B = len(ctxs)
+    mb = None if window < 0 else (window + 1 + 15) // 16 + 1
+    c = datagen.attention_case(orc, B, 32, 16, HD, 16, ctxs, seed=5 + HD + B, window=window, max_blocks=mb)
+    p = PagedDecodeParams(B, 32, 16, HD, 16, c["max_blocks"], c["num_blocks"], HD ** -0.5, window)
+    assert p.max_chunks() > 1
+    L.rvllm_paged_decode_cluster_combine(0)
+    try:
+        through_ws = run_ours(c, out_dtype=dtype)
+    finally:
+        L.rvllm_paged_decode_cluster_combine(1)
+    plain = run_ours(c, out_dtype=dtype)                     # the plain entry point takes the cluster form too
+    t = {k: dev(c[k]) for k in ("q", "k", "v", "ks", "vs", "qs", "tables", "ctx")}
+    out = torch.full((B, 32, HD), 123.0, dtype=dtype, device="cuda")
+    amax = torch.full((B, 16), -1.0, dtype=torch.float32, device="cuda")
+    ws = torch.empty(max(p.workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
+    for _ in range(2):                                       # twice: nothing is left behind between launches
+        rc = L.rvllm_paged_decode_fp8_amax(t["q"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), out.data_ptr(),
+                                           0 if dtype == torch.float16 else 1, amax.data_ptr(), t["tables"].data_ptr(),
+                                           t["ctx"].data_ptr(), ws.data_ptr(), ws.numel(), t["ks"].data_ptr(),
+                                           t["vs"].data_ptr(), t["qs"].data_ptr(), None, None, None, HD ** -0.5, B, 32, 16,
+                                           HD, 16, c["max_blocks"], c["num_blocks"], window,
+                                           torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    assert np.array_equal(got, plain)
+    assert_close(got, run_oracle(orc, c, precise=True, dtype=0 if dtype == torch.float16 else 1).astype(np.float64))
+    assert_close(got, through_ws.astype(np.float64), abs_tol=ABS_TOL, rel_tol=REL_TOL)
+    assert np.array_equal(amax.cpu().numpy(), np.abs(got.reshape(B, 16, 2 * HD)).max(axis=2))

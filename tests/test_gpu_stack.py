@@ -64,15 +64,29 @@ def bench_composition_shape(batch, **over):
     return tiny_shape(**cfg)
 
 
-@pytest.mark.parametrize("batch,fused_block", [(32, 1), (32, 0), (4, 1), (4, 0), (40, 1)])
-def test_bench_kernel_composition_against_oracle_chain(orc, batch, fused_block):
+def assert_waits_ok():
+    """No bounded wait of the tcgen05 GEMM or attention kernels ran out."""
+    import ctypes
+    from rvllm_b200 import _lib, gemm
+    status = gemm.tc_status()
+    assert status == 0, "a bounded wait ran out in the GEMM (site %d, CTA %d)" % (status >> 16, status & 0xffff)
+    st = ctypes.c_int(0)
+    assert _lib.lib().rvllm_paged_decode_tc_status(ctypes.byref(st), 1) == 0
+    assert st.value == 0, "a bounded wait ran out in the attention kernel (site %d)" % (st.value >> 16)
+
+
+@pytest.mark.parametrize("batch,fused_block,cluster_kv", [(32, 1, 1), (32, 0, 1), (4, 1, 1), (4, 0, 1), (4, 1, 0), (4, 0, 0),
+                                                         (40, 1, 1)])
+def test_bench_kernel_composition_against_oracle_chain(orc, batch, fused_block, cluster_kv):
     """256 greedy steps of the compositions the benchmark times, against the oracle chain.
 
     batch 32, block kernel on : QKV+RoPE+KV-write epilogue, tcgen05 attention leaving per-row maxima, then ONE launch
                                 for O projection .. down projection .. next RMSNorm (what the headline number runs)
     batch 32, block kernel off: the same with stand-alone kernels (O projection quantising its own A tiles, cluster
                                 kernels for the row ops)
-    batch 4                   : split-KV attention with the fused combine+quantise pass feeding either form
+    batch 4                   : split-KV attention merged inside a thread-block cluster (one launch, the batch-32 forms
+                                downstream); with that switched off, split-KV through the workspace with the fused
+                                combine+quantise pass feeding either form
     batch 40                  : above the 32-row forms: the unfused ten-launch layer
 
     Launches in one step's graph (2 sliding head_dim-128 layers + 1 global head_dim-256 layer whose RoPE stays a
@@ -80,8 +94,8 @@ def test_bench_kernel_composition_against_oracle_chain(orc, batch, fused_block):
     feedback; the final RMSNorm is a launch unless the last block kernel did it):
       batch 32 on : (norm, QKV, attention, block) + (QKV, attention, block) + (QKV, RoPE, attention, block) + 5 = 16
       batch 32 off: 8 + 8 + 9 + final norm + 5 = 31
-      batch 4  on : attention is two launches (main + combine/quantise): 5 + 4 + 5 + 5 = 19
-      batch 4  off: 9 + 9 + 10 + 1 + 5 = 34
+      batch 4     : as batch 32 (16 / 31); workspace split-KV: attention is two launches (main + combine/quantise),
+                    5 + 4 + 5 + 5 = 19 with the block kernel, 9 + 9 + 10 + 1 + 5 = 34 without
       batch 40    : 10 + 10 + 10 + 1 + 5 = 36"""
     from oracle.chain import greedy_parity
     from rvllm_b200 import _lib
@@ -91,13 +105,19 @@ def test_bench_kernel_composition_against_oracle_chain(orc, batch, fused_block):
     nblk_s = batch * (cfg["sliding_window"] // cfg["block_size"] + 1)
     assert L.rvllm_paged_decode_kernel_for(32, 16, 128, 16, nblk_s) == 4      # the tcgen05 attention kernel
     assert L.rvllm_paged_decode_kernel_for(32, 16, 256, 16, nblk_s) == 4
-    stack, w = make(cfg)
-    chunks = L.rvllm_paged_decode_max_chunks(batch, 16)
-    assert (chunks == 1) == (batch >= 32)
-    want = {(32, 1): 16, (32, 0): 31, (4, 1): 19, (4, 0): 34, (40, 1): 36}[(batch, fused_block)]
-    assert stack.launches_per_step() == want, stack.launches_per_step()
-    prompt = np.random.default_rng(batch).integers(0, cfg["vocab"], (batch, cfg["prompt_len"]), dtype=np.int32)
-    check_parity(greedy_parity(orc, stack, cfg, w, prompt, steps, LOGIT_TOL))
+    L.rvllm_paged_decode_cluster_combine(cluster_kv)
+    try:
+        stack, w = make(cfg)
+        chunks = L.rvllm_paged_decode_max_chunks(batch, 16)
+        assert (chunks == 1) == (batch >= 32)
+        want = {(32, 1, 1): 16, (32, 0, 1): 31, (4, 1, 1): 16, (4, 0, 1): 31, (4, 1, 0): 19, (4, 0, 0): 34,
+                (40, 1, 1): 36}[(batch, fused_block, cluster_kv)]
+        assert stack.launches_per_step() == want, stack.launches_per_step()
+        prompt = np.random.default_rng(batch).integers(0, cfg["vocab"], (batch, cfg["prompt_len"]), dtype=np.int32)
+        check_parity(greedy_parity(orc, stack, cfg, w, prompt, steps, LOGIT_TOL))
+        assert_waits_ok()
+    finally:
+        L.rvllm_paged_decode_cluster_combine(1)
     from rvllm_b200 import gemm
     assert gemm.tc_status() == 0
     stack.close()
