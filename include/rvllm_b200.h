@@ -145,10 +145,14 @@ int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const 
 /* gate|up projection + act(gate)*up + per-token FP8 re-quantisation behind one call
  * (reference: GEMM at layer_exec.rs:484-494 followed by FusedSiluMulFp8QuantLaunch :509).
  * W [2*I, K] rows [gate(0..I) | up(I..2I)]; out_fp8 [M, I]; out_scale [M].
- * One call, two launches: the GEMM writes its [M, 2*I] 16-bit result into the workspace and the
- * act-mul-quant row kernel reads it back (at a decode batch the buffer stays in L2).  The single-launch form
- * of this stage is the gate|up stage of rvllm_fp8_layer_block (RVLLM_BLOCK_GATEUP_ACT), same bytes.
- * Needs rvllm_fp8_gemm_gateup_workspace(M, I, K) bytes of workspace. */
+ * impl 0: one launch where the shape allows (M <= 32, K a multiple of 128 up to 6144, I a multiple of 64 up to
+ * 4 * K, every CTA of the launch resident at once): the gate|up stage of the layer-block kernel — gate and up
+ * rows of the same 64 columns form one 128-row tensor-core operand, the epilogue multiplies act(gate) by up on
+ * chip, the grid meets once for the row maxima and quantises; the [M, 2*I] intermediate never reaches HBM
+ * (preceded by a 256-byte memset of the barrier words at the front of the workspace).  Otherwise, and with
+ * impl 1 (streaming GEMM) / 2 (tcgen05 GEMM), two launches: the GEMM writes its [M, 2*I] 16-bit result into the
+ * workspace and the act-mul-quant row kernel reads it back.  impl 3: the single launch or RVLLM_E_UNSUPPORTED.
+ * Same bytes and scales in every form.  Needs rvllm_fp8_gemm_gateup_workspace(M, I, K) bytes of workspace. */
 int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void* a_fp8, const void* w_fp8,
                                     const float* a_scale, const float* w_scale, int M, int I, int K, int act,
                                     int dtype, int impl, void* workspace, size_t workspace_size, void* stream);

@@ -294,14 +294,57 @@ int rvllm_fp8_gemm_gateup_act_quant(void* out_fp8, float* out_scale, const void*
     int rc = rvllm_fused_act_mul_fp8_quant_validate((uint32_t)M, (uint32_t)I);
     if (rc) return rc;
     if (dtype != RVLLM_F16 && dtype != RVLLM_BF16) return rv_fail(RVLLM_E_INVALID, "dtype must be f16 or bf16");
+    if (act != RVLLM_ACT_SILU && act != RVLLM_ACT_GELU_TANH) return rv_fail(RVLLM_E_INVALID, "unknown activation");
+    if (impl < 0 || impl > 3) return rv_fail(RVLLM_E_INVALID, "impl must be 0..3");
     const size_t stage = ((size_t)M * 2 * (size_t)I * 2 + 255) & ~(size_t)255;
     if (!workspace || !rv_aligned(workspace, 256) || workspace_size < rvllm_fp8_gemm_gateup_workspace(M, I, K))
         return rv_fail(RVLLM_E_WORKSPACE, "gate-up workspace missing, misaligned or too small");
-    // The projection lands in the 16-bit type the standalone chain would use, so the
+    // One launch where the layer-block kernel's gate|up stage takes the shape (batch <= 32, K a multiple of 128 up to
+    // 6144, I a multiple of 64 up to 4 * K): gate and up rows of the same 64 columns are one 128-row operand, the
+    // epilogue rounds both to the 16-bit type, multiplies, keeps the products on chip, the grid meets once for the
+    // row maxima and quantises — the [M, 2*I] intermediate never reaches HBM.  Same bytes as the two launches below.
+    if (impl == 0 || impl == 3) {
+        const bool takes = rvblk::blk_shape_ok(M, K, I, K) && rv_aligned(a_fp8, 16) && rv_aligned(w_fp8, 16) &&
+                           rv_aligned(out_fp8, 16) && a_scale && w_scale && out_scale &&
+                           workspace_size >= 256 + rvblk::blk_amax_bytes(I);
+        if (takes) {
+            rvblk::BlkArgs b = {};
+            b.M = M;
+            b.H = K;
+            b.F = I;
+            b.KO = K;
+            b.act = act;
+            b.dtype = dtype == RVLLM_F16 ? 0 : 1;
+            b.phases = rvblk::PH_GU;
+            b.eps = 0.0f;
+            b.attn16 = a_fp8;  // (stages that are not run: any valid address, never read)
+            b.o_w = w_fp8;
+            b.d_w = w_fp8;
+            b.x8 = const_cast<void*>(a_fp8);
+            b.xs = const_cast<float*>(a_scale);
+            b.gu_w = w_fp8;
+            b.gu_wscale = w_scale;
+            b.h8 = out_fp8;
+            b.hs = out_scale;
+            b.workspace = workspace;
+            b.workspace_bytes = workspace_size;
+            // the grid barrier's words: zero before a launch (every launch leaves them zero, but the two-launch form
+            // of this call uses the same bytes as its staging buffer)
+            if (cudaMemsetAsync(workspace, 0, 256, (cudaStream_t)stream) != cudaSuccess) {
+                cudaGetLastError();
+                return rv_fail(RVLLM_E_LAUNCH, "cannot clear the gate-up barrier words");
+            }
+            rc = rvblk::launch_block(b, (cudaStream_t)stream);
+            if (rc == 0) return RVLLM_OK;
+            if (rc != -3) return rc;
+        }
+        if (impl == 3) return rv_fail(RVLLM_E_UNSUPPORTED, "gate-up single launch: shape not taken");
+    }
+    // Two launches.  The projection lands in the 16-bit type the standalone chain would use, so the
     // activation + re-quantisation sees bit-identical inputs either way.
     GemmArgs g = {workspace, dtype == RVLLM_F16 ? RVLLM_OUT_F16 : RVLLM_OUT_BF16, a_fp8, w_fp8, a_scale, w_scale,
                   nullptr, M, 2 * I, K};
-    rc = run_gemm(g, impl, (char*)workspace + stage, workspace_size - stage, (cudaStream_t)stream);
+    rc = run_gemm(g, impl == 3 ? 0 : impl, (char*)workspace + stage, workspace_size - stage, (cudaStream_t)stream);
     if (rc) return rc;
     return rvllm_fused_act_mul_fp8_quant_launch((uint32_t)M, (uint32_t)I, act, out_fp8, out_scale, workspace, dtype,
                                                 stream);

@@ -795,7 +795,8 @@ template <typename K> inline int block_capacity_of(K kern, int* per_sm, int* sms
     }
     const int regs_warp = ((fa.numRegs * 32 + 255) / 256) * 256;
     int n = smem_sm / (SMEM_BYTES + (int)fa.sharedSizeBytes + smem_res);
-    const int by_regs = regs_sm / (regs_warp * (THREADS / 32)), by_thr = thr_sm / THREADS, by_tmem = 512 / 32;
+    // (registers belong to the SM's four schedulers, a quarter each: whole warps per scheduler, not per SM)
+    const int by_regs = 4 * ((regs_sm / 4) / regs_warp) / (THREADS / 32), by_thr = thr_sm / THREADS, by_tmem = 512 / 32;
     n = n < by_regs ? n : by_regs;
     n = n < by_thr ? n : by_thr;
     n = n < by_tmem ? n : by_tmem;

@@ -197,27 +197,52 @@ def test_reference_named_entry_points(orc, impl):
                                           b_scale.data_ptr(), res.data_ptr(), M, N, K, ws2.data_ptr(), 16, s) != 0
 
 
-@pytest.mark.parametrize("impl", [STREAM, TC], ids=["stream", "tc"])
+SINGLE = 3  # rvllm_fp8_gemm_gateup_act_quant: the one-launch form or RVLLM_E_UNSUPPORTED
+
+
+@pytest.mark.parametrize("impl", [STREAM, TC, SINGLE, 0], ids=["stream", "tc", "single-launch", "auto"])
 @pytest.mark.parametrize("act", [0, 1])
-def test_gateup_act_quant_equals_unfused_chain(orc, impl, act):
-    """Fused entry point == GEMM then act-mul-quant, bit for bit, and close to the oracle."""
+@pytest.mark.parametrize("M,I,K", [(32, 2048, 512), (7, 1024, 1024), (32, 21504, 5376)])
+def test_gateup_act_quant_equals_unfused_chain(orc, impl, act, M, I, K):
+    """The gate|up + act + quant entry point == GEMM, then the stand-alone act-mul-quant kernel (itself bit-equal to
+    the reference's kernels, test_gpu_rowops), bit for bit: the two-launch forms against their own GEMM family, the
+    one-launch form (products never leave the chip, row maxima across a grid barrier) against the tcgen05 chain; and
+    close to the oracle."""
     from rvllm_b200 import gemm
     from rvllm_b200.launchers import FusedActMulFp8QuantLaunch
-    M, I, K = 32, 2048, 512
-    a, a_s, w, w_s, cols, want = case(orc, M, 2 * I, K, seed=7)
-    d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
-    A, W, AS, WS = d(a), d(w), d(a_s), d(w_s)
+    if I > 4096 and impl == STREAM:
+        pytest.skip("the full-size case runs on the tensor-core forms")
+    big = I > 4096
+    if big:   # operands straight on the device: the CPU oracle is not asked for 43008 x 5376 x 32
+        g = torch.Generator(device="cuda")
+        g.manual_seed(11)
+        A = torch.randint(0, 255, (M, K), dtype=torch.uint8, device="cuda", generator=g)
+        A[A == 0x7F] = 0x7E
+        W = torch.randint(0, 127, (2 * I, K), dtype=torch.uint8, device="cuda", generator=g) ^ \
+            (torch.randint(0, 2, (2 * I, K), dtype=torch.uint8, device="cuda", generator=g) << 7)
+        W[(W & 0x7F) == 0x7F] = 0x7E
+        AS = torch.rand(M, dtype=torch.float32, device="cuda", generator=g) * 1e-2 + 1e-3
+        WS = torch.rand(2 * I, dtype=torch.float32, device="cuda", generator=g) * 1e-4 + 1e-5
+    else:
+        a, a_s, w, w_s, cols, want = case(orc, M, 2 * I, K, seed=7)
+        d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+        A, W, AS, WS = d(a), d(w), d(a_s), d(w_s)
     ws = torch.empty(gemm.gateup_workspace_bytes(M, I, K), dtype=torch.uint8, device="cuda")
+    ws.fill_(0xA5)                                            # the entry point must not count on a clean workspace
     out = torch.empty((M, I), dtype=torch.uint8, device="cuda")
     sc = torch.empty(M, dtype=torch.float32, device="cuda")
-    gemm.fp8_gemm_gateup_act_quant(out, sc, A, W, AS, WS, act, 1, ws, impl=impl)
+    for _ in range(2):                                        # twice: the barrier words are left clean
+        gemm.fp8_gemm_gateup_act_quant(out, sc, A, W, AS, WS, act, 1, ws, impl=impl)
     gu = torch.empty((M, 2 * I), dtype=torch.bfloat16, device="cuda")
-    gemm.fp8_gemm_channelscale(gu, A, W, AS, WS, impl=impl)
+    gemm.fp8_gemm_channelscale(gu, A, W, AS, WS, impl=STREAM if impl == STREAM else TC)
     out2 = torch.empty_like(out)
     sc2 = torch.empty_like(sc)
     FusedActMulFp8QuantLaunch(M, I, act).launch(out2, sc2, gu)
     torch.cuda.synchronize()
-    assert torch.equal(out, out2) and torch.equal(sc, sc2)
+    assert gemm.tc_status() == 0
+    assert torch.equal(sc, sc2) and torch.equal(out, out2)
+    if big:
+        return
     # against the oracle chain: dequantised values agree within the GEMM tolerance + one FP8 step
     wb, wsc = orc.act_mul_fp8_quant(orc.to_bits16(want, orc.BF16), act, orc.BF16, orc.MODE_CUDA)
     got = orc.e4m3_decode(out.cpu().numpy()) * sc.cpu().numpy()[:, None]
