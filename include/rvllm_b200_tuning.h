@@ -44,6 +44,9 @@ void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant)
  * out of its own shared memory — no workspace traffic, no combine launch; 0 = partials through the workspace and the
  * combine kernel, as the other variants do.  Process-wide. */
 void rvllm_paged_decode_cluster_combine(int enabled);
+/* The cluster-merged form's own plan: CTAs aimed for (chunks per sequence = ceil(target / (batch * KV heads)), at most
+ * 8) and the smallest chunk in tokens; 0 restores the defaults.  Process-wide. */
+void rvllm_paged_decode_cluster_tune(int target_ctas, int min_chunk_tokens);
 /* Depth of the tcgen05 kernel's K/V ring in 16 KB units (2..8 for head_dim 128, 3..8 for 256);
  * 0 restores the automatic choice.  Tuning aid, process-wide. */
 void rvllm_paged_decode_ring(int units);

@@ -17,6 +17,10 @@
 static std::atomic<int> g_target_ctas{rvattn::TARGET_CTAS};
 static std::atomic<int> g_min_chunk_tokens{rvattn::MIN_CHUNK_TOKENS};
 static std::atomic<int> g_cluster_combine{1};
+static std::atomic<int> g_cluster_min_tokens{rvua::TOK};  // smallest chunk of the cluster-merged split-KV form
+// CTAs the cluster-merged form aims for: chunks cost it neither workspace traffic nor a second launch
+constexpr int CLUSTER_TARGET_CTAS = rvattn::TARGET_CTAS;
+static std::atomic<int> g_cluster_target{CLUSTER_TARGET_CTAS};
 static std::atomic<int> g_ring_units{0};  // tcgen05 kernel: K/V ring depth in 16 KB units, 0 = automatic
 static std::atomic<int> g_variant{0};  // 0 automatic (tcgen05 kernel where the shape allows, else 3, else 2), 1 FP32-pipe kernel,
                            // 2 mma.sync scores + FP32-pipe P.V, 3 both products on mma.sync, 4 tcgen05 / TMA
@@ -84,6 +88,10 @@ int rvllm_paged_decode_kernel_for(int num_heads, int num_kv_heads, int head_dim,
 }
 
 void rvllm_paged_decode_cluster_combine(int enabled) { g_cluster_combine = enabled != 0; }
+void rvllm_paged_decode_cluster_tune(int target_ctas, int min_chunk_tokens) {
+    g_cluster_target = target_ctas > 0 ? target_ctas : CLUSTER_TARGET_CTAS;
+    g_cluster_min_tokens = min_chunk_tokens > 0 ? min_chunk_tokens : rvua::TOK;
+}
 
 void rvllm_paged_decode_ring(int units) { g_ring_units = units > 0 ? units : 0; }
 
@@ -282,15 +290,16 @@ static int decode_core(const QuantOut& qo, const void* q_fp8, const void* k_cach
     p.amax_out = qo.amax;
     p.cluster_combine = 0;
     const bool umma = (g_variant == 4 || g_variant == 0) && rvua::supports(p, head_dim);
-    if (umma && chunks > 1 && !qo.fp8 && g_cluster_combine.load() != 0) {
+    const int cchunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_cluster_target);
+    if (umma && cchunks > 1 && !qo.fp8 && g_cluster_combine.load() != 0) {
         // Split-KV without the workspace round trip and the combine launch: up to 8 chunks of at least one
         // 128-token tile, one thread-block cluster per (sequence, KV head), merged in the chunk-0 CTA.
-        int cc = chunks < 8 ? chunks : 8;
+        int cc = cchunks < 8 ? cchunks : 8;
         const int group = num_heads / num_kv_heads;
         while (cc > 1 && cc * group * (head_dim + 2) * 4 > rvua::MAX_RECV_BYTES) cc--;
         if (cc > 1) {
             p.max_chunks = cc;
-            p.min_chunk_tokens = rvua::TOK;
+            p.min_chunk_tokens = g_cluster_min_tokens.load();
             p.cluster_combine = 1;
         }
     }
