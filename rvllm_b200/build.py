@@ -63,7 +63,8 @@ def _run(cmd):
 # (allocated in eights).  One register more and only 16 warps fit: two CTAs per SM, the 336-CTA launches of
 # the decode step run in two waves (measured: down projection 25 -> 37 us).
 REG_BUDGET = 96
-REG_BUDGET_KERNELS = (r"fp8_gemm_tc_kernelILi16E", r"fp8_gemm_tc_kernelILi32E", r"fp8_layer_block_kernel")
+REG_BUDGET_KERNELS = (r"fp8_gemm_tc_kernelILi16E", r"fp8_gemm_tc_kernelILi32E", r"fp8_gemm_tc_kernelILi64E",
+                      r"fp8_gemm_tc_kernelILi128E", r"fp8_layer_block_kernel")
 
 
 def check_register_budget(ptxas_log):

@@ -313,7 +313,10 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         __syncthreads();
     }
     const bool push = S > 1 && p.push != 0;
-    if (push) cluster_arrive();  // "this CTA runs": peers wait for it (long since complete) before their first remote store
+    // push == 3: the receive buffer is the (by then idle) ring itself — batch tiles of 64 / 128 rows, whose partials
+    // would not fit behind it.  The cluster then meets after the main loops instead ("every ring is free").
+    const bool push_ring = push && p.push == 3;
+    if (push && !push_ring) cluster_arrive();  // "this CTA runs": peers wait for it (long since complete) before their first remote store
 
     if (warp == 0) {
         if (lane == 0) {
@@ -425,7 +428,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // own rank), the cluster meets once, and each CTA sums the S slots of its columns in rank order:
         // one barrier, no remote loads, bitwise reproducible.  Measured ~2.5 us per launch less than
         // pulling the partials out of the peers' rings (two barriers and a remote-load round trip).
-        float* recv = reinterpret_cast<float*>(ring + (size_t)STAGES * C::STAGE_BYTES);  // [S][LC][TILE_W]
+        float* recv = reinterpret_cast<float*>(push_ring ? ring : ring + (size_t)STAGES * C::STAGE_BYTES);  // [S][LC][TILE_W]
         const int LC = (BN + S - 1) / S;
         constexpr int PRE = 3;
         float pre_a[PRE], pre_w[PRE], pre_res[PRE];
@@ -442,12 +445,18 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     pre_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
             }
         }
-        cluster_wait();  // every CTA of the cluster is running
+        bool ready = true;
+        if (push_ring) {
+            // own MMAs complete = every load into this CTA's ring has landed and been read: the ring is free;
+            // once the whole cluster has said so, every ring may be written
+            if (warp >= EPI_WARP0 && nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+            cluster_arrive();
+        }
+        cluster_wait();  // every CTA of the cluster is running (and, in the ring form, done with its ring)
         if (warp >= EPI_WARP0) {
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane;
-            bool ready = true;
-            if (nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+            if (!push_ring && nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
             tc_fence_after();
             const uint32_t slot = smem_u32(recv) + (uint32_t)((split * LC) * TILE_W + r) * 4u;  // [split][0][r]
             uint32_t owner = 0, lc_off = 0;
@@ -578,8 +587,26 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         };
 #pragma unroll
         for (int j = 0; j < PRE; j++) finish((int)threadIdx.x + j * THREADS, true, pre_a[j], pre_w[j], pre_res[j]);
+        // (larger batch tiles: the rest in groups as well — loads of a group before its stores, see the pull form)
 #pragma unroll 1
-        for (int e = (int)threadIdx.x + PRE * THREADS; e < LC * TILE_W; e += THREADS) finish(e, false, 0.0f, 0.0f, 0.0f);
+        for (int e0 = (int)threadIdx.x + PRE * THREADS; e0 < LC * TILE_W; e0 += PRE * THREADS) {
+            float g_a[PRE], g_w[PRE], g_res[PRE];
+#pragma unroll
+            for (int j = 0; j < PRE; j++) {
+                const int e = e0 + j * THREADS;
+                const int col = (e / TILE_W) * S + split;
+                const int m = m0 + col, n = n0 + e % TILE_W;
+                g_a[j] = g_w[j] = g_res[j] = 0.0f;
+                if (e < LC * TILE_W && col < BN && m < p.M && n < p.N) {
+                    g_a[j] = a_scale_of(m);
+                    g_w[j] = p.w_scale[n];
+                    if (RES)
+                        g_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PRE; j++) finish(e0 + j * THREADS, true, g_a[j], g_w[j], g_res[j]);
+        }
         }
     } else if (EPI != EPI_QKV_ROPE) {  // (the fused QKV epilogue exists in the push form only; the host launches no other)
     float* part = reinterpret_cast<float*>(ring);  // [BN][TILE_W] f32: split-K partials, or the logits of the argmax form
@@ -600,9 +627,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         auto as_col = [&](int c) -> float { return A16 ? s_ascale[c] : s_as[c]; };  // (S == 1 only)
         // residual values one 16-column group ahead (out and residual may be one buffer: every element is read
         // before any store of its group, and by the thread that stores it)
-        // (batch tiles of 64 rows and more only: the smaller ones are launched split, and the registers this
-        // costs would take their third CTA per SM)
-        constexpr bool RES_AHEAD = RES && BN >= 64;
+        // (256-row batch tiles only, which run one CTA per SM: the smaller ones count on three, and the registers
+        // this costs would take the third away)
+        constexpr bool RES_AHEAD = RES && BN >= 256;
         float res_nx[RES_AHEAD ? 16 : 1];
         auto fetch_res = [&](int c0) {
             if constexpr (RES_AHEAD) {
@@ -769,35 +796,16 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int e = e_first + j * e_step;
             if (e < BN * TILE_W) finish(e, sums[j], pre_a[j], pre_w[j], true, pre_res[j]);
         }
-        // The rest in groups of PRE as well: all loads of a group, then its stores.  (A load placed after a
-        // store cannot be moved above it — out and residual may be one buffer — so element-by-element code
-        // pays a full load latency per element.)
-        for (int e0 = e_first + PRE * e_step; e0 < BN * TILE_W; e0 += PRE * e_step) {
-            float g_sum[PRE], g_a[PRE], g_w[PRE], g_res[PRE];
+        // (The rest one element at a time: this form only serves 256-row tiles and forced comparisons now, and a
+        // grouped loop costs the registers that keep three CTAs of the smaller tiles on an SM.)
+        for (int e = e_first + PRE * e_step; e < BN * TILE_W; e += e_step) {
+            float sum = 0.0f;
 #pragma unroll
-            for (int j = 0; j < PRE; j++) {
-                const int e = e0 + j * e_step;
-                g_sum[j] = g_a[j] = g_w[j] = g_res[j] = 0.0f;
-                if (e < BN * TILE_W) {
-                    float sum = 0.0f;
-#pragma unroll
-                    for (int s = 0; s < 8; s++)
-                        if (s < S) sum += peer[s][e];
-                    g_sum[j] = sum;
-                    const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
-                    if (m < p.M && n < p.N) {
-                        g_a[j] = a_scale_of(m);
-                        g_w[j] = p.w_scale[n];
-                        if (RES)
-                            g_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < PRE; j++) {
-                const int e = e0 + j * e_step;
-                if (e < BN * TILE_W) finish(e, g_sum[j], g_a[j], g_w[j], true, g_res[j]);
-            }
+            for (int s = 0; s < 8; s++)
+                if (s < S) sum += peer[s][e];
+            const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
+            const bool in = m < p.M && n < p.N;
+            finish(e, sum, in ? a_scale_of(m) : 0.0f, in ? p.w_scale[n] : 0.0f, false, 0.0f);
         }
         if (!e_rest_done) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
@@ -957,7 +965,11 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     // Split-K with a small batch tile: push reduction (needs its receive buffer behind the ring);
     // otherwise the partial tile is parked in the ring itself, which must be large enough for it.
     const bool push = splits > 1 && BN <= 32 && tune().reduce != 1;
-    const int min_stages = push ? 2 : C::MIN_STAGES;
+    // 64- and 128-row batch tiles: push as well, into the peers' idle rings (the partials would not fit behind them)
+    const bool push_ring = splits > 1 && (BN == 64 || BN == 128) && tune().reduce != 1 &&
+                           (EPI == EPI_SCALE || EPI == EPI_RESIDUAL || EPI == EPI_F32);
+    const int ring_recv_bytes = push_ring ? splits * ((BN + splits - 1) / splits) * TILE_W * 4 : 0;
+    const int min_stages = (push || push_ring) ? 2 : C::MIN_STAGES;
     if (stages < min_stages) stages = min_stages;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     // dynamic shared memory this instantiation may ask for: the 227 KB per-CTA limit less its static arrays
@@ -982,7 +994,7 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     p.K = g.K;
     p.kblocks = (g.K + BK - 1) / BK;
     p.stages = stages;
-    p.push = push ? (tune().reduce == 2 ? 2 : 1) : 0;
+    p.push = push ? (tune().reduce == 2 ? 2 : 1) : push_ring ? 3 : 0;
     p.rope = rope ? *rope : RopeKv{};
     p.a16 = g.a16;
     p.amax_part = g.amax_part;
@@ -1000,6 +1012,8 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     cfg.gridDim = dim3((g.N + TILE_W - 1) / TILE_W, splits, (g.M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = C::smem_bytes(stages, push);
+    if (push_ring && stages * C::STAGE_BYTES < ring_recv_bytes)  // a few columns more than the ring holds (S not a power of two)
+        cfg.dynamicSmemBytes += ring_recv_bytes - stages * C::STAGE_BYTES;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
