@@ -118,15 +118,15 @@ struct QuantOut {
 };
 
 // tcgen05 / TMA main kernel (head_dim 128 or 256, up to 8 query heads per KV head)
-template <int HD, int GT, typename OutT>
-int launch_umma(const rvattn::Params& p, cudaStream_t s) {
+template <int HD, int GT, typename OutT, bool CL>
+int launch_umma_form(const rvattn::Params& p, cudaStream_t s) {
     if constexpr (HD == 128 || HD == 256) {
         CUtensorMap mk, mv;
         const long long slots = (long long)p.num_blocks_total * p.block_size;
         if (!rvua::cache_map(&mk, p.k_cache, slots, p.kv_heads, HD, p.block_size) ||
             !rvua::cache_map(&mv, p.v_cache, slots, p.kv_heads, HD, p.block_size))
             return rv_fail(RVLLM_E_LAUNCH, "cuTensorMapEncodeTiled failed for the KV cache");
-        auto kern = rvua::paged_decode_fp8_umma_kernel<HD, GT, OutT>;
+        auto kern = rvua::paged_decode_fp8_umma_kernel<HD, GT, OutT, CL>;
         using C = rvua::Cfg<HD>;
         static RvDeviceOnce smem_once;  // per kernel instantiation and device
         if (rv_allow_smem(smem_once, kern, C::smem_bytes(rvua::MAX_UNITS)))
@@ -144,6 +144,11 @@ int launch_umma(const rvattn::Params& p, cudaStream_t s) {
     } else {
         return rv_fail(RVLLM_E_UNSUPPORTED, "tcgen05 decode attention needs head_dim 128 or 256");
     }
+}
+
+template <int HD, int GT, typename OutT>
+int launch_umma(const rvattn::Params& p, cudaStream_t s) {
+    return p.cluster_combine ? launch_umma_form<HD, GT, OutT, true>(p, s) : launch_umma_form<HD, GT, OutT, false>(p, s);
 }
 
 template <int HD, int GT, typename OutT>

@@ -315,7 +315,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const bool push = S > 1 && p.push != 0;
     // push == 3: the receive buffer is the (by then idle) ring itself — batch tiles of 64 / 128 rows, whose partials
     // would not fit behind it.  The cluster then meets after the main loops instead ("every ring is free").
-    const bool push_ring = push && p.push == 3;
+    const bool push_ring = BN >= 64 && push && p.push == 3;  // (a compile-time "no" for the small tiles)
     if (push && !push_ring) cluster_arrive();  // "this CTA runs": peers wait for it (long since complete) before their first remote store
 
     if (warp == 0) {
@@ -796,16 +796,35 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int e = e_first + j * e_step;
             if (e < BN * TILE_W) finish(e, sums[j], pre_a[j], pre_w[j], true, pre_res[j]);
         }
-        // (The rest one element at a time: this form only serves 256-row tiles and forced comparisons now, and a
-        // grouped loop costs the registers that keep three CTAs of the smaller tiles on an SM.)
-        for (int e = e_first + PRE * e_step; e < BN * TILE_W; e += e_step) {
-            float sum = 0.0f;
+        // The rest in groups of PRE as well: all loads of a group, then its stores.  (A load placed after a
+        // store cannot be moved above it — out and residual may be one buffer — so element-by-element code
+        // pays a full load latency per element.)
+        for (int e0 = e_first + PRE * e_step; e0 < BN * TILE_W; e0 += PRE * e_step) {
+            float g_sum[PRE], g_a[PRE], g_w[PRE], g_res[PRE];
 #pragma unroll
-            for (int s = 0; s < 8; s++)
-                if (s < S) sum += peer[s][e];
-            const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
-            const bool in = m < p.M && n < p.N;
-            finish(e, sum, in ? a_scale_of(m) : 0.0f, in ? p.w_scale[n] : 0.0f, false, 0.0f);
+            for (int j = 0; j < PRE; j++) {
+                const int e = e0 + j * e_step;
+                g_sum[j] = g_a[j] = g_w[j] = g_res[j] = 0.0f;
+                if (e < BN * TILE_W) {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < 8; s++)
+                        if (s < S) sum += peer[s][e];
+                    g_sum[j] = sum;
+                    const int m = m0 + e / TILE_W, n = n0 + e % TILE_W;
+                    if (m < p.M && n < p.N) {
+                        g_a[j] = a_scale_of(m);
+                        g_w[j] = p.w_scale[n];
+                        if (RES)
+                            g_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PRE; j++) {
+                const int e = e0 + j * e_step;
+                if (e < BN * TILE_W) finish(e, g_sum[j], g_a[j], g_w[j], true, g_res[j]);
+            }
         }
         if (!e_rest_done) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");

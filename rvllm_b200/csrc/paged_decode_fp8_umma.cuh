@@ -197,7 +197,9 @@ __device__ __forceinline__ void split3(float x, uint8_t& hi, uint8_t& mid, uint8
     lo = rv::f32_to_e4m3(r);
 }
 
-template <int HD, int GT, typename OutT>
+// CL: the cluster-merged split-KV form (Params::cluster_combine), an instantiation of its own: the plain one keeps
+// its 64 registers — five CTAs of the shallowest ring share an SM (30 warps), which a batch-128 launch counts on.
+template <int HD, int GT, typename OutT, bool CL>
 __global__ void __launch_bounds__(THREADS, 1)
 paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p,
                              int nunits) {
@@ -225,7 +227,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     float* recv = reinterpret_cast<float*>(aux + C::AUX_BYTES);  // cluster-combine form only: [chunk][head][HD + 2]
 
     rv::pdl_launch();
-    if (p.cluster_combine) asm volatile("barrier.cluster.arrive.release;" ::: "memory");  // "this CTA runs"
+    if constexpr (CL) asm volatile("barrier.cluster.arrive.release;" ::: "memory");  // "this CTA runs"
     const int kvh = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.heads / p.kv_heads;
@@ -631,7 +633,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
                         const OutT stored = rv::T16<OutT>::from_f32(v);
                         out[((size_t)b * p.heads + head) * HD + d] = stored;
                         amax = fmaxf(amax, fabsf(rv::T16<OutT>::to_f32(stored)));  // fmaxf drops a NaN, as the quantiser does
-                    } else if (p.cluster_combine) {
+                    } else if (CL) {
                         // staged in this CTA's own slot 0 (for chunk 0 that is its final place); sent to the
                         // chunk-0 CTA further down, once that CTA is known to run
                         float* st = recv + (size_t)k * PSTRIDE;
@@ -660,7 +662,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         }
         tc_fence_before();
     }
-    if (p.cluster_combine) {
+    if constexpr (CL) {
         // Every thread of every CTA of the cluster, active or not, passes these barriers: first "all CTAs of the
         // cluster run" (the arrival was the kernel's first statement; shared memory of a CTA that has not started
         // must not be written), then "the partials are in the chunk-0 CTA's shared memory".
