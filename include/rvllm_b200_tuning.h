@@ -32,6 +32,9 @@ void rvllm_fp8_gemm_tc_tune(int stages, int splits);
  * instead of the cluster barrier (measured within 1 % of form 0; kept as a cross-check).  All forms
  * sum in cluster-rank order, so their results are bitwise equal (tested). */
 void rvllm_fp8_gemm_tc_reduce(int mode);
+/* CTAs a split-K launch aims for (splits = round(target / weight tiles), at most 8, at least 4 K blocks each);
+ * 0 restores the built-in 360.  Process-wide. */
+void rvllm_fp8_gemm_tc_split_target(int ctas);
 
 /* Overrides for tuning runs (0 restores the default): CTAs the grid aims for, the fewest tokens
  * worth a chunk of their own, and the main-kernel variant (1 = both products on the FP32 pipes,

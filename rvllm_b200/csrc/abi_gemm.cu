@@ -279,6 +279,7 @@ int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const 
     return rc;
 }
 
+void rvllm_fp8_gemm_tc_split_target(int ctas) { rvtc::tune().split_target = ctas > 0 ? ctas : 0; }
 void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 || mode == 2 ? mode : 0; }
 
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {

@@ -968,6 +968,7 @@ struct Tune {
     std::atomic<int> stages{0};
     std::atomic<int> splits{0};
     std::atomic<int> reduce{0};  // 1: force the pull form of the split-K reduction; 2: push form with point-to-point mbarriers
+    std::atomic<int> split_target{0};  // CTAs a split launch aims for (0: the built-in 360)
 };
 inline Tune& tune() {
     static Tune t;
@@ -1077,7 +1078,8 @@ inline int pick_splits(int M, int N, int K, int bn) {
         while (s2 > 1 && kblocks / s2 < 4) s2--;
         return s2 < 1 ? 1 : s2;
     }
-    int s = (360 + tiles / 2) / tiles;
+    const int target = tune().split_target.load() > 0 ? tune().split_target.load() : 360;
+    int s = (target + tiles / 2) / tiles;
     if (s > 8) s = 8;
     while (s > 1 && kblocks / s < 4) s--;
     if (s < 1) s = 1;
