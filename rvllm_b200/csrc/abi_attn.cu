@@ -132,11 +132,12 @@ int launch_umma_form(const rvattn::Params& p, cudaStream_t s) {
         if (rv_allow_smem(smem_once, kern, C::smem_bytes(rvua::MAX_UNITS)))
             return rv_fail(RVLLM_E_LAUNCH, "cannot raise dynamic shared memory for decode attention");
         const int ring = g_ring_units.load();
-        int units = ring > 0 ? ring : rvua::pick_units<HD>((long long)p.kv_heads * p.max_chunks * p.batch);
+        // cluster-combine form: the chunks of a (sequence, KV head) are one cluster, the receive area sits behind the rest
+        // (and counts when the ring depth is chosen: a third of the footprint at eight chunks)
+        const size_t recv = p.cluster_combine ? (size_t)C::recv_bytes(p.max_chunks, p.heads / p.kv_heads) : 0;
+        int units = ring > 0 ? ring : rvua::pick_units<HD>((long long)p.kv_heads * p.max_chunks * p.batch, (int)recv);
         if (units < C::MIN_UNITS) units = C::MIN_UNITS;
         if (units > rvua::MAX_UNITS) units = rvua::MAX_UNITS;
-        // cluster-combine form: the chunks of a (sequence, KV head) are one cluster, the receive area sits behind the rest
-        const size_t recv = p.cluster_combine ? (size_t)C::recv_bytes(p.max_chunks, p.heads / p.kv_heads) : 0;
         while (units > C::MIN_UNITS && C::smem_bytes(units) + recv > (size_t)C::smem_bytes(rvua::MAX_UNITS)) units--;
         rv_launch(kern, dim3(p.kv_heads, p.max_chunks, p.batch), dim3(rvua::THREADS), (size_t)C::smem_bytes(units) + recv, s,
                   dim3(1, p.cluster_combine ? p.max_chunks : 1, 1), mk, mv, p, units);

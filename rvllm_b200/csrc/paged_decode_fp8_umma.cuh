@@ -783,7 +783,7 @@ inline bool supports(const Params& p, int head_dim) {
 // deep one lets a CTA run further ahead of its softmax.  The choice minimises
 // ceil(CTAs / resident CTAs) x (relative time of one wave), with the per-wave weights measured on the
 // decode shapes (batch 8 / 32 / 128, contexts 576 to 4096).
-template <int HD> inline int pick_units(long long ctas) {
+template <int HD> inline int pick_units(long long ctas, int extra_bytes = 0) {
     using C = Cfg<HD>;
     struct Cand {
         int units;
@@ -796,7 +796,7 @@ template <int HD> inline int pick_units(long long ctas) {
     int best = cand[0].units;
     double best_cost = 1e300;
     for (int i = 0; i < n; i++) {
-        const long long slots = ((228 * 1024) / (C::smem_bytes(cand[i].units) + 1024)) * 148ll;
+        const long long slots = ((228 * 1024) / (C::smem_bytes(cand[i].units) + extra_bytes + 1024)) * 148ll;
         const double cost = (double)((ctas + slots - 1) / slots) * cand[i].wave;
         if (cost < best_cost) {
             best_cost = cost;
