@@ -47,6 +47,12 @@ void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant)
  * out of its own shared memory — no workspace traffic, no combine launch; 0 = partials through the workspace and the
  * combine kernel, as the other variants do.  Process-wide. */
 void rvllm_paged_decode_cluster_combine(int enabled);
+/* 1: the tcgen05 attention kernel reads context lengths and block tables, and fetches every K / V tile but the last of a
+ * sequence, without waiting for the kernel before it in the stream (programmatic dependent launch); only Q, the last
+ * tile and the scales wait.  For callers whose context lengths and block tables were written well before that kernel
+ * started (a decode step writes them once, at its start) and whose preceding kernel writes nothing but the newest
+ * token's rows.  0 = everything waits (default).  Process-wide. */
+void rvllm_paged_decode_early_meta(int enabled);
 /* The cluster-merged form's own plan: CTAs aimed for (chunks per sequence = ceil(target / (batch * KV heads)), at most
  * 8) and the smallest chunk in tokens; 0 restores the defaults.  Process-wide. */
 void rvllm_paged_decode_cluster_tune(int target_ctas, int min_chunk_tokens);

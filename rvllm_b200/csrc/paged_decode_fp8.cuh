@@ -76,6 +76,9 @@ struct Params {
     int min_chunk_tokens;  // a sequence is cut into ceil(attended / this) chunks, at most max_chunks
     int force_partial;     // always leave partials in the workspace (the fused combine+quant pass reads them)
     float* amax_out;       // tcgen05 kernel, 16-bit output: max |rounded output| per (sequence, kv_head), or null
+    int early_meta;        // tcgen05 kernel: context lengths and block tables were written before the preceding kernel
+                           // started (only the newest token's K/V, its scales and Q come from it): geometry, table
+                           // look-ups and the loads of every tile but the last do not wait for that kernel
     int cluster_combine;   // tcgen05 kernel: the chunks of a (sequence, kv_head) are one thread-block cluster and the
                            // chunk-0 CTA merges their partials out of its own shared memory (no workspace, no combine launch)
 };

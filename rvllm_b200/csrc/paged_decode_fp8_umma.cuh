@@ -252,7 +252,8 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     for (int i = tid; i < (C::P_BYTES + C::Q_BYTES) / 16; i += THREADS)  // zero P and Q tiles (padding rows stay zero)
         reinterpret_cast<uint4*>(p_tile)[i] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();  // the zeroes must be visible to the tensor core's (async-proxy) reads
-    rv::pdl_wait();
+    const bool early = p.early_meta != 0;
+    if (!early) rv::pdl_wait();
 
     // ---- sequence geometry (same rules as the other variants) ----
     const int ctx = p.context_lens[b];
@@ -299,6 +300,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     const int nh = group < GT ? group : GT;  // query heads of this KV head (the launcher guarantees group <= GT)
     if (warp != 0) {
         // The producer warp goes straight to its loads; the other five warps stage Q meanwhile.
+        if (early) rv::pdl_wait();  // Q, and the newest token's scales, come from the preceding kernel
         if (active) {
             // Q codes of the KV head's query heads -> B operand panels (K-major, swizzled by hand)
             for (int i = tid - 32; i < nh * (HD / 16); i += THREADS - 32) {
@@ -332,6 +334,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
             bool alive = true, bad_page = false;
             int slot = 0, use = 0;  // ring position of the next unit (kept incrementally: NUNITS is a run-time value)
             for (int i = 0; i < ntiles && alive; i++) {
+                if (early && i == ntiles - 1) rv::pdl_wait();  // the newest token's K / V rows are in the last tile
                 const int tok_tile = tile0 + i * TOK;
                 // pages of the tile that hold attended tokens; the rest are not fetched (their rows of the
                 // unit keep stale bytes: masked in the scores, zeroed by the softmax warps for the V panels)
