@@ -298,9 +298,31 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // 16-bit activation form: the converting warps' first K block of values, fetched one block ahead of its use
+    constexpr int CPT = (BN * 8 + 127) / 128;  // 16-byte output chunks per thread and K block (1 or 2)
+    uint4 nx[A16 ? CPT : 1][2];
+    auto fetch_a16 = [&](int i) {
+        if constexpr (A16) {
+            const int t = (int)threadIdx.x - EPI_WARP0 * 32;
+            const OutT* a16 = reinterpret_cast<const OutT*>(p.a16);
+#pragma unroll
+            for (int q = 0; q < CPT; q++) {  // this thread's chunks: row r, 16-column group cc — the same for every K block
+                const int c = t + q * 128, r = c >> 3, cc = c & 7;
+                const int m = m0 + r, k0 = (kb_lo + i) * BK + cc * 16;
+                nx[q][0] = nx[q][1] = make_uint4(0, 0, 0, 0);
+                if (c < BN * 8 && i < nkb && m < p.M && k0 < p.K) {
+                    const uint4* src = reinterpret_cast<const uint4*>(a16 + (size_t)m * p.K + k0);
+                    nx[q][0] = rv::ldg128(src);
+                    nx[q][1] = rv::ldg128(src + 1);
+                }
+            }
+        }
+    };
     if (A16) {
-        // per-row activation scale from the partial maxima the producer of the activations left behind
+        // per-row activation scale from the partial maxima the producer of the activations left behind; the
+        // converting warps' first loads go out beside those of the maxima, not after them
         rv::pdl_wait();
+        if (warp >= EPI_WARP0) fetch_a16(0);
         if ((int)threadIdx.x < BN) {
             const int m = m0 + (int)threadIdx.x;
             float amax = 0.0f;
@@ -365,24 +387,6 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // swizzled FP8 A tiles themselves (the per-token quantiser's arithmetic: scale = max(absmax / 448,
         // 1e-12), code = e4m3(x * (1 / scale))), so no separate quantiser launch and no FP8 copy in HBM.
         const int t = (int)threadIdx.x - EPI_WARP0 * 32;
-        const OutT* a16 = reinterpret_cast<const OutT*>(p.a16);
-        constexpr int CPT = (BN * 8 + 127) / 128;  // 16-byte output chunks per thread and K block (1 or 2)
-        // this thread's chunks: row r, 16-column group cc — the same for every K block
-        uint4 nx[CPT][2];                          // the next K block's 16-bit values, fetched one block ahead
-        auto fetch = [&](int i) {
-#pragma unroll
-            for (int q = 0; q < CPT; q++) {
-                const int c = t + q * 128, r = c >> 3, cc = c & 7;
-                const int m = m0 + r, k0 = (kb_lo + i) * BK + cc * 16;
-                nx[q][0] = nx[q][1] = make_uint4(0, 0, 0, 0);
-                if (c < BN * 8 && i < nkb && m < p.M && k0 < p.K) {
-                    const uint4* src = reinterpret_cast<const uint4*>(a16 + (size_t)m * p.K + k0);
-                    nx[q][0] = rv::ldg128(src);
-                    nx[q][1] = rv::ldg128(src + 1);
-                }
-            }
-        };
-        fetch(0);
         bool alive = true;
         for (int i = 0; i < nkb && alive; i++) {
             uint4 cur[CPT][2];
@@ -391,7 +395,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 cur[q][0] = nx[q][0];
                 cur[q][1] = nx[q][1];
             }
-            fetch(i + 1);
+            fetch_a16(i + 1);
             const int s = i % STAGES;
             if (i >= STAGES) alive = mbar_wait(empty + s, ((uint32_t)(i / STAGES) & 1u) ^ 1u, 5);
             if (!alive) break;
