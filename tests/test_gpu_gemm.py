@@ -444,3 +444,35 @@ def test_lm_head_argmax_epilogue_equals_logits_then_argmax(orc, M, softcap):
         assert got[2].item() == -1
     assert L.rvllm_fp8_gemm_lm_head_argmax(got.data_ptr(), A.data_ptr(), W.data_ptr(), AS.data_ptr(), WS.data_ptr(), M, V, K,
                                            softcap, ws.data_ptr(), 16, _lib.current_stream()) == _lib.E_WORKSPACE
+
+
+def test_two_devices_in_one_process(orc):
+    """cudaFuncSetAttribute belongs to a device, not to the process: the tcgen05 GEMM (split-K push form, > 48 KB of
+    dynamic shared memory) and the tcgen05 attention launched on device 0 and then on device 1 of the same process,
+    local buffers only, must give the same bytes.  Needs two GPUs; skipped otherwise."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in one process")
+    from rvllm_b200 import gemm
+    from rvllm_b200.attention import PagedDecodeFp8Launcher, PagedDecodeParams
+    M, N, K = 32, 5376, 4096
+    a, a_s, w, w_s, cols, want = case(orc, M, N, K, seed=12, n_cols=64)
+    c = datagen.attention_case(orc, 4, 32, 16, 128, 16, [600, 17, 128, 300], seed=12)
+    outs = []
+    try:
+        for dev in (0, 1):
+            torch.cuda.set_device(dev)
+            d = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda(dev)
+            out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+            gemm.fp8_gemm_channelscale(out, d(a), d(w), d(a_s), d(w_s), impl=TC)
+            p = PagedDecodeParams(4, 32, 16, 128, 16, c["max_blocks"], c["num_blocks"], 128 ** -0.5, -1)
+            ws = torch.empty(max(p.workspace_bytes(), 16), dtype=torch.uint8, device="cuda")
+            o = torch.empty((4, 32, 128), dtype=torch.float16, device="cuda")
+            PagedDecodeFp8Launcher(p).launch(d(c["q"]), d(c["k"]), d(c["v"]), o, d(c["tables"]), d(c["ctx"]), workspace=ws,
+                                             k_scale_cache=d(c["ks"]), v_scale_cache=d(c["vs"]), q_scale_cache=d(c["qs"]))
+            torch.cuda.synchronize()
+            assert gemm.tc_status() == 0
+            outs.append((out.float().cpu().numpy(), o.float().cpu().numpy()))
+    finally:
+        torch.cuda.set_device(0)
+    close(outs[0][0][:, cols], want)
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
