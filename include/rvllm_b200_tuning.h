@@ -47,12 +47,16 @@ void rvllm_paged_decode_tune(int target_ctas, int min_chunk_tokens, int variant)
  * out of its own shared memory — no workspace traffic, no combine launch; 0 = partials through the workspace and the
  * combine kernel, as the other variants do.  Process-wide. */
 void rvllm_paged_decode_cluster_combine(int enabled);
-/* 1: the tcgen05 attention kernel reads context lengths and block tables, and fetches every K / V tile but the last of a
- * sequence, without waiting for the kernel before it in the stream (programmatic dependent launch); only Q, the last
- * tile and the scales wait.  For callers whose context lengths and block tables were written well before that kernel
- * started (a decode step writes them once, at its start) and whose preceding kernel writes nothing but the newest
- * token's rows.  0 = everything waits (default).  Process-wide. */
-void rvllm_paged_decode_early_meta(int enabled);
+/* Early metadata: the tcgen05 attention kernel reads context lengths and block tables, and fetches every K / V tile but
+ * the last of a sequence, without waiting for the kernel before it in the stream (programmatic dependent launch); only
+ * Q, the last tile and the scales wait.  Legal only for a caller whose context lengths, block tables and older cache
+ * rows were complete before that kernel could start — the decode stack's graph qualifies: its bookkeeping for a step is
+ * written by the last kernel of the step before, and consecutive graph launches do not overlap.
+ * `rvllm_paged_decode_hint_early_meta()`: one-shot, calling thread only — the next decode-attention launch made from
+ * this thread runs in that mode.  `rvllm_paged_decode_early_meta(mode)`: process-wide override, 0 = as hinted
+ * (default), 1 = always, -1 = never.  Same bytes either way. */
+void rvllm_paged_decode_hint_early_meta(void);
+void rvllm_paged_decode_early_meta(int mode);
 /* The cluster-merged form's own plan: CTAs aimed for (chunks per sequence = ceil(target / (batch * KV heads)), at most
  * 8) and the smallest chunk in tokens; 0 restores the defaults.  Process-wide. */
 void rvllm_paged_decode_cluster_tune(int target_ctas, int min_chunk_tokens);

@@ -46,6 +46,7 @@ SIGNATURES = {
     "rvllm_paged_decode_cluster_combine": (None, [_i32]),
     "rvllm_paged_decode_cluster_tune": (None, [_i32, _i32]),
     "rvllm_paged_decode_early_meta": (None, [_i32]),
+    "rvllm_paged_decode_hint_early_meta": (None, []),
     "rvllm_fused_rmsnorm_fp8_quant_validate": (_i32, [_u32, _u32, _f32]),
     "rvllm_fused_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _i32, _vp]),
     "rvllm_fused_add_rmsnorm_fp8_quant_launch": (_i32, [_u32, _u32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp]),

@@ -17,7 +17,8 @@
 static std::atomic<int> g_target_ctas{rvattn::TARGET_CTAS};
 static std::atomic<int> g_min_chunk_tokens{rvattn::MIN_CHUNK_TOKENS};
 static std::atomic<int> g_cluster_combine{1};
-static std::atomic<int> g_early_meta{0};
+static std::atomic<int> g_early_meta{0};       // 0: when the caller hinted it (below), 1: always, -1: never
+static thread_local int t_early_meta_once = 0;  // one-shot hint of the calling thread, taken by its next launch
 static std::atomic<int> g_cluster_min_tokens{rvua::TOK};  // smallest chunk of the cluster-merged split-KV form
 // CTAs the cluster-merged form aims for: chunks cost it neither workspace traffic nor a second launch
 constexpr int CLUSTER_TARGET_CTAS = rvattn::TARGET_CTAS;
@@ -88,7 +89,8 @@ int rvllm_paged_decode_kernel_for(int num_heads, int num_kv_heads, int head_dim,
     return 2;
 }
 
-void rvllm_paged_decode_early_meta(int enabled) { g_early_meta = enabled != 0; }
+void rvllm_paged_decode_early_meta(int mode) { g_early_meta = mode > 0 ? 1 : (mode < 0 ? -1 : 0); }
+void rvllm_paged_decode_hint_early_meta(void) { t_early_meta_once = 1; }
 void rvllm_paged_decode_cluster_combine(int enabled) { g_cluster_combine = enabled != 0; }
 void rvllm_paged_decode_cluster_tune(int target_ctas, int min_chunk_tokens) {
     g_cluster_target = target_ctas > 0 ? target_ctas : CLUSTER_TARGET_CTAS;
@@ -297,7 +299,11 @@ static int decode_core(const QuantOut& qo, const void* q_fp8, const void* k_cach
     p.force_partial = qo.fp8 ? 1 : 0;
     p.amax_out = qo.amax;
     p.cluster_combine = 0;
-    p.early_meta = g_early_meta.load();
+    {
+        const int mode = g_early_meta.load(), hinted = t_early_meta_once;
+        t_early_meta_once = 0;
+        p.early_meta = mode > 0 || (mode == 0 && hinted);
+    }
     const bool umma = (g_variant == 4 || g_variant == 0) && rvua::supports(p, head_dim);
     const int cchunks = rvattn::pick_max_chunks(batch_size, num_kv_heads, g_cluster_target);
     if (umma && cchunks > 1 && !qo.fp8 && g_cluster_combine.load() != 0) {

@@ -38,29 +38,39 @@ __global__ void fill_tables_kernel(int* tables, int n, unsigned long long mul, u
         tables[i] = (int)(((unsigned long long)i * mul + add) % (unsigned long long)n);
 }
 
-// Per-step bookkeeping, on the device so that a graph replay needs no host input:
-// slot of the token being written this step, for the global and the ring (sliding) layout.
-__global__ void prepare_step_kernel(const int* __restrict__ positions, const int* __restrict__ tables_global,
-                                    const int* __restrict__ tables_sliding, int* __restrict__ slots_global,
-                                    int* __restrict__ slots_sliding, int* __restrict__ ctx_lens, int batch,
-                                    int block_size, int mb_global, int mb_sliding) {
-    rv::pdl_launch();
-    rv::pdl_wait();
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= batch) return;
-    const int pos = positions[b];
+// Per-step bookkeeping, on the device so that a graph replay needs no host input: slot of the token written at
+// position `pos`, for the global and the ring (sliding) layout, and the context length that includes it.
+__device__ __forceinline__ void place_token(int b, int pos, const int* __restrict__ tables_global,
+                                            const int* __restrict__ tables_sliding, int* __restrict__ slots_global,
+                                            int* __restrict__ slots_sliding, int* __restrict__ ctx_lens, int block_size,
+                                            int mb_global, int mb_sliding) {
     const int page = pos / block_size, off = pos % block_size;
     const int blk = page < mb_global ? tables_global[b * mb_global + page] : -1;  // -1: no block dealt to this page
     slots_global[b] = blk >= 0 ? blk * block_size + off : -1;
     slots_sliding[b] = mb_sliding > 0 ? tables_sliding[b * mb_sliding + page % mb_sliding] * block_size + off : -1;
     ctx_lens[b] = pos + 1;
 }
+// After a reset or a seeding: the bookkeeping of the first step.  Every later step finds what its predecessor's
+// advance_kernel left, so that inside a step nothing writes slots, context lengths or block tables: kernels of the step
+// may read them without waiting for the kernel before them.
+__global__ void prepare_step_kernel(const int* __restrict__ positions, const int* __restrict__ tables_global,
+                                    const int* __restrict__ tables_sliding, int* __restrict__ slots_global,
+                                    int* __restrict__ slots_sliding, int* __restrict__ ctx_lens, int batch,
+                                    int block_size, int mb_global, int mb_sliding) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    place_token(b, positions[b], tables_global, tables_sliding, slots_global, slots_sliding, ctx_lens, block_size, mb_global,
+                mb_sliding);
+}
 
 // After argmax: record the emitted token, choose the next input token (prompt while it lasts,
-// then greedy feedback), advance the position and the step counter.  One block.
+// then greedy feedback), advance the position and the step counter, and place the next step's token.  One block.
 __global__ void advance_kernel(int* __restrict__ tokens, const int* __restrict__ next, int* __restrict__ positions,
                                const int* __restrict__ prompt, int prompt_len, int* __restrict__ history,
-                               int* __restrict__ step_counter, int max_steps, int batch) {
+                               int* __restrict__ step_counter, int max_steps, int batch,
+                               const int* __restrict__ tables_global, const int* __restrict__ tables_sliding,
+                               int* __restrict__ slots_global, int* __restrict__ slots_sliding, int* __restrict__ ctx_lens,
+                               int block_size, int mb_global, int mb_sliding) {
     rv::pdl_launch();
     rv::pdl_wait();
     const int step = *step_counter;
@@ -70,6 +80,8 @@ __global__ void advance_kernel(int* __restrict__ tokens, const int* __restrict__
         if (step < max_steps) history[(size_t)step * batch + b] = emitted;
         tokens[b] = (pos + 1 < prompt_len) ? prompt[(size_t)b * prompt_len + pos + 1] : emitted;
         positions[b] = pos + 1;
+        place_token(b, pos + 1, tables_global, tables_sliding, slots_global, slots_sliding, ctx_lens, block_size, mb_global,
+                    mb_sliding);
     }
     __syncthreads();
     if (threadIdx.x == 0) *step_counter = step + 1;
@@ -111,6 +123,7 @@ struct rvllm_stack {
     std::vector<LayerState> ls;
     cudaStream_t stream = nullptr;
     int skip_mask = 0;  // timing aid: launches left out of the step (rvllm_stack_debug_skip at creation time)
+    bool capturing = false;  // enqueue_step is recording the graph (its kernels then run behind a complete predecessor step)
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int launches = 0;
@@ -281,6 +294,15 @@ namespace {
 std::atomic<int> g_skip_mask{0};
 
 // Enqueues one decode step on the stack's stream; counts launches when asked.
+// The bookkeeping of the first step after the positions were set from the host (plain launch, stream order).
+int place_first_tokens(rvllm_stack* s) {
+    const rvllm_stack_config& c = s->cfg;
+    prepare_step_kernel<<<(c.batch + 127) / 128, 128, 0, s->stream>>>(s->positions, s->tables_global, s->tables_sliding,
+                                                                      s->slots_global, s->slots_sliding, s->ctx_lens, c.batch,
+                                                                      c.block_size, s->mb_global, s->mb_sliding);
+    return rv_launched("prepare_step");
+}
+
 int enqueue_step(rvllm_stack* s, int* launches) {
     const int skip = s->skip_mask;
     auto on = [skip](int bit) { return (skip & bit) == 0; };
@@ -288,11 +310,8 @@ int enqueue_step(rvllm_stack* s, int* launches) {
     const int B = c.batch, H = c.hidden;
     void* st = (void*)s->stream;
     int n = 0;
-    rv_launch(prepare_step_kernel, dim3((B + 127) / 128), dim3(128), 0, s->stream, dim3(1, 1, 1), s->positions, s->tables_global, s->tables_sliding,
-                                                                s->slots_global, s->slots_sliding, s->ctx_lens, B,
-                                                                c.block_size, s->mb_global, s->mb_sliding);
-    RV_TRY(rv_launched("prepare_step"));
-    n++;
+    // (slots, context lengths and block tables of this step were left by the previous step's advance_kernel, or by
+    // reset / seeding: nothing below writes them)
     RV_TRY(rvllm_embedding_gather_launch(s->residual, s->head.embedding, s->tokens, B, H, c.vocab, st));
     n++;
     // x_fp8 / x_scale hold the current layer's attention-block input (RMSNorm + quant of the residual) when the
@@ -347,7 +366,11 @@ int enqueue_step(rvllm_stack* s, int* launches) {
             have16 = try16;  // (left out: timing aid)
         } else {
             // (a) first: single chunk, or split-KV merged inside a thread-block cluster (small batches)
+            // In the graph the step's bookkeeping (context lengths, slots) and every older cache row were complete
+            // before the step began — they come from the previous graph launch or from reset / seeding — so attention
+            // need not wait for the QKV kernel before it reads them.  Eager launches chain across steps: no hint.
             int a16 = RVLLM_E_UNSUPPORTED;
+            if (s->capturing) rvllm_paged_decode_hint_early_meta();
             if (try16)
                 a16 = rvllm_paged_decode_fp8_amax(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, s->attn_amax,
                                                   tables, s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale,
@@ -360,6 +383,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
             } else if (a16 != RVLLM_E_UNSUPPORTED) {
                 RV_TRY(a16);
             } else if (rvllm_paged_decode_max_chunks(B, c.kv_heads) > 1) {
+                if (s->capturing) rvllm_paged_decode_hint_early_meta();
                 RV_TRY(rvllm_paged_decode_fp8_quant(s->q_fp8, L.k_cache, L.v_cache, s->attn_fp8, s->attn_scale, c.dtype, tables,
                                                     s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
                                                     s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads,
@@ -367,6 +391,7 @@ int enqueue_step(rvllm_stack* s, int* launches) {
                                                     L.window_left, st));
                 n += 2;
             } else {
+                if (s->capturing) rvllm_paged_decode_hint_early_meta();
                 RV_TRY(rvllm_paged_decode_fp8(s->q_fp8, L.k_cache, L.v_cache, s->attn_out, c.dtype, tables,
                                               s->ctx_lens, s->attn_ws, s->attn_ws_bytes, L.k_scale, L.v_scale,
                                               s->q_scale, nullptr, nullptr, nullptr, sm_scale, B, c.heads, c.kv_heads,
@@ -442,7 +467,9 @@ int enqueue_step(rvllm_stack* s, int* launches) {
         n++;
     }
     rv_launch(advance_kernel, dim3(1), dim3(256), 0, s->stream, dim3(1, 1, 1), s->tokens, s->next_tokens, s->positions, s->prompt, c.prompt_len,
-                                             s->history, s->step_counter, c.max_steps, B);
+                                             s->history, s->step_counter, c.max_steps, B, (const int*)s->tables_global,
+                                             (const int*)s->tables_sliding, s->slots_global, s->slots_sliding, s->ctx_lens,
+                                             c.block_size, s->mb_global, s->mb_sliding);
     RV_TRY(rv_launched("advance"));
     n += 1;
     if (launches) *launches = n;
@@ -582,7 +609,9 @@ int rvllm_stack_create(rvllm_stack** out, const rvllm_stack_config* cfg, const r
     if (rc == RVLLM_OK) rc = cuda_ok(cudaStreamSynchronize(s->stream), "eager warm-up step");
     if (rc == RVLLM_OK) rc = cuda_ok(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
     if (rc == RVLLM_OK) {
+        s->capturing = true;
         int rc2 = enqueue_step(s, nullptr);
+        s->capturing = false;
         cudaError_t e = cudaStreamEndCapture(s->stream, &s->graph);
         rc = rc2 != RVLLM_OK ? rc2 : cuda_ok(e, "end capture");
     }
@@ -627,6 +656,7 @@ int rvllm_stack_reset(rvllm_stack* s, const int32_t* prompt_tokens) {
     }
     s->steps_done = 0;
     s->start_pos = 0;
+    RV_TRY(place_first_tokens(s));
     return cuda_ok(cudaStreamSynchronize(s->stream), "reset");
 }
 
@@ -661,6 +691,7 @@ static int seed_common(rvllm_stack* s, const int32_t* contexts, int uniform) {
     RV_TRY(rv_launched("seed context"));
     RV_TRY(cuda_ok(cudaMemcpyAsync(s->positions, pos.data(), sizeof(int) * c.batch, cudaMemcpyHostToDevice, s->stream),
                    "upload positions"));
+    RV_TRY(place_first_tokens(s));
     RV_TRY(cuda_ok(cudaStreamSynchronize(s->stream), "seed context"));
     s->start_pos = most;
     return RVLLM_OK;
