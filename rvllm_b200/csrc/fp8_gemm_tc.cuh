@@ -449,6 +449,34 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     pre_res[j] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(p.residual)[(size_t)m * p.N + n]);
             }
         }
+        // Fused QKV epilogue: everything its first two rounds of tokens need besides the sums — activation scale,
+        // position, cache slot, and (dependent on the position) the cos / sin pair — is fetched here, while the
+        // main loop still runs; fetched inside the rounds, these are three L2 round trips in a row per round.
+        constexpr int QPRE = 2;
+        float q_as[QPRE], q_c[QPRE], q_s[QPRE], q_wlo = 0.0f, q_whi = 0.0f;
+        int q_pos[QPRE], q_slot[QPRE];
+        if constexpr (EPI == EPI_QKV_ROPE) {
+            const RopeKv& rk = p.rope;
+            const int grp = (int)threadIdx.x >> 6, d = (int)threadIdx.x & 63;
+            const int kind = (int)blockIdx.x < rk.heads ? 0 : ((int)blockIdx.x < rk.heads + rk.kv_heads ? 1 : 2);
+            q_wlo = p.w_scale[n0 + d];
+            q_whi = p.w_scale[n0 + d + 64];
+#pragma unroll
+            for (int it = 0; it < QPRE; it++) {
+                const int lc = it * 3 + grp, col = lc * S + split, m = m0 + col;
+                q_as[it] = q_c[it] = q_s[it] = 0.0f;
+                q_pos[it] = q_slot[it] = -1;
+                if (lc < LC && col < BN && m < p.M) {
+                    q_as[it] = a_scale_of(m);
+                    q_pos[it] = rk.positions[m];
+                    if (kind != 0) q_slot[it] = rk.slot_mapping[m];
+                    if (kind != 2 && q_pos[it] >= 0 && q_pos[it] < rk.max_positions) {
+                        q_c[it] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.cos_t)[(size_t)q_pos[it] * 64 + d]);
+                        q_s[it] = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.sin_t)[(size_t)q_pos[it] * 64 + d]);
+                    }
+                }
+            }
+        }
         bool ready = true;
         if (push_ring) {
             // own MMAs complete = every load into this CTA's ring has landed and been read: the ring is free;
@@ -510,11 +538,12 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int kind = tile < rk.heads ? 0 : (tile < rk.heads + rk.kv_heads ? 1 : 2);
             const int head = kind == 0 ? tile : (kind == 1 ? tile - rk.heads : tile - rk.heads - rk.kv_heads);
             const int grp = (int)threadIdx.x >> 6, d = (int)threadIdx.x & 63;
-            const float ws_lo = p.w_scale[n0 + d], ws_hi = p.w_scale[n0 + d + 64];
+            const float ws_lo = q_wlo, ws_hi = q_whi;
             for (int lc0 = 0; lc0 < LC; lc0 += 3) {            // uniform trip count: the barriers below are block-wide
                 const int lc = lc0 + grp;
                 const int col = lc * S + split, m = m0 + col;
                 const bool live = lc < LC && col < BN && m < p.M;
+                const int it = lc0 / 3;                         // rounds 0 and 1 were fetched ahead
                 float lo = 0.0f, hi = 0.0f;
                 int pos = -1;
                 if (live) {
@@ -525,15 +554,21 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             sum_lo += recv[(size_t)(sp * LC + lc) * TILE_W + d];
                             sum_hi += recv[(size_t)(sp * LC + lc) * TILE_W + d + 64];
                         }
-                    const float as = a_scale_of(m);
+                    const float as = it < QPRE ? q_as[it < QPRE ? it : 0] : a_scale_of(m);
                     const float a = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32_sat(as * (ws_lo * sum_lo)));
                     const float b = rv::T16<OutT>::to_f32(rv::T16<OutT>::from_f32_sat(as * (ws_hi * sum_hi)));
-                    pos = rk.positions[m];
+                    pos = it < QPRE ? q_pos[it < QPRE ? it : 0] : rk.positions[m];
                     lo = a;
                     hi = b;
                     if (kind != 2 && pos >= 0 && pos < rk.max_positions) {
-                        const float c = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.cos_t)[(size_t)pos * 64 + d]);
-                        const float sn = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.sin_t)[(size_t)pos * 64 + d]);
+                        float c, sn;
+                        if (it < QPRE) {
+                            c = q_c[it < QPRE ? it : 0];
+                            sn = q_s[it < QPRE ? it : 0];
+                        } else {
+                            c = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.cos_t)[(size_t)pos * 64 + d]);
+                            sn = rv::T16<OutT>::to_f32(reinterpret_cast<const OutT*>(rk.sin_t)[(size_t)pos * 64 + d]);
+                        }
                         lo = a * c - b * sn;
                         hi = a * sn + b * c;
                     }
@@ -554,7 +589,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         o[d + 64] = rv::f32_to_e4m3(hi * inv);
                         if (d == 0) rk.q_scale[(size_t)m * rk.heads + head] = sc;
                     } else {
-                        const int slot = rk.slot_mapping[m];
+                        const int slot = it < QPRE ? q_slot[it < QPRE ? it : 0] : rk.slot_mapping[m];
                         if (slot >= 0 && slot < rk.num_cache_slots) {
                             const size_t sidx = (size_t)slot * rk.kv_heads + head;
                             uint8_t* o = (kind == 1 ? rk.k_cache : rk.v_cache) + sidx * TILE_W;

@@ -27,7 +27,6 @@ __device__ __forceinline__ void rmsnorm_quant_row(uint8_t* __restrict__ out, flo
                                                   float eps, int hidden) {
     __shared__ __align__(16) T srow[STAGE_ELEMS];
     rv::pdl_launch();
-    rv::pdl_wait();
     __shared__ float red[33];
     const int row = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const size_t base = (size_t)row * hidden;
@@ -36,6 +35,14 @@ __device__ __forceinline__ void rmsnorm_quant_row(uint8_t* __restrict__ out, flo
                         (residual == nullptr || (((reinterpret_cast<uintptr_t>(residual + base) |
                                                    reinterpret_cast<uintptr_t>(residual_out + base)) & 15) == 0));
     const bool staged = hidden <= STAGE_ELEMS && vec_ok;
+    // Rows of at most 8 * blockDim values (every decode shape): a thread's one vector of the row and
+    // of gamma stays in registers across the absmax and the encode pass.  gamma is a weight: its vector is
+    // fetched before the wait for the kernel ahead in the stream (under programmatic dependent launch; a
+    // plain launch starts behind that kernel anyway), not behind the sum-of-squares reduction.
+    const bool one_vec = vec_ok && (hidden >> 3) <= nt && ((reinterpret_cast<uintptr_t>(out + base) & 7) == 0);
+    uint4 keep_x = make_uint4(0, 0, 0, 0), keep_g = make_uint4(0, 0, 0, 0);
+    if (one_vec && tid < (hidden >> 3)) keep_g = rv::ldg128(reinterpret_cast<const uint4*>(gamma) + tid);
+    rv::pdl_wait();
 
     float ss = 0.0f;
     if (residual != nullptr) {
@@ -69,14 +76,9 @@ __device__ __forceinline__ void rmsnorm_quant_row(uint8_t* __restrict__ out, flo
     const T* src = staged ? srow : (residual != nullptr ? residual_out + base : x);
 
     float amax = 0.0f;
-    // Rows of at most 8 * blockDim values (every decode shape): a thread's one vector of the row and
-    // of gamma stays in registers across the absmax and the encode pass.
-    const bool one_vec = vec_ok && (hidden >> 3) <= nt && ((reinterpret_cast<uintptr_t>(out + base) & 7) == 0);
-    uint4 keep_x = make_uint4(0, 0, 0, 0), keep_g = make_uint4(0, 0, 0, 0);
     if (one_vec) {
         if (tid < (hidden >> 3)) {
             keep_x = reinterpret_cast<const uint4*>(src)[tid];
-            keep_g = rv::ldg128(reinterpret_cast<const uint4*>(gamma) + tid);
             const uint32_t* xp = &keep_x.x;
             const uint32_t* gp = &keep_g.x;
 #pragma unroll
