@@ -35,6 +35,8 @@ void rvllm_fp8_gemm_tc_reduce(int mode);
 /* CTAs a split-K launch aims for (splits = round(target / weight tiles), at most 8, at least 4 K blocks each);
  * 0 restores the built-in 360.  Process-wide. */
 void rvllm_fp8_gemm_tc_split_target(int ctas);
+/* Split-K factor of one weight shape [N, K] (batch tiles up to 128 rows), four slots; splits 0 clears the slot. */
+void rvllm_fp8_gemm_tc_split_for(int slot, int N, int K, int splits);
 
 /* Overrides for tuning runs (0 restores the default): CTAs the grid aims for, the fewest tokens
  * worth a chunk of their own, and the main-kernel variant (1 = both products on the FP32 pipes,

@@ -279,6 +279,11 @@ int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const 
     return rc;
 }
 
+void rvllm_fp8_gemm_tc_split_for(int slot, int N, int K, int splits) {
+    if (slot < 0 || slot >= 4) return;
+    rvtc::tune().split_for[slot] = (splits >= 1 && splits <= 8 && N > 0 && K > 0)
+                                       ? (((long long)N << 40) | ((long long)K << 8) | (long long)splits) : 0ll;
+}
 void rvllm_fp8_gemm_tc_split_target(int ctas) { rvtc::tune().split_target = ctas > 0 ? ctas : 0; }
 void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 || mode == 2 ? mode : 0; }
 

@@ -1008,6 +1008,7 @@ struct Tune {
     std::atomic<int> splits{0};
     std::atomic<int> reduce{0};  // 1: force the pull form of the split-K reduction; 2: push form with point-to-point mbarriers
     std::atomic<int> split_target{0};  // CTAs a split launch aims for (0: the built-in 360)
+    std::atomic<long long> split_for[4] = {};  // per-shape overrides: (N << 40) | (K << 8) | splits, 0 = unused
 };
 inline Tune& tune() {
     static Tune t;
@@ -1116,6 +1117,10 @@ inline int pick_splits(int M, int N, int K, int bn) {
         if (s2 > 8) s2 = 8;
         while (s2 > 1 && kblocks / s2 < 4) s2--;
         return s2 < 1 ? 1 : s2;
+    }
+    for (int i = 0; i < 4; i++) {
+        const long long e = tune().split_for[i].load();
+        if (e != 0 && (e >> 40) == N && ((e >> 8) & 0xffffffffll) == K && bn <= 128) return (int)(e & 0xff);
     }
     const int target = tune().split_target.load() > 0 ? tune().split_target.load() : 360;
     int s = (target + tiles / 2) / tiles;
