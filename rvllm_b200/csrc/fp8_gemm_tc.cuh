@@ -532,7 +532,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // absmax, quantise, and write Q / the paged K or V cache with their scales — the arithmetic of
             // the RoPE + KV-write kernel (v3/kernels/fused_rope_partial_fp8kv.cu:54-214), without the 16-bit
             // round trip through HBM and without the extra launch.  64 threads per token, 3 tokens at a time.
-            __shared__ float s_amax[3][2];
+            __shared__ float s_amax[2][3][2];  // [round parity][token group][warp of the group]
             const RopeKv& rk = p.rope;
             const int tile = blockIdx.x;                       // == head index over Q heads, then K heads, then V heads
             const int kind = tile < rk.heads ? 0 : (tile < rk.heads + rk.kv_heads ? 1 : 2);
@@ -576,10 +576,13 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 // head absmax over the group's 64 threads (+inf carries "a value was not finite")
                 float am = (!isfinite(lo) || !isfinite(hi)) ? CUDART_INF_F : fmaxf(fabsf(lo), fabsf(hi));
                 am = rv::warp_max(am);
-                if ((threadIdx.x & 31) == 0) s_amax[grp][(threadIdx.x >> 5) & 1] = am;
-                __syncthreads();
-                am = fmaxf(s_amax[grp][0], s_amax[grp][1]);
-                __syncthreads();
+                // the two warps of a token group meet on a barrier of their own (ids 2-4), once per round: the
+                // rounds alternate between two copies of the scratch, and a warp cannot reach the round after next
+                // before its partner has read this one
+                float* sa = s_amax[it & 1][grp];
+                if ((threadIdx.x & 31) == 0) sa[(threadIdx.x >> 5) & 1] = am;
+                asm volatile("bar.sync %0, 64;" ::"r"(2 + grp) : "memory");
+                am = fmaxf(sa[0], sa[1]);
                 if (live && pos >= 0 && pos < rk.max_positions) {
                     const float sc = isinf(am) ? CUDART_NAN_F : fmaxf(am / 448.0f, 1e-12f);
                     const float inv = 1.0f / sc;
