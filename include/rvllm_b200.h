@@ -125,7 +125,7 @@ int rvllm_fp8_gemm_tc_status(int* status, int reset);
  * kv_head) scales) done in the GEMM's epilogue: the result of rvllm_fp8_gemm_channelscale into a
  * [M, (heads + 2*kv_heads)*128] 16-bit buffer followed by rvllm_rope_fp8kv_launch with rotary_dim =
  * head_dim, bit for bit, without the buffer and without the second launch.  head_dim must be 128 (one
- * 128-row weight tile is one head) and M <= 32; returns RVLLM_E_UNSUPPORTED for shapes it does not
+ * 128-row weight tile is one head) and M <= 128; returns RVLLM_E_UNSUPPORTED for shapes it does not
  * take (use the two calls).  dtype: the 16-bit type of the implied intermediate and of the tables. */
 int rvllm_fp8_gemm_qkv_rope_fp8kv(const void* a_fp8, const void* w_fp8, const float* a_scale, const float* w_scale, int M,
                                   int K, int heads, int kv_heads, int head_dim, int dtype, void* q_fp8, float* q_scale,

@@ -1030,7 +1030,7 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     const bool push = splits > 1 && BN <= 32 && tune().reduce != 1;
     // 64- and 128-row batch tiles: push as well, into the peers' idle rings (the partials would not fit behind them)
     const bool push_ring = splits > 1 && (BN == 64 || BN == 128) && tune().reduce != 1 &&
-                           (EPI == EPI_SCALE || EPI == EPI_RESIDUAL || EPI == EPI_F32);
+                           (EPI == EPI_SCALE || EPI == EPI_RESIDUAL || EPI == EPI_F32 || EPI == EPI_QKV_ROPE);
     const int ring_recv_bytes = push_ring ? splits * ((BN + splits - 1) / splits) * TILE_W * 4 : 0;
     const int min_stages = (push || push_ring) ? 2 : C::MIN_STAGES;
     if (stages < min_stages) stages = min_stages;
@@ -1069,8 +1069,8 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
         return rvhost::fail_msg(-3, "the argmax epilogue needs an unsplit launch and its partial buffers");
     if (EPI == EPI_RESIDUAL_A16 && (!g.a16 || !g.amax_part || g.amax_parts <= 0 || BN > 32))
         return rvhost::fail_msg(-3, "the 16-bit activation form needs a16, partial maxima and a batch tile of at most 32 rows");
-    if (EPI == EPI_QKV_ROPE && (!push || !rope))
-        return rvhost::fail_msg(-3, "the fused QKV epilogue needs a split-K launch with a batch tile of at most 32 rows");
+    if (EPI == EPI_QKV_ROPE && (!(push || push_ring) || !rope))
+        return rvhost::fail_msg(-3, "the fused QKV epilogue needs a split-K launch with a batch tile of at most 128 rows");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((g.N + TILE_W - 1) / TILE_W, splits, (g.M + BN - 1) / BN);
     cfg.blockDim = dim3(THREADS);
@@ -1178,15 +1178,24 @@ inline int launch(const TcArgs& g, void*, size_t, cudaStream_t s) {
 // (one weight tile per head), N = (heads + 2 * kv_heads) * 128, M <= 32.  dtype: 0 f16, 1 bf16 (the type
 // the unfused GEMM would have stored, and of the cos / sin tables).  -3: shape not taken, use the two kernels.
 inline int launch_qkv_rope(const TcArgs& g, const RopeKv& rk, int dtype, cudaStream_t s) {
-    if (g.K % 16 != 0 || g.M > 32 || g.N != (rk.heads + 2 * rk.kv_heads) * TILE_W)
+    if (g.K % 16 != 0 || g.M > 128 || g.N != (rk.heads + 2 * rk.kv_heads) * TILE_W)
         return rvhost::fail_msg(-3, "fused QKV epilogue: shape not taken");
     const Plan pl = plan_for(g.M, g.N, g.K);
     if (pl.splits < 2 || tune().reduce == 1) return rvhost::fail_msg(-3, "fused QKV epilogue: needs the split-K push form");
-    if (pl.bn == 16)
-        return dtype == 0 ? launch_one<16, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
-                          : launch_one<16, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
-    return dtype == 0 ? launch_one<32, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
-                      : launch_one<32, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+    switch (pl.bn) {
+        case 16:
+            return dtype == 0 ? launch_one<16, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
+                              : launch_one<16, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+        case 32:
+            return dtype == 0 ? launch_one<32, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
+                              : launch_one<32, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+        case 64:  // (64- and 128-row tiles: the push goes into the peers' idle rings)
+            return dtype == 0 ? launch_one<64, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
+                              : launch_one<64, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+        default:
+            return dtype == 0 ? launch_one<128, EPI_QKV_ROPE, __half>(g, pl.splits, pl.stages, s, &rk)
+                              : launch_one<128, EPI_QKV_ROPE, __nv_bfloat16>(g, pl.splits, pl.stages, s, &rk);
+    }
 }
 
 // Residual GEMM whose activation operand is given as 16-bit values plus per-row partial maxima: the per-token

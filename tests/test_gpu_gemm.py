@@ -315,7 +315,8 @@ def test_gemm_rejects_bad_arguments():
 
 
 @pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
-@pytest.mark.parametrize("M,heads,kv_heads,K", [(32, 32, 16, 5376), (7, 8, 4, 1024), (1, 4, 4, 640)])
+@pytest.mark.parametrize("M,heads,kv_heads,K", [(32, 32, 16, 5376), (7, 8, 4, 1024), (1, 4, 4, 640), (128, 32, 16, 5376),
+                                                 (100, 32, 16, 5376), (50, 8, 4, 1024), (64, 32, 16, 5376)])
 def test_fused_qkv_rope_epilogue_equals_gemm_then_rope(orc, dtype, M, heads, kv_heads, K):
     """The QKV GEMM with RoPE + Q quantisation + paged KV write in its epilogue must leave the same
     bytes and scale bits as the GEMM into a 16-bit buffer followed by the RoPE / KV-write kernel:

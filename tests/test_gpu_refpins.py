@@ -188,7 +188,7 @@ def test_rope_partial_fp8kv_bit_exact_vs_reference_kernel(orc, T, heads, kv_head
 
 
 @needs_ref
-@pytest.mark.parametrize("M,heads,kv_heads,K", [(32, 32, 16, 5376), (7, 8, 4, 1024)])
+@pytest.mark.parametrize("M,heads,kv_heads,K", [(32, 32, 16, 5376), (7, 8, 4, 1024), (128, 32, 16, 5376), (50, 8, 4, 1024)])
 def test_fused_qkv_rope_epilogue_bit_exact_vs_gemm_then_reference_rope_kernel(orc, M, heads, kv_heads, K):
     """The QKV GEMM with RoPE + Q quantisation + KV write in its epilogue against: the same GEMM into an
     f16 buffer, then the reference's own RoPE / KV-write kernel."""
