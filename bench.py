@@ -843,6 +843,66 @@ def ablation(torch, cfg, weights, batches, steps):
     return out
 
 
+GEMM_TRACE_POINTS = ["CTA runs", "predecessor complete", "first K block in shared memory", "last MMA issued",
+                     "accumulator complete", "partials exchanged", "outputs stored"]
+
+
+def gemm_trace(torch, cfg, weights, B, reps=5):
+    """Timeline of the tcgen05 GEMM launches of one decode step inside the CUDA graph: the kernel's own %globaltimer
+    stamps (earliest and latest CTA per point, rvllm_fp8_gemm_tc_trace), read after single graph replays.  Launch
+    order per layer: QKV, O, gate|up, down; the LM head closes the step.  Reported per kind, averaged over the
+    sliding layers: how long before its predecessor's completion the launch was resident, and the phases after it;
+    and the time between a launch's last store and the next launch's "predecessor complete" (the row kernel or the
+    attention in between, with both hand-offs)."""
+    import numpy as np
+    from rvllm_b200 import _lib
+    from rvllm_b200.stack import DecodeStack
+    L = _lib.lib()
+    c = dict(cfg, batch=B)
+    G = 4 * c["num_layers"] + 1
+    tr = torch.zeros((G, 16), dtype=torch.int64, device="cuda")
+    _lib.check(L.rvllm_fp8_gemm_tc_trace(tr.data_ptr(), G), "fp8_gemm_tc_trace")
+    try:
+        stack = DecodeStack(c, weights)      # the graph is recorded with the rows in place
+    finally:
+        L.rvllm_fp8_gemm_tc_trace(None, 0)
+    stack.seed_context(c["prompt_len"] - 1)
+    stack.run(4)
+    stack.sync()
+    acc = []
+    for _ in range(reps):
+        tr[:, 0::2] = -1                     # all ones: the even entries take a minimum
+        tr[:, 1::2] = 0
+        torch.cuda.synchronize()
+        stack.run(1)
+        stack.sync()
+        t = tr.cpu().numpy().view(np.uint64).astype(np.float64)
+        acc.append((t - t[0, 0]) / 1e3)      # us from the first CTA of the first GEMM
+    stack.close()
+    t = np.mean(acc, axis=0)                 # [G][16]
+    kinds = ["QKV (+RoPE / KV write)", "O projection", "gate|up", "down projection"]
+    global_every = c["global_every"]
+    rows = []
+    for k, kind in enumerate(kinds):
+        sel = [4 * l + k for l in range(1, c["num_layers"]) if not (global_every and (l + 1) % global_every == 0)]
+        first = lambda pt: t[sel, 2 * pt].mean()
+        last = lambda pt: t[sel, 2 * pt + 1].mean()
+        prev_end = np.mean([t[i - 1, 13] for i in sel])
+        rows.append({"launch": kind, "launches_averaged": len(sel),
+                     "resident_before_predecessor_done_us": last(1) - first(0),
+                     "previous_gemm_end_to_predecessor_done_us": first(1) - prev_end,
+                     "predecessor_done_to_first_k_block_us": last(2) - last(1),
+                     "first_k_block_to_last_mma_us": last(3) - last(2),
+                     "last_mma_to_accumulator_us": last(4) - last(3),
+                     "accumulator_to_exchange_us": (last(5) - last(4)) if t[sel[0], 11] > 0 else None,
+                     "to_outputs_stored_us": last(6) - (last(5) if t[sel[0], 11] > 0 else last(4)),
+                     "predecessor_done_to_end_us": last(6) - first(1)})
+    head = {"predecessor_done_to_end_us": t[G - 1, 13] - t[G - 1, 2], "start_to_end_us": t[G - 1, 13] - t[G - 1, 0]}
+    return {"batch": B, "layers": c["num_layers"], "points": GEMM_TRACE_POINTS, "per_kind": rows, "lm_head": head,
+            "step_span_us": float(t[:, 13].max()),
+            "note": "globaltimer stamps, mean of %d single graph replays; sliding layers 1.. averaged" % reps}
+
+
 def greedy_parity_block(steps):
     """The composition the headline number times (fused QKV+RoPE epilogue, tcgen05 attention leaving per-row
     maxima, O projection quantising its own A tiles, fused gate|up activation, cluster argmax) decoded greedily at
@@ -994,6 +1054,8 @@ def main():
                     help="only the decode attention at batch 64 with contexts uniform in [512, 32768]")
     ap.add_argument("--fused-block", type=int, default=0, choices=[0, 1],
                     help="1: run the step with the one-launch layer block (O projection .. next RMSNorm) instead of the chain")
+    ap.add_argument("--gemm-trace", action="store_true",
+                    help="only the in-graph timeline of the GEMM launches of a step (the kernels' own time stamps)")
     ap.add_argument("--ablate", default="", help="only the in-graph cost of each launch of a layer, for these batches (comma list)")
     ap.add_argument("--layer-block-trace", action="store_true",
                     help="only the layer-block kernel alone at the layer dimensions, with its stage-boundary time stamps")
@@ -1027,7 +1089,7 @@ def main():
         peak, src = measured_peaks()
         print(json.dumps({"roofline": dominant_kernel_roofline(torch, cfg, w, args.batch, peak, src)}))
         return
-    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels or args.layer_block_trace or args.ablate:
+    if args.gemm_sweep or args.ragged_attention or args.vs_ref_kernels or args.layer_block_trace or args.ablate or args.gemm_trace:
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the CUDA path has no CPU fallback")
@@ -1040,6 +1102,10 @@ def main():
             print(json.dumps({"ref_kernels": reference_kernel_table(torch, cfg)}))
         if args.layer_block_trace:
             print(json.dumps({"layer_block": layer_block_trace(torch, cfg, args.batch)}))
+        if args.gemm_trace:
+            from rvllm_b200.stack import random_weights
+            w = random_weights(cfg, seed=3)
+            print(json.dumps({"gemm_trace": gemm_trace(torch, cfg, w, args.batch)}))
         if args.ablate:
             from rvllm_b200.stack import random_weights
             w = random_weights(cfg, seed=3)

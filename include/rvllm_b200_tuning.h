@@ -35,6 +35,15 @@ void rvllm_fp8_gemm_tc_reduce(int mode);
 /* CTAs a split-K launch aims for (splits = round(target / weight tiles), at most 8, at least 4 K blocks each);
  * 0 restores the built-in 360.  Process-wide. */
 void rvllm_fp8_gemm_tc_split_target(int ctas);
+/* Timing aid of the tcgen05 GEMM: while a device buffer of `slots` x 16 u64 is set, every launch takes the next row
+ * (launch order, modulo `slots`; the count restarts with this call) and leaves, for each of 8 points, the
+ * %globaltimer stamp of the earliest and of the latest CTA to pass it: 0 CTA runs, 1 the kernel ahead in the stream
+ * is complete, 2 operands of the first K block in shared memory, 3 last MMA issued, 4 accumulator complete,
+ * 5 split-K partials exchanged (push forms), 6 outputs stored.  Even entries must be preset to all ones (they take a
+ * minimum), odd entries to 0.  A launch recorded into a CUDA graph keeps its row.  slots 0 or a null buffer: off.
+ * The stamps exist only in a library built with RVLLM_TC_TRACE=1 (they cost the decode step 1.2 % even when off);
+ * otherwise setting a buffer returns RVLLM_E_UNSUPPORTED. */
+int rvllm_fp8_gemm_tc_trace(void* device_u64_buffer, int slots);
 /* Split-K factor of one weight shape [N, K] (batch tiles up to 128 rows), four slots; splits 0 clears the slot. */
 void rvllm_fp8_gemm_tc_split_for(int slot, int N, int K, int splits);
 

@@ -71,6 +71,7 @@ SIGNATURES = {
     "rvllm_fp8_gemm_tc_reduce": (None, [_i32]),
     "rvllm_fp8_gemm_tc_split_target": (None, [_i32]),
     "rvllm_fp8_gemm_tc_split_for": (None, [_i32, _i32, _i32, _i32]),
+    "rvllm_fp8_gemm_tc_trace": (_i32, [_vp, _i32]),
     "rvllm_fp8_gemm_residual_from16": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "rvllm_fp8_gemm_qkv_rope_fp8kv": (_i32, [_vp] * 4 + [_i32] * 6 + [_vp] * 10 + [_i32] * 2 + [_vp]),
     "rvllm_fp8_gemm_lm_head_argmax_workspace": (_sz, [_i32, _i32]),

@@ -101,6 +101,8 @@ def build_library(force=False, verbose=False):
     def compile_one(unit):
         obj = os.path.join(OBJ, os.path.splitext(unit)[0] + ".o")
         cmd = [NVCC, *ARCH, *COMMON, "-Xptxas=-v", "-c", os.path.join(CSRC, unit), "-o", obj]
+        if os.environ.get("RVLLM_TC_TRACE", "0") not in ("", "0"):
+            cmd.insert(1, "-DRVLLM_TC_TRACE=1")  # timing-aid build: the GEMM's %globaltimer stamps (bench.py --gemm-trace)
         log = _run(cmd)
         check_register_budget(log)
         return obj, log

@@ -279,6 +279,18 @@ int rvllm_fp8_gemm_residual_from16(void* out, int dtype, const void* a16, const 
     return rc;
 }
 
+int rvllm_fp8_gemm_tc_trace(void* device_u64_buffer, int slots) {
+    rvtc::tune().trace = slots > 0 ? reinterpret_cast<unsigned long long*>(device_u64_buffer) : nullptr;
+    rvtc::tune().trace_slots = slots > 0 ? slots : 0;
+    rvtc::tune().trace_next = 0;
+#if RVLLM_TC_TRACE
+    return RVLLM_OK;
+#else
+    return device_u64_buffer && slots > 0
+               ? rv_fail(RVLLM_E_UNSUPPORTED, "the GEMM time stamps are not compiled into this build (RVLLM_TC_TRACE=1 python -m rvllm_b200.build)")
+               : RVLLM_OK;
+#endif
+}
 void rvllm_fp8_gemm_tc_split_for(int slot, int N, int K, int splits) {
     if (slot < 0 || slot >= 4) return;
     rvtc::tune().split_for[slot] = (splits >= 1 && splits <= 8 && N > 0 && K > 0)

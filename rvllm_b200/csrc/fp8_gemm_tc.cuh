@@ -93,6 +93,8 @@ struct TcParams {
     float* arg_val;
     int* arg_idx;
     float softcap;
+    // timing aid (null = off): 8 points x {earliest, latest} %globaltimer stamps over the CTAs of this launch
+    unsigned long long* trace;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -225,6 +227,25 @@ __device__ __forceinline__ bool arg_better(float cv, int ci, float bv, int bi) {
     return cv > bv || (cv == bv && ci < bi);
 }
 
+// Timing aid: the earliest and the latest CTA to pass point k of a launch (rvllm_fp8_gemm_tc_trace).  Compiled in
+// only with -DRVLLM_TC_TRACE=1: even switched off, the seven tests and calls cost the decode step 1.2 % (measured).
+#ifndef RVLLM_TC_TRACE
+#define RVLLM_TC_TRACE 0
+#endif
+__device__ __forceinline__ void trace_point(unsigned long long* tr, int k) {
+#if RVLLM_TC_TRACE
+    if (tr != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMin(tr + 2 * k, t);
+        atomicMax(tr + 2 * k + 1, t);
+    }
+#else
+    (void)tr;
+    (void)k;
+#endif
+}
+
 // Meeting point of the four epilogue warps alone (named barrier 1; the block-wide barrier is 0).
 __device__ __forceinline__ void epi_warps_sync() {
     __syncwarp();
@@ -277,6 +298,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     auto a_scale_of = [&](int m) -> float { return A16 ? s_ascale[m - m0] : p.a_scale[m]; };
     rv::pdl_launch();
     if (threadIdx.x == 0) {
+        trace_point(p.trace, 0);  // the CTA runs
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full + s, A16 ? 5 : 1);  // the producer's arrival (+ one per converting warp)
             mbar_init(empty + s, 1);
@@ -333,6 +355,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             s_ainv[threadIdx.x] = 1.0f / sc;
         }
         __syncthreads();
+        if (threadIdx.x == 0) trace_point(p.trace, 1);  // predecessor complete, row scales known
     }
     const bool push = S > 1 && p.push != 0;
     // push == 3: the receive buffer is the (by then idle) ring itself — batch tiles of 64 / 128 rows, whose partials
@@ -345,6 +368,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int pre = nkb < STAGES ? nkb : STAGES;  // (their weight tiles are already on the way)
             if (!A16) {
                 rv::pdl_wait();
+                trace_point(p.trace, 1);  // the kernel ahead in the stream is complete
                 for (int i = 0; i < pre; i++)
                     tma_load_2d(ring + (size_t)i * C::STAGE_BYTES + TILE_W * BK, &map_a, (kb_lo + i) * BK, m0, full + i);
             }
@@ -369,6 +393,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
                 alive = mbar_wait(full + s, ph, 2);
                 if (!alive) break;
+                if (i == 0) trace_point(p.trace, 2);  // both operands of the first K block are in shared memory
                 tc_fence_after();
                 const uint32_t w_addr = smem_u32(ring + (size_t)s * C::STAGE_BYTES);
                 const uint64_t adesc = smem_desc_sw128(w_addr);
@@ -380,6 +405,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 umma_commit(empty + s);  // frees the stage once these MMAs have read it
             }
             umma_commit(acc_ready);  // arrives when every MMA issued above has completed
+            trace_point(p.trace, 3);  // the last MMA is issued
         }
     }
     if (A16 && warp >= EPI_WARP0) {
@@ -482,6 +508,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // own MMAs complete = every load into this CTA's ring has landed and been read: the ring is free;
             // once the whole cluster has said so, every ring may be written
             if (warp >= EPI_WARP0 && nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+            if (threadIdx.x == EPI_WARP0 * 32) trace_point(p.trace, 4);  // the accumulator is complete
             cluster_arrive();
         }
         cluster_wait();  // every CTA of the cluster is running (and, in the ring form, done with its ring)
@@ -489,6 +516,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane;
             if (!push_ring && nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+            if (!push_ring && threadIdx.x == EPI_WARP0 * 32) trace_point(p.trace, 4);  // the accumulator is complete
             tc_fence_after();
             const uint32_t slot = smem_u32(recv) + (uint32_t)((split * LC) * TILE_W + r) * 4u;  // [split][0][r]
             uint32_t owner = 0, lc_off = 0;
@@ -525,6 +553,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             cluster_arrive();
             cluster_wait();
         }
+        if (threadIdx.x == 0) trace_point(p.trace, 5);  // the partials of this CTA's columns are in its receive buffer
         if constexpr (EPI == EPI_QKV_ROPE) {
             // Fused QKV epilogue.  The weight tile is one head (128 output channels): this CTA holds, for
             // each batch column it finishes, the whole head of one token.  Round to the activation type (the
@@ -687,6 +716,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         fetch_res(0);
         bool ready = true;
         if (nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
+        if (threadIdx.x == EPI_WARP0 * 32) trace_point(p.trace, 4);  // the accumulator is complete
         tc_fence_after();
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -873,6 +903,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     }
     __syncthreads();
+    if (threadIdx.x == 0) trace_point(p.trace, 6);  // every output of the CTA is stored
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -1012,6 +1043,9 @@ struct Tune {
     std::atomic<int> reduce{0};  // 1: force the pull form of the split-K reduction; 2: push form with point-to-point mbarriers
     std::atomic<int> split_target{0};  // CTAs a split launch aims for (0: the built-in 360)
     std::atomic<long long> split_for[4] = {};  // per-shape overrides: (N << 40) | (K << 8) | splits, 0 = unused
+    std::atomic<unsigned long long*> trace{nullptr};  // timing aid: [trace_slots][16] u64 on the device, or null
+    std::atomic<int> trace_slots{0};
+    std::atomic<int> trace_next{0};                   // launches made since the buffer was set
 };
 inline Tune& tune() {
     static Tune t;
@@ -1065,6 +1099,11 @@ int launch_one(const TcArgs& g, int splits, int stages, cudaStream_t s, const Ro
     p.arg_val = g.arg_val;
     p.arg_idx = g.arg_idx;
     p.softcap = g.softcap;
+    p.trace = nullptr;
+    if (unsigned long long* tr = tune().trace.load()) {  // every launch its own row, in launch order
+        const int slots = tune().trace_slots.load();
+        if (slots > 0) p.trace = tr + (size_t)(tune().trace_next.fetch_add(1) % slots) * 16;
+    }
     if (EPI == EPI_ARGMAX && (splits != 1 || !g.arg_val || !g.arg_idx))
         return rvhost::fail_msg(-3, "the argmax epilogue needs an unsplit launch and its partial buffers");
     if (EPI == EPI_RESIDUAL_A16 && (!g.a16 || !g.amax_part || g.amax_parts <= 0 || BN > 32))
