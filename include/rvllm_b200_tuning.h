@@ -26,11 +26,12 @@ int rvllm_b200_get_pdl(void);
 /* Overrides of the tcgen05 kernel's automatic choices, for tuning runs: TMA ring depth
  * (2..8) and split-K factor (1..8); 0 restores the automatic choice.  Process-wide. */
 void rvllm_fp8_gemm_tc_tune(int stages, int splits);
-/* Form of the split-K reduction inside a cluster: 0 automatic (partials are pushed into the finishing
- * CTA's receive buffer when the batch tile has at most 32 rows and the cluster meets once, else they
- * are pulled out of the peers' rings), 1 always pull, 2 push with point-to-point mbarrier arrivals
- * instead of the cluster barrier (measured within 1 % of form 0; kept as a cross-check).  All forms
- * sum in cluster-rank order, so their results are bitwise equal (tested). */
+/* Form of the split-K reduction inside a cluster: 0 automatic (batch tiles up to 32 rows: partials are pushed into
+ * the finishing CTA's receive buffer and every sender arrives on the owner's mbarrier; 64- and 128-row tiles: pushed
+ * into the peers' idle rings between two cluster barriers; 256-row tiles: pulled out of the peers' rings), 1 always
+ * pull, 2 the same as 0, 3 the small-tile push completed by one cluster barrier instead of the mbarrier arrivals
+ * (1.3 us per layer slower in the decode graph; kept as a cross-check).  All forms sum in cluster-rank order, so their
+ * results are bitwise equal (tested). */
 void rvllm_fp8_gemm_tc_reduce(int mode);
 /* CTAs a split-K launch aims for (splits = round(target / weight tiles), at most 8, at least 4 K blocks each);
  * 0 restores the built-in 360.  Process-wide. */

@@ -297,7 +297,7 @@ void rvllm_fp8_gemm_tc_split_for(int slot, int N, int K, int splits) {
                                        ? (((long long)N << 40) | ((long long)K << 8) | (long long)splits) : 0ll;
 }
 void rvllm_fp8_gemm_tc_split_target(int ctas) { rvtc::tune().split_target = ctas > 0 ? ctas : 0; }
-void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode == 1 || mode == 2 ? mode : 0; }
+void rvllm_fp8_gemm_tc_reduce(int mode) { rvtc::tune().reduce = mode >= 1 && mode <= 3 ? mode : 0; }
 
 size_t rvllm_fp8_gemm_gateup_workspace(int M, int I, int K) {
     if (M <= 0 || I <= 0 || K <= 0) return 0;

@@ -190,7 +190,7 @@ def test_split_k_push_and_pull_reductions_are_bitwise_equal(orc, M, splits, mode
         res = torch.from_numpy(np.random.default_rng(8).standard_normal((M, N)).astype(np.float32)).to(dt).cuda()
     outs = []
     try:
-        for reduce_mode in (0, 1, 2):  # push + cluster barrier, pull, push + point-to-point mbarriers
+        for reduce_mode in (0, 1, 3):  # push + mbarrier arrivals (ring push above 32 rows), pull, push + cluster barrier
             _lib.lib().rvllm_fp8_gemm_tc_tune(0, splits)
             _lib.lib().rvllm_fp8_gemm_tc_reduce(reduce_mode)
             outs.append(run(TC, a, a_s, w, w_s, dt, residual=res))
