@@ -280,6 +280,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     uint64_t* acc_ready = empty + MAX_STAGES;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_ready + 1);
     uint64_t* recv_bar = reinterpret_cast<uint64_t*>(header + 512);  // push reduction: all partials for this CTA have landed
+    uint64_t* free_bar = recv_bar + 1;                               // ring push: every CTA of the cluster is done with its ring
     const int STAGES = p.stages;
 
     cg::cluster_group cluster = cg::this_cluster();
@@ -305,6 +306,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         mbar_init(acc_ready, 1);
         mbar_init(recv_bar, (uint32_t)gridDim.y * 4u);  // one arrival per epilogue warp of every CTA of the cluster
+        mbar_init(free_bar, (uint32_t)gridDim.y);       // one arrival per CTA of the cluster
         fence_barrier_init();
         // This thread is also the TMA producer.  Weights never depend on the previous kernel: fill the ring
         // with weight tiles right away (before the block even meets; the barriers are this thread's own),
@@ -362,7 +364,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // would not fit behind it.  The cluster then meets after the main loops instead ("every ring is free").
     const bool push_ring = BN >= 64 && push && p.push >= 3;  // (a compile-time "no" for the small tiles)
     const bool push_mbar = p.push == 2 || p.push == 3;       // completion: arrivals on the owners' mbarriers (else a cluster barrier)
-    if (push && !push_ring) cluster_arrive();  // "this CTA runs": peers wait for it (long since complete) before their first remote store
+    // "this CTA runs": peers wait for it (long since complete) before their first remote store or arrival
+    if (push && (!push_ring || push_mbar)) cluster_arrive();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -510,9 +513,19 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // once the whole cluster has said so, every ring may be written
             if (warp >= EPI_WARP0 && nkb > 0) ready = mbar_wait(acc_ready, 0, 3);
             if (threadIdx.x == EPI_WARP0 * 32) trace_point(p.trace, 4);  // the accumulator is complete
-            cluster_arrive();
+            if (push_mbar) {
+                // one warp tells every CTA of the cluster (itself included); the pushing warps wait for all of them
+                cluster_wait();  // (every CTA runs: its barriers exist)
+                if (warp == EPI_WARP0) {
+                    __syncwarp();
+                    if (lane < S) mbar_arrive_peer(free_bar, (uint32_t)lane);
+                }
+                if (warp >= EPI_WARP0) mbar_wait_cluster(free_bar, 0, 8);
+            } else {
+                cluster_arrive();
+            }
         }
-        cluster_wait();  // every CTA of the cluster is running (and, in the ring form, done with its ring)
+        if (!(push_ring && push_mbar)) cluster_wait();  // every CTA of the cluster is running (and, in the ring + barrier form, done with its ring)
         if (warp >= EPI_WARP0) {
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane;
