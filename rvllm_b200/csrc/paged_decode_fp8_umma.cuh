@@ -221,13 +221,13 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     uint64_t* s_free = s_ready + 2;                        // [2] softmax has read the score tile
     uint64_t* p_ready = s_free + 2;                        // P tile written (and accumulator rescaled)
     uint64_t* pv_done = p_ready + 1;                       // the tile's second product has completed
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* merge_bar = pv_done + 1;                     // cluster form, chunk 0: the other chunks' partials have landed
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(merge_bar + 1);
     float* red = reinterpret_cast<float*>(aux + 256);      // [2][4][8] tile maxima, then [4][8] sums (96 floats)
     unsigned* s_bad = reinterpret_cast<unsigned*>(aux + 256 + 96 * 4);
     float* recv = reinterpret_cast<float*>(aux + C::AUX_BYTES);  // cluster-combine form only: [chunk][head][HD + 2]
 
     rv::pdl_launch();
-    if constexpr (CL) asm volatile("barrier.cluster.arrive.release;" ::: "memory");  // "this CTA runs"
     const int kvh = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.heads / p.kv_heads;
@@ -245,6 +245,7 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         }
         mbar_init(p_ready, 4);
         mbar_init(pv_done, 1);
+        if constexpr (CL) mbar_init(merge_bar, (uint32_t)(gridDim.y - 1) * 4u);  // four warps of every other CTA of the cluster
         *s_bad = 0;
         fence_barrier_init();
     }
@@ -296,6 +297,8 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // "this CTA runs and its barriers exist": the other CTAs of the cluster wait for this before they touch its memory
+    if constexpr (CL) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     const uint32_t tmem_base = *tmem_holder;
     const int nh = group < GT ? group : GT;  // query heads of this KV head (the launcher guarantees group <= GT)
     if (warp != 0) {
@@ -670,14 +673,44 @@ paged_decode_fp8_umma_kernel(const __grid_constant__ CUtensorMap map_k, const __
         // cluster run" (the arrival was the kernel's first statement; shared memory of a CTA that has not started
         // must not be written), then "the partials are in the chunk-0 CTA's shared memory".
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-        if (chunk != 0 && active && nchunks > 1 && warp >= 2) {
-            bar_softmax();  // the staged partial is complete
-            const uint32_t dst = smem_u32(recv + (size_t)chunk * nh * PSTRIDE);
-            for (int i = tid - 64; i < nh * PSTRIDE; i += 128) st_cluster_f32(dst + (uint32_t)i * 4u, 0u, recv[i]);
+        // The partials travel without a second cluster-wide barrier: every softmax warp of every other CTA — with a
+        // partial or not — arrives (release, cluster scope) on chunk 0's mbarrier after its stores; chunk 0 waits for
+        // all of them; the others are done.
+        if (chunk != 0 && warp >= 2) {
+            if (active && nchunks > 1) {
+                bar_softmax();  // the staged partial is complete
+                const uint32_t dst = smem_u32(recv + (size_t)chunk * nh * PSTRIDE);
+                for (int i = tid - 64; i < nh * PSTRIDE; i += 128) st_cluster_f32(dst + (uint32_t)i * 4u, 0u, recv[i]);
+            }
+            asm volatile("fence.acq_rel.cluster;" ::: "memory");  // every lane's stores, before the warp's one arrival
+            __syncwarp();
+            if (lane == 0)
+                asm volatile(
+                    "{\n\t.reg .b32 ra;\n\t"
+                    "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+                    "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(merge_bar)), "r"(0u)
+                    : "memory");
         }
-        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-        if (chunk == 0 && active && nchunks > 1 && warp >= 2) {
+        bool merged = true;
+        if (chunk == 0 && warp >= 2) {
+            unsigned* s_flag = s_bad + 1;  // one thread waits (bounded), the four warps share its verdict
+            if (tid == 64) {
+                uint32_t ok = 0;
+                for (uint32_t spin = 0; spin < WAIT_LIMIT && !ok; spin++)
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                        "selp.u32 %0, 1, 0, p;\n\t}"
+                        : "=r"(ok)
+                        : "r"(smem_u32(merge_bar)), "r"(0u)
+                        : "memory");
+                if (!ok) atomicCAS(&g_status, 0, (10 << 16) | (int)(blockIdx.x & 0xffff));
+                *s_flag = ok;
+            }
+            bar_softmax();
+            merged = *s_flag != 0;
+        }
+        if (chunk == 0 && active && nchunks > 1 && warp >= 2 && merged) {
             // The merge of the combine kernel, chunk by chunk in order (same arithmetic, same order), then the
             // store and the per-(sequence, KV head) maximum of the single-chunk path.
             const int row = (warp - 2) * 32 + lane;
