@@ -142,3 +142,18 @@ def test_build_register_budget_check():
     build.check_register_budget(ok)  # the 256-row tile runs one CTA per SM: no budget
     with pytest.raises(RuntimeError, match="register budget"):
         build.check_register_budget(ok.replace("Used 96 registers", "Used 97 registers"))
+
+
+def test_library_is_not_the_time_stamp_build():
+    """The GEMM's %globaltimer stamps are a build option (they cost the decode step 1.2 % even when off): the library
+    that ships must refuse a trace buffer, unless the build was asked for them."""
+    import ctypes
+    from rvllm_b200 import _lib
+
+    if os.environ.get("RVLLM_TC_TRACE", "0") not in ("", "0"):
+        pytest.skip("a time-stamp build was asked for")
+    L = _lib.lib()
+    try:
+        assert L.rvllm_fp8_gemm_tc_trace(ctypes.c_void_p(4096), 1) == _lib.E_UNSUPPORTED
+    finally:
+        assert L.rvllm_fp8_gemm_tc_trace(None, 0) == _lib.OK
