@@ -35,6 +35,19 @@ def test_every_declared_symbol_is_exported(L):
     assert not missing, missing
 
 
+def test_every_exported_function_is_declared():
+    """The reverse direction: nothing callable is exported behind the headers' back.  The only
+    undeclared C symbols are the host stubs of the `extern "C" __global__` kernels, whose names
+    are the reference's PTX entry points (they end in `_kernel`)."""
+    import subprocess
+    from rvllm_b200 import _lib, build
+    build.build_library()
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = {f[2] for f in (l.split() for l in out.splitlines()) if len(f) == 3 and f[1] == "T" and not f[2].startswith("_")}
+    extra = sorted(n for n in exported - declared_symbols() if not n.endswith("_kernel"))
+    assert not extra, extra
+
+
 def test_python_binding_table_matches_header():
     from rvllm_b200 import _lib
     assert set(_lib.SIGNATURES) <= declared_symbols()
